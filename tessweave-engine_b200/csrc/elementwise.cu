@@ -1,0 +1,213 @@
+// Memory-bound kernels around the matrix products: embedding rows into the
+// fp32 residual stream, residual add fused with RMSNorm, bias + rotary position
+// encoding fused with the write of K and V into cache pages, SiLU(gate)*up.
+//
+// All statistics, angles and sums are fp32; `T` is the storage type of
+// activations and cache (float or bf16).  Every kernel takes any row width.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding: resid[n, :] = float(table[ids[n], :]).  No scaling
+// (reference: flow_engine/model.py:176).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ table,
+                             const int* __restrict__ ids, int hidden, int vocab, int* status) {
+    const int n = blockIdx.x;
+    int id = ids[n];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicOr(status, TW_ERR_TOKEN_ID);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) resid[(size_t)n * hidden + i] = 0.f;
+        return;
+    }
+    const T* row = table + (size_t)id * hidden;
+    float* dst = resid + (size_t)n * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = tw_to_float(row[i]);
+}
+
+TW_EXPORT int tw_embed(void* resid, const void* table, const int* ids, int n_tokens, int hidden, int vocab,
+                       int dtype, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (dtype == TW_F32)
+        embed_kernel<float><<<n_tokens, 256, 0, stream>>>((float*)resid, (const float*)table, ids, hidden, vocab, status);
+    else
+        embed_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>((float*)resid, (const __nv_bfloat16*)table, ids,
+                                                                   hidden, vocab, status);
+    return TW_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// Residual add + RMSNorm.
+//   v = resid[src] + delta[src]            (delta may be null)
+//   resid[src] = v                         (only when rows == null)
+//   out[r] = T( (v * (1 / sqrt(mean(v^2) + eps))) * weight )
+// rows != null selects source rows (the final norm runs on the wanted rows
+// only); the residual stream is then left untouched.
+// Reference: flow_engine/model.py:21-23 (fp32 statistics).  The reference casts
+// the normalised value to the activation type before the multiply by the
+// weight; here the product is formed in fp32 and rounded once.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,
+                                   const float* __restrict__ weight, float eps, int hidden,
+                                   const int* __restrict__ rows) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* x = resid + (size_t)src * hidden;
+    const T* d = delta ? delta + (size_t)src * hidden : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = x[i];
+        if (d) v += tw_to_float(d[i]);
+        if (!rows && d) x[i] = v;
+        ss += v * v;
+    }
+    ss = tw_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    T* o = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = x[i];
+        if (rows && d) v += tw_to_float(d[i]);
+        o[i] = tw_from_float<T>((v * inv) * weight[i]);
+    }
+}
+
+TW_EXPORT int tw_add_rmsnorm(void* out, float* resid, const void* delta, const float* weight, float eps,
+                             int n_rows, int hidden, const int* rows, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    if (dtype == TW_F32)
+        add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((float*)out, resid, (const float*)delta, weight, eps,
+                                                                  hidden, rows);
+    else
+        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
+            (__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, weight, eps, hidden, rows);
+    return TW_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// Bias + rotary position encoding + cache write, one block per token.
+//
+// qkv row layout: [q heads | k heads | v heads], each head `D` wide.
+//   x += bias                                       (bias may be null)
+//   angle_i = float(position) * inv_freq[i]         (fp32; inv_freq may be null: no rotation)
+//   y[i]        = x[i] * cos - x[i + D/2] * sin     (rotate-half pairing)
+//   y[i + D/2]  = x[i + D/2] * cos + x[i] * sin
+// q is rewritten in place; rotated k and v go to the page that the request's
+// block table names for this position:
+//   page = table[slot_row][pos / P];  element ((page * Hkv + h) * P + pos % P) * D + d
+// Reference: flow_engine/model.py:26-33,184-187; flow_engine/cache.py:93-100.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const float* __restrict__ bias,
+                                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                     const int* __restrict__ seq_slot, const int* __restrict__ block_table,
+                                     int table_stride, const float* __restrict__ inv_freq, T* __restrict__ k_cache,
+                                     T* __restrict__ v_cache, int Hq, int Hkv, int D, int page_size, int num_pages,
+                                     int write_cache, int* status) {
+    const int n = blockIdx.x;
+    const int s = seq_of_token[n];
+    if (s < 0) return;  // padding row of a fixed-size batch
+    const int pos = positions[n];
+    const int half = D >> 1;
+    T* row = qkv + (size_t)n * qkv_stride;
+
+    int page = -1;
+    if (write_cache) {
+        const int blk = pos / page_size;
+        page = blk < table_stride ? block_table[(size_t)seq_slot[s] * table_stride + blk] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicOr(status, TW_ERR_PAGE);
+            page = -1;
+        }
+    }
+    const int in_page = pos % page_size;
+    const int rot_heads = write_cache ? Hq + Hkv : Hq;
+
+    for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
+        const int head = idx / half, i = idx - head * half;
+        const int col = head * D + i;
+        float x1 = tw_to_float(row[col]), x2 = tw_to_float(row[col + half]);
+        if (bias) { x1 += bias[col]; x2 += bias[col + half]; }
+        float y1 = x1, y2 = x2;
+        if (inv_freq) {
+            const float ang = (float)pos * inv_freq[i];
+            float sn, cs;
+            sincosf(ang, &sn, &cs);
+            y1 = x1 * cs - x2 * sn;
+            y2 = x2 * cs + x1 * sn;
+        }
+        if (head < Hq) {
+            row[col] = tw_from_float<T>(y1);
+            row[col + half] = tw_from_float<T>(y2);
+        } else if (page >= 0) {
+            const int kvh = head - Hq;
+            T* dst = k_cache + (((size_t)page * Hkv + kvh) * page_size + in_page) * D;
+            dst[i] = tw_from_float<T>(y1);
+            dst[i + half] = tw_from_float<T>(y2);
+        }
+    }
+    if (page >= 0) {
+        const int voff = (Hq + Hkv) * D;
+        for (int idx = threadIdx.x; idx < Hkv * D; idx += blockDim.x) {
+            const int kvh = idx / D, d = idx - kvh * D;
+            float v = tw_to_float(row[voff + idx]);
+            if (bias) v += bias[voff + idx];
+            v_cache[(((size_t)page * Hkv + kvh) * page_size + in_page) * D + d] = tw_from_float<T>(v);
+        }
+    }
+}
+
+TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* bias, const int* positions,
+                               const int* seq_of_token, const int* seq_slot, const int* block_table, int table_stride,
+                               const float* inv_freq, void* k_cache, void* v_cache, int n_tokens, int Hq, int Hkv,
+                               int D, int page_size, int num_pages, int write_cache, int dtype, int* status,
+                               cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (D <= 0 || (D & 1)) return (int)cudaErrorInvalidValue;
+    const int work = (Hq + Hkv) * (D / 2);
+    const int threads = work >= 1024 ? 256 : 128;
+    if (dtype == TW_F32)
+        rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>(
+            (float*)qkv, qkv_stride, bias, positions, seq_of_token, seq_slot, block_table, table_stride, inv_freq,
+            (float*)k_cache, (float*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache, status);
+    else
+        rope_kv_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+            (__nv_bfloat16*)qkv, qkv_stride, bias, positions, seq_of_token, seq_slot, block_table, table_stride,
+            inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache,
+            status);
+    return TW_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU activation: out[n, i] = silu(gate[n, i]) * up[n, i], silu(z) = z / (1 + exp(-z)),
+// with gate = gate_up[n, i] and up = gate_up[n, I + i] (rows packed [gate; up]).
+// Reference: flow_engine/model.py:76-80.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, long total) {
+    long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long step = (long)gridDim.x * blockDim.x;
+    for (; idx < total; idx += step) {
+        const long n = idx / inter;
+        const int i = (int)(idx - n * inter);
+        const float g = tw_to_float(gate_up[n * 2 * inter + i]);
+        const float u = tw_to_float(gate_up[n * 2 * inter + inter + i]);
+        const float act = g / (1.0f + expf(-g));
+        out[idx] = tw_from_float<T>(act * u);
+    }
+}
+
+TW_EXPORT int tw_silu_mul(void* out, const void* gate_up, int n_rows, int inter, int dtype, cudaStream_t stream) {
+    const long total = (long)n_rows * inter;
+    if (total <= 0) return 0;
+    long blocks = (total + 255) / 256;
+    if (blocks > 148L * 16) blocks = 148L * 16;
+    if (dtype == TW_F32)
+        silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
+    else
+        silu_mul_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)out,
+                                                                        (const __nv_bfloat16*)gate_up, inter, total);
+    return TW_LAUNCH_CHECK();
+}

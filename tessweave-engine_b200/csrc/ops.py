@@ -1,0 +1,198 @@
+"""Python side of the CUDA kernels: thin launch wrappers over the compiled libraries.
+
+Each wrapper checks what the kernel assumes (device, element type, contiguity,
+sizes it can take) and raises a clear error otherwise; a kernel is never handed
+a shape it would compute wrongly.  There is no fallback: if a library cannot be
+compiled or loaded, the call fails.  Launches go to torch's current stream, so
+they order with library matrix products and can be captured in CUDA graphs.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_void_p, c_int, c_float
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 activations, not {dtype}")
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(cond: bool, message: str) -> None:
+    if not cond:
+        raise KernelError(message)
+
+
+def _cuda(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel operands must live on a CUDA device; this engine has no CPU path")
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code} at launch "
+                          f"({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
+
+
+_sigs_done: set[str] = set()
+
+
+def _fn(lib_name: str, fn_name: str, defines=None):
+    lib = load_library(lib_name, defines)
+    fn = getattr(lib, fn_name)
+    key = f"{lib_name}:{fn_name}:{defines}"
+    if key not in _sigs_done:
+        fn.restype = c_int
+        _sigs_done.add(key)
+    return fn
+
+
+# ---------------------------------------------------------------------------
+def embed(resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, n_tokens: int, status: torch.Tensor) -> None:
+    """resid[n] = float(table[ids[n]]); resid is fp32 [>=n_tokens, hidden]."""
+    _cuda(resid, table, ids, status)
+    _need(resid.dtype == torch.float32 and resid.is_contiguous(), "embed: residual stream must be contiguous fp32")
+    _need(table.is_contiguous() and ids.dtype == torch.int32, "embed: table contiguous, ids int32")
+    _need(resid.shape[0] >= n_tokens and ids.numel() >= n_tokens and resid.shape[1] == table.shape[1],
+          "embed: shapes disagree")
+    code = _fn("elementwise", "tw_embed")(_ptr(resid), _ptr(table), _ptr(ids), c_int(n_tokens),
+                                          c_int(table.shape[1]), c_int(table.shape[0]),
+                                          c_int(dtype_code(table.dtype)), _ptr(status), _stream())
+    _check(code, "embed")
+
+
+def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
+                eps: float, n_rows: int, rows: torch.Tensor | None = None) -> None:
+    """resid += delta (in place, fp32) and out = rmsnorm(resid) * weight.
+
+    With ``rows`` (int32 indices) only those rows are normalised, into out[0..n_rows),
+    and the residual stream is left as it was.
+    """
+    _cuda(out, resid, delta, weight, rows)
+    hidden = resid.shape[1]
+    _need(resid.dtype == torch.float32 and resid.is_contiguous(), "rmsnorm: residual stream must be contiguous fp32")
+    _need(weight.dtype == torch.float32 and weight.numel() == hidden, "rmsnorm: weight must be fp32 [hidden]")
+    _need(out.is_contiguous() and out.shape[1] == hidden and out.shape[0] >= n_rows, "rmsnorm: bad output")
+    if delta is not None:
+        _need(delta.dtype == out.dtype and delta.is_contiguous() and delta.shape[1] == hidden,
+              "rmsnorm: delta must match the output type and width")
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.numel() >= n_rows, "rmsnorm: rows must be int32")
+    else:
+        _need(resid.shape[0] >= n_rows, "rmsnorm: fewer residual rows than asked")
+    code = _fn("elementwise", "tw_add_rmsnorm")(_ptr(out), _ptr(resid), _ptr(delta), _ptr(weight), c_float(eps),
+                                                c_int(n_rows), c_int(hidden), _ptr(rows),
+                                                c_int(dtype_code(out.dtype)), _stream())
+    _check(code, "add_rmsnorm")
+
+
+def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                  seq_slot: torch.Tensor, block_table: torch.Tensor, inv_freq: torch.Tensor | None,
+                  k_pages: torch.Tensor, v_pages: torch.Tensor, n_tokens: int, n_q_heads: int, n_kv_heads: int,
+                  head_dim: int, write_cache: bool, status: torch.Tensor) -> None:
+    """Add the bias, rotate q and k by position, store k and v in their cache pages.
+
+    qkv: [>=n_tokens, (Hq + 2 Hkv) * D]; k_pages/v_pages: [pages, Hkv, page, D].
+    """
+    _cuda(qkv, bias, positions, seq_of_token, seq_slot, block_table, inv_freq, k_pages, v_pages, status)
+    width = (n_q_heads + 2 * n_kv_heads) * head_dim
+    _need(qkv.stride(1) == 1 and qkv.shape[1] == width, "rope: qkv row must be [q | k | v] heads")
+    _need(head_dim % 2 == 0, f"rope: head_dim {head_dim} must be even")
+    _need(k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype and k_pages.is_contiguous()
+          and v_pages.is_contiguous(), "rope: cache pages must be contiguous and of the activation type")
+    _need(tuple(k_pages.shape[1:]) == (n_kv_heads, k_pages.shape[2], head_dim) and v_pages.shape == k_pages.shape,
+          "rope: cache pages must be [pages, kv_heads, page, head_dim]")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(),
+          "rope: block table must be contiguous int32 [requests, blocks]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == width, "rope: bias must be fp32 [(Hq+2Hkv)*D]")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2, "rope: inv_freq must be fp32 [D/2]")
+    code = _fn("elementwise", "tw_rope_kv_write")(
+        _ptr(qkv), c_int(qkv.stride(0)), _ptr(bias), _ptr(positions), _ptr(seq_of_token), _ptr(seq_slot),
+        _ptr(block_table), c_int(block_table.shape[1]), _ptr(inv_freq), _ptr(k_pages), _ptr(v_pages),
+        c_int(n_tokens), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(k_pages.shape[2]),
+        c_int(k_pages.shape[0]), c_int(1 if write_cache else 0), c_int(dtype_code(qkv.dtype)), _ptr(status), _stream())
+    _check(code, "rope_kv_write")
+
+
+def rotate_heads(rows: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                 inv_freq: torch.Tensor | None, n_tokens: int, n_heads: int, head_dim: int) -> None:
+    """In place on the first ``n_heads`` heads of each packed row: add the bias, then rotate
+    by position (either may be absent).  Nothing is written to a cache."""
+    _cuda(rows, bias, positions, seq_of_token, inv_freq)
+    _need(rows.stride(1) == 1 and rows.shape[1] >= n_heads * head_dim and head_dim % 2 == 0, "rotate_heads: bad rows")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() >= n_heads * head_dim, "rotate_heads: bias must be fp32")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2, "rotate_heads: inv_freq fp32 [D/2]")
+    code = _fn("elementwise", "tw_rope_kv_write")(
+        _ptr(rows), c_int(rows.stride(0)), _ptr(bias), _ptr(positions), _ptr(seq_of_token), _ptr(None), _ptr(None),
+        c_int(0), _ptr(inv_freq), _ptr(None), _ptr(None), c_int(n_tokens), c_int(n_heads), c_int(0), c_int(head_dim),
+        c_int(1), c_int(0), c_int(0), c_int(dtype_code(rows.dtype)), _ptr(None), _stream())
+    _check(code, "rotate_heads")
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, n_rows: int) -> None:
+    """out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]."""
+    _cuda(out, gate_up)
+    inter = out.shape[1]
+    _need(gate_up.shape[1] == 2 * inter and gate_up.is_contiguous() and out.is_contiguous()
+          and gate_up.dtype == out.dtype, "silu_mul: gate_up must be contiguous [n, 2I] of the output type")
+    code = _fn("elementwise", "tw_silu_mul")(_ptr(out), _ptr(gate_up), c_int(n_rows), c_int(inter),
+                                             c_int(dtype_code(out.dtype)), _stream())
+    _check(code, "silu_mul")
+
+
+def attention_generic(out: torch.Tensor, q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                      seq_slot: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      n_tokens: int, n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
+                      status: torch.Tensor) -> None:
+    """Exact paged causal attention, one block per (token, head).  q may be a column
+    slice of the packed qkv buffer (row stride is passed on)."""
+    _cuda(out, q, positions, seq_of_token, seq_slot, block_table, k_pages, v_pages, status)
+    _need(head_dim <= 256, f"attention: head_dim {head_dim} above 256 is not supported")
+    _need(n_q_heads % n_kv_heads == 0, "attention: query heads must be a multiple of key/value heads")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype, "attention: bad operands")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: bad block table")
+    code = _fn("attention_generic", "tw_attn_generic")(
+        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(positions), _ptr(seq_of_token),
+        _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(n_tokens),
+        c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]),
+        c_int(window), c_float(scale), c_int(dtype_code(q.dtype)), _ptr(status), _stream())
+    _check(code, "attention_generic")
+
+
+def sample(out: torch.Tensor, logits: torch.Tensor, n_rows: int, temperature: torch.Tensor | None = None,
+           seed: torch.Tensor | None = None, counter: torch.Tensor | None = None) -> None:
+    """out[r] = chosen token of row r (int32).  Rows with temperature 0 are greedy."""
+    _cuda(out, logits, temperature, seed, counter)
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and logits.dim() == 2, "sample: logits fp32 [rows, vocab]")
+    _need(out.dtype == torch.int32 and out.numel() >= n_rows, "sample: out must be int32")
+    if temperature is not None:
+        _need(temperature.dtype == torch.float32 and seed is not None and counter is not None
+              and seed.dtype == torch.int64 and counter.dtype == torch.int64, "sample: temperature fp32, seed/counter int64")
+    code = _fn("sampling", "tw_sample")(_ptr(out), _ptr(logits), c_int(n_rows), c_int(logits.shape[1]),
+                                        _ptr(temperature), _ptr(seed), _ptr(counter), _stream())
+    _check(code, "sample")

@@ -1,0 +1,125 @@
+// Token selection on fp32 logits, one block per row.
+//
+//   temperature == 0:  the largest logit; the lowest index wins a tie
+//                      (reference: flow_engine/engine.py:155-156, argmax).
+//   temperature  > 0:  e_v = exp((x_v - max) / temperature);  u = uniform(seed, counter);
+//                      the first index whose running sum of e exceeds u * sum(e)
+//                      (reference: flow_engine/engine.py:157-158 samples from
+//                      softmax(logits / T) with a per-request seeded generator; its CPU
+//                      stream cannot be reproduced on the device, so the engine defines
+//                      its own counter-based uniform, below).
+//
+// uniform(seed, counter): splitmix64 of seed + (counter + 1) * 0x9E3779B97F4A7C15,
+// top 24 bits, times 2^-24.  A request's draws depend on its own seed and on how
+// many tokens it has drawn, never on its neighbours in the batch.
+#include "common.cuh"
+
+__host__ __device__ inline float tw_uniform(unsigned long long seed, unsigned long long counter) {
+    unsigned long long z = seed + (counter + 1ull) * 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+#define TW_SAMPLE_THREADS 1024
+
+__global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int vocab,
+                              const float* __restrict__ temperature, const long long* __restrict__ seed,
+                              const long long* __restrict__ counter) {
+    __shared__ float sval[32];
+    __shared__ int sidx[32];
+    __shared__ float swarp[32];
+    __shared__ float sbcast[2];
+    __shared__ int sbest;
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* x = logits + (size_t)r * vocab;
+    const int chunk = (vocab + TW_SAMPLE_THREADS - 1) / TW_SAMPLE_THREADS;
+    const int begin = tid * chunk, end = min(vocab, begin + chunk);
+
+    // -- maximum and its lowest index
+    float best = -INFINITY;
+    int besti = 0x7fffffff;
+    for (int v = begin; v < end; ++v) {
+        const float f = x[v];
+        if (f > best) { best = f; besti = v; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+        if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+    }
+    if (lane == 0) { sval[warp] = best; sidx[warp] = besti; }
+    __syncthreads();
+    if (warp == 0) {
+        best = sval[lane]; besti = sidx[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+            if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+        }
+        if (lane == 0) { sbcast[0] = best; sbest = besti; }
+    }
+    __syncthreads();
+    const float mx = sbcast[0];
+    const float temp = temperature ? temperature[r] : 0.f;
+    if (!(temp > 0.f)) {
+        if (tid == 0) out[r] = sbest < vocab ? sbest : 0;
+        return;
+    }
+
+    // -- running sums of e in index order: per-thread chunk sums, then a block scan
+    float local = 0.f;
+    for (int v = begin; v < end; ++v) local += expf((x[v] - mx) / temp);
+    float incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    if (lane == 31) swarp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        float w = swarp[lane];
+        float wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += t;
+        }
+        swarp[lane] = wi - w;  // exclusive prefix of the warp totals
+        if (lane == 31) sbcast[1] = wi;
+    }
+    if (tid == 0) sbest = 0x7fffffff;
+    __syncthreads();
+    const float total = sbcast[1];
+    const float u = tw_uniform((unsigned long long)seed[r], (unsigned long long)counter[r]);
+    const float target = u * total;
+    // Every thread walks its own chunk from its exclusive prefix; the lowest index at
+    // which a running sum passes the target wins.
+    float c = swarp[warp] + (incl - local);
+    int cand = 0x7fffffff;
+    for (int v = begin; v < end; ++v) {
+        c += expf((x[v] - mx) / temp);
+        if (c > target) { cand = v; break; }
+    }
+    if (cand != 0x7fffffff) atomicMin(&sbest, cand);
+    __syncthreads();
+    if (tid == 0) out[r] = sbest < vocab ? sbest : vocab - 1;
+}
+
+// temperature, seed and counter may be null: every row is then greedy.
+TW_EXPORT int tw_sample(int* out, const float* logits, int n_rows, int vocab, const float* temperature,
+                        const long long* seed, const long long* counter, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (vocab <= 0) return (int)cudaErrorInvalidValue;
+    sample_kernel<<<n_rows, TW_SAMPLE_THREADS, 0, stream>>>(out, logits, vocab, temperature, seed, counter);
+    return TW_LAUNCH_CHECK();
+}
+
+// Host-side copy of the uniform, for tools that want to predict a draw.
+TW_EXPORT float tw_uniform_host(unsigned long long seed, unsigned long long counter) {
+    return tw_uniform(seed, counter);
+}

@@ -1,0 +1,182 @@
+"""The step function.
+
+One step takes a batch of (request, its next tokens) -- portions of prompts beside
+single decoded tokens, cut anywhere -- runs exactly those tokens as one flat batch
+against the cache that earlier steps left, and returns fp32 logits at the wanted
+rows.  The reference's forward takes uniform [B, T] batches only (flow_engine/
+model.py:167-204) and its scheduler runs decode and prefill as two calls
+(flow_engine/engine.py:249-260); here both are rows of one call.
+
+All per-step metadata travels in one pinned host buffer and one host-to-device
+copy.  The device copy lives at a fixed address, as do the workspace buffers, so a
+decode-only step of a given size can be captured once as a CUDA graph and replayed.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..csrc import ops
+from ..models.model import Model
+from ..parts.base import StepContext, Workspace
+from ..parts.linear import configure_matmul_precision
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request in a step."""
+    slot: int                      # request slot (from the cache manager's lease)
+    tokens: list[int]              # consecutive tokens, the first at position ``start``
+    start: int                     # tokens of this request already in the cache
+    want: list[int] = field(default_factory=list)   # indices into ``tokens`` whose logits are wanted
+
+
+class StepError(RuntimeError):
+    """A kernel reported a bad token id or a missing page."""
+
+
+_STATUS_TEXT = {1: "a token id lies outside the vocabulary", 2: "a block table holds no page where one is needed",
+                4: "a bounded wait in a kernel ran out"}
+
+
+class ModelRunner:
+    def __init__(self, model: Model, cache: CacheManager, max_step_tokens: int, max_step_seqs: int,
+                 max_logit_rows: int | None = None, cuda_graphs: bool = True):
+        if model.runtime.device.type != "cuda":
+            raise RuntimeError("the step function runs on a CUDA device only; there is no CPU path")
+        configure_matmul_precision()
+        self.model, self.cache = model, cache
+        self.device = model.runtime.device
+        self.max_tokens = int(max_step_tokens)
+        self.max_seqs = int(max_step_seqs)
+        self.max_rows = int(max_logit_rows or max_step_tokens)
+        self.workspace = Workspace(self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.vocab = model.spec.vocab_size
+        # ---- one staging buffer for all metadata of a step (int32 units)
+        n, s, m = self.max_tokens, self.max_seqs, self.max_rows
+        sizes = [("seed", 2 * m), ("counter", 2 * m), ("temperature", m), ("token_ids", n), ("positions", n),
+                 ("seq_of_token", n), ("seq_slot", s), ("seq_q_start", s), ("seq_q_len", s), ("seq_kv_len", s),
+                 ("logit_rows", m)]
+        self._offsets, total = {}, 0
+        for name, size in sizes:
+            self._offsets[name] = (total, size)
+            total += size + (-size % 4)          # keep every field 16-byte aligned
+        self._host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
+        self._dev = torch.zeros(total, dtype=torch.int32, device=self.device)
+        self._h = {k: self._host[o:o + sz] for k, (o, sz) in self._offsets.items()}
+        self._d = {k: self._dev[o:o + sz] for k, (o, sz) in self._offsets.items()}
+        self.sampled = torch.zeros(m + 1, dtype=torch.int32, device=self.device)   # ids, then the status word
+        self._sampled_host = torch.zeros(m + 1, dtype=torch.int32, pin_memory=True)
+        self._staged = torch.cuda.Event()
+        self._staged.record()
+        self.use_graphs = bool(cuda_graphs and model.graph_safe)
+        self._graphs: dict[int, tuple] = {}
+        self.launches = 0
+
+    # ------------------------------------------------------------------ batch building
+    def _stage(self, entries: list[StepEntry], pad_to: int = 0) -> tuple[StepContext, int]:
+        """Fill the staging buffer for ``entries`` and copy it to the device."""
+        h = self._h
+        self._staged.synchronize()       # the previous step's copy has read the pinned buffer
+        n = sum(len(e.tokens) for e in entries)
+        s = len(entries)
+        if n == 0:
+            raise ValueError("a step needs at least one token")
+        rows_total = max(n, pad_to)
+        seqs_total = max(s, pad_to) if pad_to else s
+        if rows_total > self.max_tokens or seqs_total > self.max_seqs:
+            raise ValueError(f"step of {n} tokens / {s} requests exceeds the runner's limits "
+                             f"({self.max_tokens} tokens, {self.max_seqs} requests)")
+        ids, pos, sot, rows = [], [], [], []
+        slot, qs, ql, kl = [], [], [], []
+        cursor = 0
+        for si, e in enumerate(entries):
+            t = len(e.tokens)
+            if t == 0:
+                raise ValueError("an entry without tokens cannot be part of a step")
+            ids.extend(e.tokens)
+            pos.extend(range(e.start, e.start + t))
+            sot.extend([si] * t)
+            slot.append(e.slot); qs.append(cursor); ql.append(t); kl.append(e.start + t)
+            for w in e.want:
+                if not 0 <= w < t:
+                    raise ValueError(f"wanted place {w} lies outside the {t} tokens of the entry")
+                rows.append(cursor + w)
+            cursor += t
+        m = len(rows)
+        if m > self.max_rows:
+            raise ValueError(f"{m} wanted rows exceed the runner's limit of {self.max_rows}")
+        pad = rows_total - n
+        h["token_ids"][:rows_total] = torch.tensor(ids + [0] * pad, dtype=torch.int32)
+        h["positions"][:rows_total] = torch.tensor(pos + [0] * pad, dtype=torch.int32)
+        h["seq_of_token"][:rows_total] = torch.tensor(sot + [-1] * pad, dtype=torch.int32)
+        spad = seqs_total - s
+        h["seq_slot"][:seqs_total] = torch.tensor(slot + [0] * spad, dtype=torch.int32)
+        h["seq_q_start"][:seqs_total] = torch.tensor(qs + [0] * spad, dtype=torch.int32)
+        h["seq_q_len"][:seqs_total] = torch.tensor(ql + [0] * spad, dtype=torch.int32)
+        h["seq_kv_len"][:seqs_total] = torch.tensor(kl + [0] * spad, dtype=torch.int32)
+        if m:
+            h["logit_rows"][:m] = torch.tensor(rows, dtype=torch.int32)
+        self._dev.copy_(self._host, non_blocking=True)
+        self._staged.record()
+        self.cache.sync_tables()
+        d = self._d
+        ctx = StepContext(
+            runtime=self.model.runtime, workspace=self.workspace, n_tokens=rows_total, n_seqs=seqs_total,
+            token_ids=d["token_ids"][:rows_total], positions=d["positions"][:rows_total],
+            seq_of_token=d["seq_of_token"][:rows_total], seq_slot=d["seq_slot"][:seqs_total],
+            seq_q_start=d["seq_q_start"][:seqs_total], seq_q_len=d["seq_q_len"][:seqs_total],
+            seq_kv_len=d["seq_kv_len"][:seqs_total], status=self.status,
+            host_slot=slot, host_q_start=qs, host_q_len=ql, host_kv_len=kl,
+            max_q_len=max(ql), max_kv_len=max(kl), decode_only=all(t == 1 for t in ql))
+        return ctx, m
+
+    # ------------------------------------------------------------------ the step
+    @torch.inference_mode()
+    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+        """Run the tokens of ``entries`` and return fp32 logits ``[wanted rows, vocab]`` on the
+        device, in the order of the entries and of their ``want`` lists."""
+        ctx, m = self._stage(entries)
+        logits = self.workspace.get("runner.logits", (max(m, 1), self.vocab), torch.float32)
+        self.model.forward(ctx, self.cache.views(), self._d["logit_rows"], m, logits)
+        return logits[:m]
+
+    # ------------------------------------------------------------------ sampling
+    def stage_sampling(self, temperature: list[float], seed: list[int], counter: list[int]) -> None:
+        """Per wanted row: temperature (0 = greedy), seed and draw counter.  Must be called
+        before ``step`` of the same batch, as it travels in the same copy."""
+        m = len(temperature)
+        self._h["temperature"].view(torch.float32)[:m] = torch.tensor(temperature, dtype=torch.float32)
+        self._h["seed"].view(torch.int64)[:m] = torch.tensor(seed, dtype=torch.int64)
+        self._h["counter"].view(torch.int64)[:m] = torch.tensor(counter, dtype=torch.int64)
+
+    @torch.inference_mode()
+    def sample(self, logits: torch.Tensor, greedy_only: bool = False) -> list[int]:
+        """Choose one token per row of ``logits`` on the device; one copy brings the ids and
+        the kernels' status word to the host."""
+        m = logits.shape[0]
+        if greedy_only:
+            ops.sample(self.sampled, logits, m)
+        else:
+            ops.sample(self.sampled, logits, m, self._d["temperature"].view(torch.float32),
+                       self._d["seed"].view(torch.int64), self._d["counter"].view(torch.int64))
+        self.sampled[m:m + 1].copy_(self.status)
+        self._sampled_host[:m + 1].copy_(self.sampled[:m + 1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        out = self._sampled_host[:m + 1].tolist()
+        self._raise_on_status(out[m])
+        return out[:m]
+
+    # ------------------------------------------------------------------ errors
+    def _raise_on_status(self, code: int) -> None:
+        if code:
+            self.status.zero_()
+            what = "; ".join(text for bit, text in _STATUS_TEXT.items() if code & bit) or f"code {code}"
+            raise StepError(f"a kernel refused part of the step: {what}")
+
+    def check_status(self) -> None:
+        """Read the kernels' status word (synchronises) and raise if a kernel refused something."""
+        self._raise_on_status(int(self.status.item()))

@@ -1,0 +1,90 @@
+"""Grouped-query attention over a paged cache."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import (Mixer, PagedKV, PagedView, PartSpec, Runtime, StepContext, WeightDecl, build_part,
+                   register_part)
+from .linear import matmul_nt
+
+
+@register_part("mixer", "gqa_attention")
+class GQAAttention(Mixer):
+    """q/k/v projections (optionally biased), position encoding on q and k, paged causal
+    attention with ``n_heads / n_kv_heads`` query heads per key/value head, output projection.
+
+        q, k, v = split(h @ Wqkv.T + b)                 rows packed [Wq; Wk; Wv]
+        q, k    = position(q), position(k)
+        cache[slot(position)] = k, v
+        out_h   = softmax(q_h . k_{h // group} * scale  over keys p <= position [, p > position - window]) @ v
+        delta   = out @ Wo.T
+
+    Reference: flow_engine/model.py:36-55 (projections, packing), 183-201 (forward),
+    flow_engine/cache.py:93-100 (slots).  Weight names are the checkpoint's.
+    """
+
+    def __init__(self, runtime: Runtime, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 qkv_bias: bool, position: PartSpec, scale: float | None = None, window: int | None = None,
+                 out_bias: bool = False):
+        super().__init__(runtime)
+        if min(hidden, n_heads, n_kv_heads, head_dim) <= 0 or n_heads % n_kv_heads:
+            raise ValueError("attention: heads must be positive and n_heads a multiple of n_kv_heads")
+        if head_dim % 2 or head_dim > 256:
+            raise ValueError(f"attention: head_dim {head_dim} must be even and at most 256")
+        if out_bias:
+            raise ValueError("attention: a bias on the output projection is not implemented")
+        if window is not None and window <= 0:
+            raise ValueError("attention: window must be positive or None")
+        self.hidden, self.n_heads, self.n_kv_heads, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
+        self.scale = float(scale) if scale is not None else head_dim ** -0.5
+        self.window = window
+        self.q_size, self.kv_size = n_heads * head_dim, n_kv_heads * head_dim
+        self.qkv_width = self.q_size + 2 * self.kv_size
+        self.position = build_part("position", position, runtime)
+        self.w_qkv = runtime.empty(self.qkv_width, hidden)
+        self.b_qkv = torch.empty(self.qkv_width, dtype=torch.float32, device=runtime.device) if qkv_bias else None
+        self.w_o = runtime.empty(hidden, self.q_size)
+
+    def weights(self) -> list[WeightDecl]:
+        q, kv = self.q_size, self.kv_size
+        spans = (("q_proj", 0, q), ("k_proj", q, q + kv), ("v_proj", q + kv, q + 2 * kv))
+        decls = [WeightDecl(f"{n}.weight", (e - b, self.hidden), dest=self.w_qkv[b:e]) for n, b, e in spans]
+        if self.b_qkv is not None:
+            decls += [WeightDecl(f"{n}.bias", (e - b,), role="vector", dest=self.b_qkv[b:e]) for n, b, e in spans]
+        decls.append(WeightDecl("o_proj.weight", (self.hidden, self.q_size), dest=self.w_o))
+        return decls
+
+    def cache_need(self) -> PagedKV:
+        return PagedKV(self.n_kv_heads, self.head_dim, self.window)
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache, write_cache: bool) -> torch.Tensor:
+        if not isinstance(cache, PagedView):
+            raise TypeError("gqa_attention needs a paged key/value cache")
+        n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
+        qkv = ws.get("attn.qkv", (n, self.qkv_width), dt)
+        matmul_nt(qkv, h, self.w_qkv)
+        table = self.position.fused_rotary_table(self.head_dim)
+        if table is None:
+            # generic path: bias, then the position part's own transformation, then the cache write
+            if self.b_qkv is not None:
+                ops.rotate_heads(qkv, self.b_qkv, ctx.positions, ctx.seq_of_token, None, n,
+                                 self.n_heads + 2 * self.n_kv_heads, self.head_dim)
+            self.position.apply(ctx, qkv, self.n_heads + self.n_kv_heads, self.head_dim)
+            bias = None
+        else:
+            bias = self.b_qkv
+        ops.rope_kv_write(qkv, bias, ctx.positions, ctx.seq_of_token, ctx.seq_slot, cache.block_table, table,
+                          cache.k_pages, cache.v_pages, n, self.n_heads, self.n_kv_heads, self.head_dim,
+                          write_cache, ctx.status)
+        out = ws.get("attn.out", (n, self.q_size), dt)
+        self._attend(ctx, out, qkv, cache)
+        delta = ws.get("mixer.delta", (n, self.hidden), dt)
+        matmul_nt(delta, out, self.w_o)
+        return delta
+
+    def _attend(self, ctx: StepContext, out: torch.Tensor, qkv: torch.Tensor, cache: PagedView) -> None:
+        q = qkv[:, : self.q_size]
+        ops.attention_generic(out, q, ctx.positions, ctx.seq_of_token, ctx.seq_slot, cache.block_table,
+                              cache.k_pages, cache.v_pages, ctx.n_tokens, self.n_heads, self.n_kv_heads,
+                              self.head_dim, self.window or 0, self.scale, ctx.status)

@@ -1,0 +1,274 @@
+"""Interfaces of the parts a model is put together from, and their registries.
+
+A model is a list of blocks; a block arranges a mixer, a feed-forward and their
+norms; a mixer may use a position encoding.  Every part gets its sizes and
+constants as parameters, declares the weights it wants by name, says what cache it
+needs, and runs on the rows of a step.  No part knows which model it is in.
+
+A part kind is registered under a name in its category; a model description
+(``ModelSpec``) names kinds and parameters only, so a new mixer, feed-forward,
+norm or position encoding is added by registering it: no framework file changes.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+
+# ---------------------------------------------------------------------------
+# what a part is described by
+# ---------------------------------------------------------------------------
+@dataclass(frozen=True)
+class PartSpec:
+    """Kind name plus keyword parameters of one part."""
+    kind: str
+    params: dict = field(default_factory=dict)
+
+    def with_params(self, **more) -> "PartSpec":
+        return PartSpec(self.kind, {**self.params, **more})
+
+
+@dataclass
+class WeightDecl:
+    """One tensor a part expects from the checkpoint.
+
+    ``name`` is relative to the part's prefix.  ``role`` decides how it is kept:
+    ``matrix`` in the run's element type, ``vector`` always in fp32 (a tensor stored
+    in 32 bits stays so; bf16 widens exactly), ``table_int`` in int32.  ``dest`` is
+    the device storage the loader copies into, usually a slice of a packed buffer.
+    ``init`` is the random-weights rule: ``normal`` ~ N(0, std), ``one_plus_normal``
+    ~ 1 + N(0, 0.1), ``zeros``.
+    """
+    name: str
+    shape: tuple[int, ...]
+    role: str = "matrix"
+    init: str = "normal"
+    dest: torch.Tensor | None = None
+
+
+# ---------------------------------------------------------------------------
+# what a part may need from the cache manager
+# ---------------------------------------------------------------------------
+@dataclass(frozen=True)
+class PagedKV:
+    """Keys and values for every token (or the last ``window`` tokens), in pages."""
+    kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class FixedState:
+    """A state of fixed size per request (``numel`` elements of ``dtype``)."""
+    numel: int
+    dtype: torch.dtype = torch.float32
+
+
+# ---------------------------------------------------------------------------
+# run-time handles
+# ---------------------------------------------------------------------------
+@dataclass
+class Runtime:
+    """Where and in which element type a model lives."""
+    device: torch.device
+    dtype: torch.dtype
+
+    def empty(self, *shape, dtype=None) -> torch.Tensor:
+        return torch.empty(*shape, dtype=dtype or self.dtype, device=self.device)
+
+
+class Workspace:
+    """Named scratch tensors that only ever grow; shared by all parts of a model.
+
+    A buffer asked for under one name is reused by every layer, so the memory of a
+    step does not grow with depth, and addresses stay fixed for CUDA graphs.
+    """
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._buffers: dict[str, torch.Tensor] = {}
+        self.frozen = False
+
+    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        numel = 1
+        for s in shape:
+            numel *= int(s)
+        buf = self._buffers.get(name)
+        if buf is None or buf.dtype != dtype or buf.numel() < numel:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name!r} would have to grow while a CUDA graph holds its address")
+            buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            self._buffers[name] = buf
+        return buf[:numel].view(*shape)
+
+    def reserve(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> None:
+        self.get(name, shape, dtype)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._buffers.values())
+
+
+@dataclass
+class PagedView:
+    """One cache layer of a paged group, as a mixer sees it."""
+    k_pages: torch.Tensor          # [pages, kv_heads, page_size, head_dim]
+    v_pages: torch.Tensor
+    block_table: torch.Tensor      # int32 [request slots, max blocks], -1 where no page is held
+    page_size: int
+    window: int | None
+    host_tables: Any = None        # callable slot -> list[int], for parts that want the table on the host
+
+
+@dataclass
+class StateView:
+    """One cache layer of fixed-size per-request state."""
+    state: torch.Tensor            # [request slots, numel]
+
+
+@dataclass
+class StepContext:
+    """Everything a part may read about the step that is running.
+
+    Device tensors are int32.  ``n_tokens`` rows are live; rows beyond belong to the
+    padding of a fixed-size (graph) batch and have ``seq_of_token == -1``.
+    """
+    runtime: Runtime
+    workspace: Workspace
+    n_tokens: int                  # rows in this step (including padding rows)
+    n_seqs: int
+    token_ids: torch.Tensor        # [n_tokens]
+    positions: torch.Tensor        # [n_tokens] absolute position of each row in its request
+    seq_of_token: torch.Tensor     # [n_tokens] index into the per-sequence arrays, -1 = padding
+    seq_slot: torch.Tensor         # [n_seqs] request slot (row of block tables and state)
+    seq_q_start: torch.Tensor      # [n_seqs] first row of the sequence in this step
+    seq_q_len: torch.Tensor        # [n_seqs] rows of the sequence in this step
+    seq_kv_len: torch.Tensor       # [n_seqs] tokens the request holds after this step
+    status: torch.Tensor           # int32 [1] error bits written by kernels
+    # host copies of the per-sequence arrays, for parts that loop on the host
+    host_slot: list[int] = field(default_factory=list)
+    host_q_start: list[int] = field(default_factory=list)
+    host_q_len: list[int] = field(default_factory=list)
+    host_kv_len: list[int] = field(default_factory=list)
+    max_q_len: int = 1
+    max_kv_len: int = 1
+    decode_only: bool = False      # every sequence brings exactly one token
+
+
+# ---------------------------------------------------------------------------
+# part base classes
+# ---------------------------------------------------------------------------
+class Part:
+    """Common behaviour: parameters in, weight declarations out."""
+    graph_safe = True   # False if forward() syncs with the host or allocates
+
+    def __init__(self, runtime: Runtime):
+        self.runtime = runtime
+
+    def weights(self) -> list[WeightDecl]:
+        return []
+
+    def finalize(self) -> None:
+        """Called once after every declared weight has been filled."""
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for w in self.weights():
+            if w.dest is not None:
+                base = w.dest.untyped_storage().data_ptr()
+                if (base, w.dest.storage_offset()) not in seen:
+                    seen.add((base, w.dest.storage_offset()))
+                    total += w.dest.numel() * w.dest.element_size()
+        return total
+
+
+class Norm(Part):
+    """out = norm(resid [+ delta]); updates the fp32 residual stream in place."""
+
+    def forward(self, ctx: StepContext, out: torch.Tensor, resid: torch.Tensor, delta: torch.Tensor | None,
+                n_rows: int, rows: torch.Tensor | None = None) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Encodes positions into queries and keys.
+
+    ``apply`` rewrites the q and k heads of the packed rows in place.  A mixer that
+    can fuse the encoding into another kernel asks ``fused_rotary_table()``; ``None``
+    means "call apply()".
+    """
+
+    def apply(self, ctx: StepContext, qk: torch.Tensor, n_heads: int, head_dim: int) -> None:
+        raise NotImplementedError
+
+    def fused_rotary_table(self, head_dim: int) -> torch.Tensor | None:
+        return None
+
+
+class Mixer(Part):
+    """Mixes information between the tokens of a request (attention here)."""
+
+    def cache_need(self) -> PagedKV | FixedState | None:
+        return None
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache: PagedView | StateView | None,
+                write_cache: bool) -> torch.Tensor:
+        """h: [n_tokens, hidden] normalised rows.  Returns the delta for the residual stream."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """Token-wise transformation (dense or routed)."""
+
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of a mixer and a feed-forward around the residual stream."""
+
+    def forward(self, ctx: StepContext, stream: "ResidualStream", cache, write_cache: bool) -> None:
+        raise NotImplementedError
+
+    def parts(self) -> dict[str, Part]:
+        raise NotImplementedError
+
+
+@dataclass
+class ResidualStream:
+    """The fp32 residual rows plus a delta the next norm still has to add."""
+    resid: torch.Tensor
+    pending: torch.Tensor | None = None
+
+
+# ---------------------------------------------------------------------------
+# registries
+# ---------------------------------------------------------------------------
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+_REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {c: {} for c in CATEGORIES}
+
+
+def register_part(category: str, kind: str):
+    """Class decorator: make ``kind`` buildable in ``category``."""
+    if category not in _REGISTRY:
+        raise KeyError(f"unknown part category {category!r}; one of {CATEGORIES}")
+
+    def deco(cls):
+        _REGISTRY[category][kind] = cls
+        cls.kind = kind
+        return cls
+    return deco
+
+
+def build_part(category: str, spec: PartSpec, runtime: Runtime, **extra) -> Part:
+    try:
+        cls = _REGISTRY[category][spec.kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRY.get(category, {}))) or "none"
+        raise KeyError(f"no {category} part of kind {spec.kind!r} is registered (known: {known})") from None
+    return cls(runtime, **spec.params, **extra)
+
+
+def registered(category: str) -> list[str]:
+    return sorted(_REGISTRY[category])

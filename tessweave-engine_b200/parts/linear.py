@@ -1,0 +1,33 @@
+"""Matrix products ``out = x @ w.T`` (w stored [out_features, in_features], as nn.Linear).
+
+The reference's engine runs its projections through a library (nn.Linear, i.e.
+cuBLAS: flow_engine/model.py:39-43,71-73,108); so does this function where no
+hand-written kernel takes the shape.  float32 products run in true fp32: TF32 and
+every other reduced-precision matrix mode is switched off before the first call.
+bfloat16 products accumulate in fp32 (no reduced-precision split-K sums).
+"""
+from __future__ import annotations
+
+import torch
+
+_configured = False
+
+
+def configure_matmul_precision() -> None:
+    """No TF32 in fp32 products, no bf16 accumulation in bf16 products."""
+    global _configured
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.set_float32_matmul_precision("highest")
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    _configured = True
+
+
+def matmul_nt(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """out[n, o] = sum_i x[n, i] * w[o, i]; all three of one element type."""
+    if not _configured:
+        configure_matmul_precision()
+    if not x.is_cuda:
+        raise RuntimeError("matrix products run on the GPU only; this engine has no CPU path")
+    torch.mm(x, w.t(), out=out)
+    return out
