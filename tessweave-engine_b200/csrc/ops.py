@@ -56,9 +56,11 @@ def _check(code: int, what: str) -> None:
 
 
 _sigs_done: set[str] = set()
+LAUNCHES = [0]      # kernel launchers called so far (each call launches at least one kernel)
 
 
 def _fn(lib_name: str, fn_name: str, defines=None):
+    LAUNCHES[0] += 1
     lib = load_library(lib_name, defines)
     fn = getattr(lib, fn_name)
     key = f"{lib_name}:{fn_name}:{defines}"

@@ -33,6 +33,9 @@ class StepEntry:
     want: list[int] = field(default_factory=list)   # indices into ``tokens`` whose logits are wanted
 
 
+GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
 class StepError(RuntimeError):
     """A kernel reported a bad token id or a missing page."""
 
@@ -51,7 +54,7 @@ class ModelRunner:
         self.device = model.runtime.device
         self.max_tokens = int(max_step_tokens)
         self.max_seqs = int(max_step_seqs)
-        self.max_rows = int(max_logit_rows or max_step_tokens)
+        self.max_rows = max(int(max_logit_rows or max_step_tokens), self.max_seqs)
         self.workspace = Workspace(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.vocab = model.spec.vocab_size
@@ -74,11 +77,13 @@ class ModelRunner:
         self._staged.record()
         self.use_graphs = bool(cuda_graphs and model.graph_safe)
         self._graphs: dict[int, tuple] = {}
+        self.graph_kernels: dict[int, int] = {}      # bucket -> this engine's kernels inside the captured graph
         self.launches = 0
 
     # ------------------------------------------------------------------ batch building
-    def _stage(self, entries: list[StepEntry], pad_to: int = 0) -> tuple[StepContext, int]:
-        """Fill the staging buffer for ``entries`` and copy it to the device."""
+    def _stage(self, entries: list[StepEntry], pad_to: int = 0, all_rows: bool = False) -> tuple[StepContext, int]:
+        """Fill the staging buffer for ``entries`` and copy it to the device.  ``pad_to`` pads the
+        batch with rows that belong to no request; ``all_rows`` asks for the logits of every row."""
         h = self._h
         self._staged.synchronize()       # the previous step's copy has read the pinned buffer
         n = sum(len(e.tokens) for e in entries)
@@ -106,6 +111,8 @@ class ModelRunner:
                     raise ValueError(f"wanted place {w} lies outside the {t} tokens of the entry")
                 rows.append(cursor + w)
             cursor += t
+        if all_rows:
+            rows = list(range(rows_total))
         m = len(rows)
         if m > self.max_rows:
             raise ValueError(f"{m} wanted rows exceed the runner's limit of {self.max_rows}")
@@ -131,24 +138,103 @@ class ModelRunner:
             seq_q_start=d["seq_q_start"][:seqs_total], seq_q_len=d["seq_q_len"][:seqs_total],
             seq_kv_len=d["seq_kv_len"][:seqs_total], status=self.status,
             host_slot=slot, host_q_start=qs, host_q_len=ql, host_kv_len=kl,
-            max_q_len=max(ql), max_kv_len=max(kl), decode_only=all(t == 1 for t in ql))
+            max_q_len=max(ql), max_kv_len=max(kl), decode_only=all(t == 1 for t in ql), fixed_shape=bool(pad_to))
         return ctx, m
+
+    def _padding_context(self, rows: int, logit_rows: int) -> StepContext:
+        """A step of ``rows`` padding rows: every kernel runs, none touches the cache."""
+        h = self._h
+        self._staged.synchronize()
+        h["token_ids"][:rows] = 0
+        h["positions"][:rows] = 0
+        h["seq_of_token"][:rows] = -1
+        seqs = min(rows, self.max_seqs)
+        for key in ("seq_slot", "seq_q_start", "seq_q_len", "seq_kv_len"):
+            h[key][:seqs] = 0
+        h["logit_rows"][:logit_rows] = torch.arange(logit_rows, dtype=torch.int32) % rows
+        self._dev.copy_(self._host, non_blocking=True)
+        self._staged.record()
+        d = self._d
+        return StepContext(
+            runtime=self.model.runtime, workspace=self.workspace, n_tokens=rows, n_seqs=seqs,
+            token_ids=d["token_ids"][:rows], positions=d["positions"][:rows], seq_of_token=d["seq_of_token"][:rows],
+            seq_slot=d["seq_slot"][:seqs], seq_q_start=d["seq_q_start"][:seqs], seq_q_len=d["seq_q_len"][:seqs],
+            seq_kv_len=d["seq_kv_len"][:seqs], status=self.status, host_slot=[0] * seqs, host_q_start=[0] * seqs,
+            host_q_len=[0] * seqs, host_kv_len=[0] * seqs, max_q_len=1,
+            max_kv_len=self.cache.max_blocks * self.cache.page_size, decode_only=(rows <= self.max_seqs),
+            fixed_shape=True)
 
     # ------------------------------------------------------------------ the step
     @torch.inference_mode()
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
         """Run the tokens of ``entries`` and return fp32 logits ``[wanted rows, vocab]`` on the
         device, in the order of the entries and of their ``want`` lists."""
+        if self.use_graphs and entries and all(len(e.tokens) == 1 for e in entries):
+            bucket = next((b for b in GRAPH_BUCKETS if len(entries) <= b <= self.max_seqs), None)
+            if bucket is not None:
+                return self._graph_step(entries, bucket)
         ctx, m = self._stage(entries)
         logits = self.workspace.get("runner.logits", (max(m, 1), self.vocab), torch.float32)
         self.model.forward(ctx, self.cache.views(), self._d["logit_rows"], m, logits)
         return logits[:m]
+
+    # ------------------------------------------------------------------ CUDA graphs for decode-only steps
+    def reserve(self) -> None:
+        """Run one step of padding rows at the largest size, so that every workspace buffer
+        has its final address, then forbid growth: captured graphs hold these addresses."""
+        if self.workspace.frozen:
+            return
+        logits = self.workspace.get("runner.logits", (self.max_rows, self.vocab), torch.float32)
+        ctx = self._padding_context(self.max_tokens, self.max_rows)
+        self.model.forward(ctx, self.cache.views(), self._d["logit_rows"], self.max_rows, logits)
+        for bucket in GRAPH_BUCKETS:
+            if bucket <= self.max_seqs:       # decode-only kernels may use buffers of their own
+                ctx = self._padding_context(bucket, bucket)
+                self.model.forward(ctx, self.cache.views(), self._d["logit_rows"], bucket, logits)
+        torch.cuda.current_stream().synchronize()
+        self.status.zero_()
+        self.workspace.frozen = True
+
+    def _capture(self, bucket: int):
+        self.reserve()
+        rows = bucket
+        logits = self.workspace.get("runner.logits", (self.max_rows, self.vocab), torch.float32)
+        ctx = self._padding_context(bucket, rows)
+        views = self.cache.views()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.model.forward(ctx, views, self._d["logit_rows"], rows, logits)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES[0]
+        with torch.cuda.graph(graph):
+            self.model.forward(ctx, views, self._d["logit_rows"], rows, logits)
+        self.graph_kernels[bucket] = ops.LAUNCHES[0] - before
+        self.status.zero_()
+        self._graphs[bucket] = (graph, logits)
+        return self._graphs[bucket]
+
+    def _graph_step(self, entries: list[StepEntry], bucket: int) -> torch.Tensor:
+        graph, logits = self._graphs.get(bucket) or self._capture(bucket)
+        wanted = [i for i, e in enumerate(entries) if e.want]
+        for e in entries:
+            e_want = e.want
+            if e_want and e_want != [0]:
+                raise ValueError("a single-token entry can only want place 0")
+        self._stage([StepEntry(e.slot, e.tokens, e.start, []) for e in entries], pad_to=bucket, all_rows=True)
+        graph.replay()
+        if wanted == list(range(len(wanted))):
+            return logits[:len(wanted)]
+        return logits.index_select(0, torch.tensor(wanted, dtype=torch.long, device=self.device))
 
     # ------------------------------------------------------------------ sampling
     def stage_sampling(self, temperature: list[float], seed: list[int], counter: list[int]) -> None:
         """Per wanted row: temperature (0 = greedy), seed and draw counter.  Must be called
         before ``step`` of the same batch, as it travels in the same copy."""
         m = len(temperature)
+        self._staged.synchronize()
         self._h["temperature"].view(torch.float32)[:m] = torch.tensor(temperature, dtype=torch.float32)
         self._h["seed"].view(torch.int64)[:m] = torch.tensor(seed, dtype=torch.int64)
         self._h["counter"].view(torch.int64)[:m] = torch.tensor(counter, dtype=torch.int64)

@@ -91,10 +91,4 @@ class Model:
 
     def head_logits(self, ctx: StepContext, logits: torch.Tensor, y: torch.Tensor, n_rows: int) -> None:
         """logits = y @ head.T in fp32 (reference: flow_engine/model.py:204)."""
-        out = logits[:n_rows]
-        if self.runtime.dtype == torch.float32:
-            matmul_nt(out, y, self.head)
-        else:
-            tmp = ctx.workspace.get("model.logits_lp", (n_rows, self.spec.vocab_size), self.runtime.dtype)
-            matmul_nt(tmp, y, self.head)
-            out.copy_(tmp)
+        matmul_nt(logits[:n_rows], y, self.head)

@@ -154,6 +154,7 @@ class StepContext:
     max_q_len: int = 1
     max_kv_len: int = 1
     decode_only: bool = False      # every sequence brings exactly one token
+    fixed_shape: bool = False      # the launch is being captured: sizes must not depend on host values of this step
 
 
 # ---------------------------------------------------------------------------

@@ -24,10 +24,14 @@ def configure_matmul_precision() -> None:
 
 
 def matmul_nt(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """out[n, o] = sum_i x[n, i] * w[o, i]; all three of one element type."""
+    """out[n, o] = sum_i x[n, i] * w[o, i].  x and w are of one element type; out is of the
+    same type, or fp32 for a bf16 product whose result must not be rounded (the logits)."""
     if not _configured:
         configure_matmul_precision()
     if not x.is_cuda:
         raise RuntimeError("matrix products run on the GPU only; this engine has no CPU path")
-    torch.mm(x, w.t(), out=out)
+    if out.dtype != x.dtype:
+        torch.mm(x, w.t(), out_dtype=out.dtype, out=out)
+    else:
+        torch.mm(x, w.t(), out=out)
     return out
