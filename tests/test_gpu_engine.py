@@ -1,0 +1,139 @@
+"""Generation through the Python entry point and the scheduler, on the GPU."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2
+from helpers import CONFIGS, PAGE_SIZE, plain_logits, random_tokens
+import tessweave_engine_b200 as tw
+
+pytestmark = pytest.mark.gpu
+
+
+def plain_generate(folder, prompt, n, temperature=0.0, seed=0):
+    config, weights = plain_qwen2.read_folder(folder)
+    return plain_qwen2.generate(config, weights, prompt, n, temperature, seed)
+
+
+def assert_plausible(folder, prompt, output, margin):
+    """Every generated token is the plain implementation's best one, or within ``margin`` of it
+    (reduced precision may flip a near-tie; the reference says the same, docs/BENCHMARKS.md:7)."""
+    logits = plain_logits(folder, prompt + output)
+    for i, tok in enumerate(output):
+        row = logits[len(prompt) + i - 1]
+        assert row.max() - row[tok] <= margin, f"token {i} ({tok}) is {row.max() - row[tok]:.3f} below the best"
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_equals_plain(name, model_folders):
+    vocab = CONFIGS[name]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 40 + n) for n in (5, 17, 33)]
+    model = tw.load_model(model_folders[name], "float32", "cuda")
+    cfg = tw.EngineConfig(min_prefill_chunk=1, block_size=PAGE_SIZE[name], kv_blocks=24, max_context=64, max_active=3, prefill_chunk=7)
+    out = tw.generate(model, prompts, max_tokens=8, ignore_eos=True, engine_config=cfg)
+    assert out == [plain_generate(model_folders[name], p, 8) for p in prompts]
+    model16 = tw.load_model(model_folders[name], "bfloat16", "cuda")
+    out16 = tw.generate(model16, prompts, max_tokens=8, ignore_eos=True, engine_config=cfg)
+    for p, o in zip(prompts, out16):
+        assert len(o) == 8
+        assert_plausible(model_folders[name], p, o, margin=0.08)
+
+
+def test_graphs_and_eager_steps_agree(model_folders):
+    vocab = CONFIGS["B"]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 70 + n) for n in (3, 12, 20, 9, 31)]
+    model = tw.load_model(model_folders["B"], "float32", "cuda")
+    outs = []
+    for graphs in (True, False):
+        cfg = tw.EngineConfig(min_prefill_chunk=1, block_size=8, kv_blocks=64, max_context=64, max_active=5, prefill_chunk=16,
+                              cuda_graphs=graphs)
+        outs.append(tw.generate(model, prompts, max_tokens=14, ignore_eos=True, engine_config=cfg))
+    assert outs[0] == outs[1] == [plain_generate(model_folders["B"], p, 14) for p in prompts]
+
+
+def test_chunked_prefill_with_shared_prefix_and_temperature(model_folders):
+    """Four prompts of 1, 9, 24 and 40 tokens, two sharing a 16-token prefix, prompt portions of 7,
+    12 tokens at temperature 0.8 with a fixed seed."""
+    vocab = CONFIGS["B"]["vocab_size"]
+    shared = random_tokens(vocab, 16, 1)
+    prompts = [random_tokens(vocab, 1, 2), random_tokens(vocab, 9, 3), shared + random_tokens(vocab, 8, 4),
+               shared + random_tokens(vocab, 24, 5)]
+    model = tw.load_model(model_folders["B"], "float32", "cuda")
+    engine = tw.Engine(model, tw.EngineConfig(min_prefill_chunk=1, block_size=8, kv_blocks=40, max_context=64, max_active=4, prefill_chunk=7))
+    first = engine.submit(prompts[2], max_tokens=12, temperature=0.8, seed=102, ignore_eos=True)
+    while first.computed < 24:
+        engine.step()                       # the owner of the prefix has computed it
+    others = [engine.submit(p, max_tokens=12, temperature=0.8, seed=100 + i, ignore_eos=True)
+              for i, p in enumerate(prompts) if i != 2]
+    engine.run_until_done()
+    assert others[2].cached == 16 and first.cached == 0
+    requests = [others[0], others[1], first, others[2]]
+    for i, r in enumerate(requests):
+        assert r.output == plain_generate(model_folders["B"], prompts[i], 12, 0.8, 100 + i), f"request {i}"
+    engine.close()
+    engine.cache.check_invariants()
+    assert engine.stats()["free_blocks"] == 40
+
+
+def test_seeded_sampling_does_not_depend_on_neighbours(model_folders):
+    vocab = CONFIGS["A"]["vocab_size"]
+    prompt = random_tokens(vocab, 11, 8)
+    model = tw.load_model(model_folders["A"], "float32", "cuda")
+    cfg = tw.EngineConfig(min_prefill_chunk=1, block_size=16, kv_blocks=32, max_context=64, max_active=4, prefill_chunk=8, prefix_cache=False)
+    alone = tw.Engine(model, cfg)
+    r = alone.submit(prompt, max_tokens=10, temperature=1.0, seed=5, ignore_eos=True)
+    alone.run_until_done()
+    crowd = tw.Engine(model, cfg)
+    crowd.submit(random_tokens(vocab, 20, 9), max_tokens=10, temperature=1.3, seed=1, ignore_eos=True)
+    r2 = crowd.submit(prompt, max_tokens=10, temperature=1.0, seed=5, ignore_eos=True)
+    crowd.submit(random_tokens(vocab, 4, 10), max_tokens=10, ignore_eos=True)
+    crowd.run_until_done()
+    assert r.output == r2.output and len(set(r.output)) > 1
+    r3 = crowd.submit(prompt, max_tokens=10, temperature=1.0, seed=6, ignore_eos=True)
+    crowd.run_until_done()
+    assert r3.output != r.output
+    alone.close(); crowd.close()
+
+
+def test_few_pages_requests_wait_and_all_finish(model_folders):
+    vocab = CONFIGS["A"]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 20 + n) for n in (30, 18, 25, 7, 40)]
+    model = tw.load_model(model_folders["A"], "float32", "cuda")
+    engine = tw.Engine(model, tw.EngineConfig(min_prefill_chunk=1, block_size=16, kv_blocks=6, max_context=64, max_active=4,
+                                              prefill_chunk=16, prefix_cache=False))
+    reqs = [engine.submit(p, max_tokens=6, ignore_eos=True) for p in prompts]
+    engine.step()
+    assert sum(r.status == "active" for r in reqs) < 5          # 6 pages cannot hold all five budgets
+    engine.run_until_done()
+    assert [r.output for r in reqs] == [plain_generate(model_folders["A"], p, 6) for p in prompts]
+    engine.close()
+    assert engine.stats()["free_blocks"] == 6
+
+
+def test_eos_stops_generation(model_folders):
+    model = tw.load_model(model_folders["A"], "float32", "cuda")
+    prompt = random_tokens(256, 9, 77)
+    free_run = plain_generate(model_folders["A"], prompt, 12)
+    model.spec = type(model.spec)(**{**model.spec.__dict__, "eos_token_ids": (free_run[3],)})
+    engine = tw.Engine(model, tw.EngineConfig(min_prefill_chunk=1, block_size=16, kv_blocks=8, max_context=64, max_active=1))
+    r = engine.submit(prompt, max_tokens=12)
+    engine.run_until_done()
+    stop_at = free_run.index(free_run[3])
+    assert r.output == free_run[:stop_at + 1] and r.status == "stop"
+    engine.close()
+
+
+def test_bad_token_is_reported_by_the_kernel(model_folders):
+    from tessweave_engine_b200.engine.runner import StepEntry, StepError
+    model = tw.load_model(model_folders["A"], "float32", "cuda")
+    cache = tw.CacheManager(model.cache_needs(), 16, 4, 2, 64, torch.float32, model.runtime.device, prefix_cache=False)
+    runner = tw.ModelRunner(model, cache, 16, 2, cuda_graphs=False)
+    lease = cache.admit(None)
+    cache.ensure(lease, 3)
+    runner.step([StepEntry(lease.slot, [1, 999, 2], 0, [2])])
+    with pytest.raises(StepError, match="vocabulary"):
+        runner.check_status()
+    other = cache.admit(None)                                   # no pages taken for it
+    runner.step([StepEntry(other.slot, [1, 2], 0, [1])])
+    with pytest.raises(StepError, match="page"):
+        runner.check_status()

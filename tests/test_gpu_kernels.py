@@ -1,0 +1,279 @@
+"""Each CUDA kernel alone against a plain fp32 torch computation of the same operation,
+at sizes other than the tiny models': odd widths, head sizes from 16 to 256, permuted
+pages, windows.  Where random inputs would hide a fault, inputs are made so that it shows."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": dict(atol=3e-5, rtol=3e-5), "bfloat16": dict(atol=2.5e-2, rtol=2.5e-2)}
+
+
+def ops():
+    from tessweave_engine_b200.csrc import ops as o
+    return o
+
+
+def dev(t, dtype=None):
+    return t.to("cuda", dtype) if dtype else t.to("cuda")
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(100, 37), (3584, 1000)])
+def test_embed(dtype, hidden, vocab):
+    torch.manual_seed(0)
+    table = dev(torch.randn(vocab, hidden), DTYPES[dtype])
+    ids = torch.tensor([0, vocab - 1, 5, 5, 17], dtype=torch.int32, device="cuda")
+    resid = torch.full((5, hidden), 7.0, device="cuda")
+    st = status()
+    ops().embed(resid, table, ids, 5, st)
+    assert torch.equal(resid, table[ids.long()].float()) and int(st) == 0
+    bad = torch.tensor([3, vocab], dtype=torch.int32, device="cuda")
+    ops().embed(resid, table, bad, 2, st)
+    assert int(st) == 1 and float(resid[1].abs().sum()) == 0          # refused, not read out of bounds
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [96, 1000, 3584, 5120])
+def test_add_rmsnorm(dtype, hidden):
+    torch.manual_seed(1)
+    dt = DTYPES[dtype]
+    n, eps = 9, 1e-5
+    resid = dev(torch.randn(n, hidden) * 3)
+    delta = dev(torch.randn(n, hidden), dt)
+    weight = dev(1 + 0.1 * torch.randn(hidden))
+    want_resid = resid + delta.float()
+    want = plain_qwen2.rms_norm(want_resid.cpu(), weight.cpu(), eps)
+    out = torch.empty(n, hidden, device="cuda", dtype=dt)
+    r = resid.clone()
+    ops().add_rmsnorm(out, r, delta, weight, eps, n)
+    assert torch.allclose(r, want_resid, atol=1e-6)
+    assert torch.allclose(out.float().cpu(), want, **TOL[dtype])
+    # no delta: the stream is only read
+    r2 = resid.clone()
+    ops().add_rmsnorm(out, r2, None, weight, eps, n)
+    assert torch.equal(r2, resid)
+    assert torch.allclose(out.float().cpu(), plain_qwen2.rms_norm(resid.cpu(), weight.cpu(), eps), **TOL[dtype])
+    # selected rows: the stream stays as it was, the delta is still counted
+    rows = torch.tensor([7, 0, 3], dtype=torch.int32, device="cuda")
+    r3 = resid.clone()
+    out3 = torch.empty(3, hidden, device="cuda", dtype=dt)
+    ops().add_rmsnorm(out3, r3, delta, weight, eps, 3, rows)
+    assert torch.equal(r3, resid)
+    assert torch.allclose(out3.float().cpu(), want[rows.long().cpu()], **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    torch.manual_seed(2)
+    dt = DTYPES[dtype]
+    n, inter = 5, 200
+    gu = dev(torch.randn(n, 2 * inter) * 4, dt)
+    out = torch.empty(n, inter, device="cuda", dtype=dt)
+    ops().silu_mul(out, gu, n)
+    g, u = gu.float().cpu()[:, :inter], gu.float().cpu()[:, inter:]
+    assert torch.allclose(out.float().cpu(), g * torch.sigmoid(g) * u, **TOL[dtype])
+
+
+def paged_setup(lengths, page, kv_heads, head_dim, dtype, seed=0, extra_pages=5):
+    """Random keys/values for requests of the given lengths, scattered over permuted pages."""
+    g = torch.Generator().manual_seed(seed)
+    blocks = [math.ceil(n / page) for n in lengths]
+    total = sum(blocks) + extra_pages
+    perm = torch.randperm(total, generator=g).tolist()
+    width = max(blocks) + 1
+    table = torch.full((len(lengths) + 2, width), -1, dtype=torch.int32)
+    slots = list(range(len(lengths), 0, -1))                       # request i uses table row slots[i]
+    k_pages = torch.full((total, kv_heads, page, head_dim), float("nan"))
+    v_pages = torch.full((total, kv_heads, page, head_dim), float("nan"))
+    ks, vs = [], []
+    cursor = 0
+    for i, n in enumerate(lengths):
+        k = torch.randn(n, kv_heads, head_dim, generator=g)
+        v = torch.randn(n, kv_heads, head_dim, generator=g)
+        ks.append(k); vs.append(v)
+        for b in range(blocks[i]):
+            pid = perm[cursor]; cursor += 1
+            table[slots[i], b] = pid
+            chunk = slice(b * page, min(n, (b + 1) * page))
+            m = chunk.stop - chunk.start
+            k_pages[pid, :, :m] = k[chunk].transpose(0, 1)
+            v_pages[pid, :, :m] = v[chunk].transpose(0, 1)
+    return dict(table=dev(table), slots=slots, k_pages=dev(k_pages, dtype), v_pages=dev(v_pages, dtype), k=ks, v=vs)
+
+
+def dense_attention(q, k, v, positions, window=None):
+    """q: [rows, Hq, D] at the given positions of one request; k, v: [n, Hkv, D]; fp32."""
+    rep = q.shape[1] // k.shape[1]
+    kk, vv = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
+    s = torch.einsum("rhd,nhd->hrn", q, kk) * q.shape[-1] ** -0.5
+    p = torch.arange(k.shape[0])
+    pos = torch.as_tensor(positions)
+    visible = p[None, :] <= pos[:, None]
+    if window:
+        visible &= p[None, :] > pos[:, None] - window
+    s = s.masked_fill(~visible[None], float("-inf"))
+    return torch.einsum("hrn,nhd->rhd", torch.softmax(s, -1), vv)
+
+
+CASES = [(8, 8, 16), (8, 2, 32), (8, 1, 64), (6, 3, 48), (28, 4, 128), (4, 2, 256), (3, 1, 80)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d", CASES)
+@pytest.mark.parametrize("window", [0, 24])
+def test_attention_generic_ragged_rows(dtype, hq, hkv, d, window):
+    """Decode rows and prompt portions of four requests in one launch (lengths 1/17/65/257
+    as tools/validate_cuda.py:25-57), pages in random order, page size 16 and 8."""
+    dt = DTYPES[dtype]
+    lengths = [1, 17, 65, 257]
+    page = 16 if d != 48 else 8
+    setup = paged_setup(lengths, page, hkv, d, dt, seed=hq * 100 + d)
+    rows_of = [[0], [16], list(range(60, 65)), [0, 1, 15, 16, 17, 255, 256]]       # request -> positions in this step
+    g = torch.Generator().manual_seed(5)
+    n = sum(len(r) for r in rows_of)
+    q = torch.randn(n, hq, d, generator=g)
+    positions, seq_of_token = [], []
+    for i, r in enumerate(rows_of):
+        positions += r; seq_of_token += [i] * len(r)
+    qd = dev(q.reshape(n, hq * d), dt)
+    out = torch.full((n, hq * d), float("nan"), device="cuda", dtype=dt)
+    st = status()
+    ops().attention_generic(out, qd, dev(torch.tensor(positions, dtype=torch.int32)),
+                            dev(torch.tensor(seq_of_token, dtype=torch.int32)),
+                            dev(torch.tensor(setup["slots"], dtype=torch.int32)), setup["table"], setup["k_pages"],
+                            setup["v_pages"], n, hq, hkv, d, window, d ** -0.5, st)
+    assert int(st) == 0
+    cursor = 0
+    for i, r in enumerate(rows_of):
+        rq = qd[cursor:cursor + len(r)].float().cpu().reshape(len(r), hq, d)
+        k = setup["k"][i].to(dt).float(); v = setup["v"][i].to(dt).float()
+        want = dense_attention(rq, k, v, r, window or None)
+        got = out[cursor:cursor + len(r)].float().cpu().reshape(len(r), hq, d)
+        assert torch.allclose(got, want, **TOL[dtype]), f"request {i}"
+        cursor += len(r)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("where", ["first_of_page", "last_of_page", "position_zero", "window_edge_inside", "window_edge_outside"])
+def test_attention_finds_one_far_key(dtype, where):
+    """One key among hundreds is made to dominate (its score stands out by a scaled query and
+    key).  The output must be that key's value: a kernel that skips a page, misreads a page's
+    first or last slot, or is off by one at a window's edge shows here, which random inputs hide."""
+    dt = DTYPES[dtype]
+    hq, hkv, d, page, n = 4, 2, 32, 16, 400
+    window = 0
+    pos = n - 1
+    target = {"first_of_page": 16 * 7, "last_of_page": 16 * 9 + 15, "position_zero": 0}.get(where)
+    if where.startswith("window_edge"):
+        window = 100
+        target = pos - window + 1 if where.endswith("inside") else pos - window
+    setup = paged_setup([n], page, hkv, d, dt, seed=3)
+    q = torch.randn(1, hq, d) * 0.1
+    direction = torch.randn(d); direction /= direction.norm()
+    q[0, :] = direction * 12.0
+    kp, vp = setup["k_pages"], setup["v_pages"]
+    pid = int(setup["table"][setup["slots"][0], target // page])
+    kp[pid, :, target % page] = (direction * 12.0).to(dt).cuda()           # score 144 / sqrt(32) ~ 25, far above the rest
+    marker = torch.arange(d, dtype=torch.float32) / d + 2.0
+    vp[pid, :, target % page] = marker.to(dt).cuda()
+    out = torch.empty(1, hq * d, device="cuda", dtype=dt)
+    st = status()
+    ops().attention_generic(out, dev(q.reshape(1, hq * d), dt), dev(torch.tensor([pos], dtype=torch.int32)),
+                            dev(torch.tensor([0], dtype=torch.int32)), dev(torch.tensor(setup["slots"], dtype=torch.int32)),
+                            setup["table"], kp, vp, 1, hq, hkv, d, window, d ** -0.5, st)
+    k = setup["k"][0].clone(); v = setup["v"][0].clone()
+    k[target] = direction * 12.0; v[target] = marker
+    want = dense_attention(q.to(dt).float(), k.to(dt).float(), v.to(dt).float(), [pos], window or None)
+    got = out.float().cpu().reshape(1, hq, d)
+    assert torch.allclose(got, want, **TOL[dtype])
+    hit = (got[0, 0] - marker).abs().max() < 0.5
+    assert bool(hit) == (where != "window_edge_outside")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 16), (3, 1, 32, 8), (6, 3, 48, 4), (28, 4, 128, 16)])
+def test_rope_kv_write(dtype, hq, hkv, d, page):
+    """Bias, rotation and the scatter into pages, against plain_qwen2.rope; tokens of two
+    requests at scattered positions, tables with pages in reverse order."""
+    dt = DTYPES[dtype]
+    torch.manual_seed(4)
+    theta = 1e6 if d >= 32 else 1e4
+    positions = [0, 1, page - 1, page, 3 * page + 2, 1500, page - 1, page]
+    seq_of_token = [0, 0, 0, 0, 0, 0, 1, 1]
+    n = len(positions)
+    width = (hq + 2 * hkv) * d
+    qkv = torch.randn(n, width)
+    bias = torch.randn(width) * 0.5
+    blocks = 1500 // page + 1
+    pages = blocks + 4
+    table = torch.full((3, blocks), -1, dtype=torch.int32)
+    table[2, :] = torch.arange(blocks - 1, -1, -1, dtype=torch.int32)           # request 0 -> row 2
+    table[0, :2] = torch.tensor([pages - 1, pages - 2], dtype=torch.int32)      # request 1 -> row 0
+    kp = torch.zeros(pages, hkv, page, d, device="cuda", dtype=dt)
+    vp = torch.zeros_like(kp)
+    inv = dev(theta ** (-torch.arange(0, d, 2, dtype=torch.float32) / d))
+    x = dev(qkv, dt)
+    st = status()
+    ops().rope_kv_write(x, dev(bias), dev(torch.tensor(positions, dtype=torch.int32)),
+                        dev(torch.tensor(seq_of_token, dtype=torch.int32)), dev(torch.tensor([2, 0], dtype=torch.int32)),
+                        dev(table), inv, kp, vp, n, hq, hkv, d, True, st)
+    assert int(st) == 0
+    src = qkv.to(dt).float() + bias
+    q_want = plain_qwen2.rope(src[:, :hq * d].reshape(n, hq, d), positions, theta)
+    k_want = plain_qwen2.rope(src[:, hq * d:(hq + hkv) * d].reshape(n, hkv, d), positions, theta)
+    v_want = src[:, (hq + hkv) * d:].reshape(n, hkv, d)
+    tol = TOL[dtype] if dtype == "bfloat16" else dict(atol=2e-5, rtol=1e-5)
+    assert torch.allclose(x[:, :hq * d].float().cpu().reshape(n, hq, d), q_want, **tol)
+    rows = {0: 2, 1: 0}
+    for i, (p, s) in enumerate(zip(positions, seq_of_token)):
+        pid = int(table[rows[s], p // page])
+        assert torch.allclose(kp[pid, :, p % page].float().cpu(), k_want[i], **tol), f"k of token {i}"
+        assert torch.allclose(vp[pid, :, p % page].float().cpu(), v_want[i], **tol), f"v of token {i}"
+    written = sum(1 for _ in positions)
+    assert int((kp.float().abs().sum(-1) > 0).sum()) == written * hkv          # nothing else was touched
+    # a position without a page is refused and reported, not written somewhere
+    st2 = status()
+    ops().rope_kv_write(x, None, dev(torch.tensor([5 * page], dtype=torch.int32)), dev(torch.tensor([1], dtype=torch.int32)),
+                        dev(torch.tensor([2, 0], dtype=torch.int32)), dev(table), inv, kp, vp, 1, hq, hkv, d, True, st2)
+    assert int(st2) == 2
+
+
+def test_sample_greedy_and_temperature():
+    torch.manual_seed(6)
+    vocab = 152064
+    logits = torch.randn(6, vocab) * 2
+    logits[1, 777] = 50; logits[1, 90000] = 50                 # a tie: the lowest index wins
+    logits[2, vocab - 1] = 60
+    logits[3, 0] = 60
+    out = torch.zeros(6, dtype=torch.int32, device="cuda")
+    ops().sample(out, dev(logits), 6)
+    assert out.tolist() == [int(logits[i].argmax()) if i != 1 else 777 for i in range(6)]
+    # temperature rows beside greedy rows; each row's draw depends on its own seed and counter only
+    temps = [0.0, 0.8, 1.0, 2.0, 0.8, 0.3]
+    seeds = [0, 11, 12, 13, 11, 99]
+    counters = [0, 0, 5, 7, 1, 2]
+    small = torch.randn(6, 1000) * 3
+    out2 = torch.zeros(6, dtype=torch.int32, device="cuda")
+    ops().sample(out2, dev(small), 6, dev(torch.tensor(temps)), dev(torch.tensor(seeds)), dev(torch.tensor(counters)))
+    want = [plain_qwen2.choose(small[i], temps[i], seeds[i], counters[i]) for i in range(6)]
+    assert out2.tolist() == want
+    alone = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops().sample(alone, dev(small[4:5]), 1, dev(torch.tensor([0.8])), dev(torch.tensor([11])), dev(torch.tensor([1])))
+    assert int(alone) == want[4]
+    # many draws follow the distribution
+    row = torch.tensor([[0.0, 1.0, 2.0, -30.0, 0.5]]).repeat(4000, 1)
+    out3 = torch.zeros(4000, dtype=torch.int32, device="cuda")
+    ops().sample(out3, dev(row), 4000, dev(torch.ones(4000)), dev(torch.full((4000,), 3)), dev(torch.arange(4000)))
+    freq = np.bincount(out3.cpu().numpy(), minlength=5) / 4000
+    assert np.abs(freq - torch.softmax(row[0], 0).numpy()).max() < 0.03

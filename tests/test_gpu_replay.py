@@ -1,0 +1,130 @@
+"""Replay of the same requests under every way of cutting the work, against the plain
+implementation: whole; most of it at once and the last 32 tokens one by one; portions of
+changing size down to two tokens; mixed, up to four live requests with so few pages that
+they are used again (freed pages are filled with NaN first).  In float32 and in bfloat16."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from helpers import (CONFIGS, PAGE_SIZE, ROOT, max_live_tokens, plain_logits, random_tokens, replay_in_process,
+                     schedule_mixed, schedule_portions, schedule_tail, schedule_whole)
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = [70, 1, 45, 100, 2, 33, 64, 129]
+
+
+def requests_for(name):
+    vocab = CONFIGS[name]["vocab_size"]
+    return {f"r{i}": random_tokens(vocab, n, 10 + i) for i, n in enumerate(LENGTHS)}
+
+
+def tolerance(dtype, reference):
+    """float32: 1e-4 absolute.  bfloat16: 3% of the largest logit magnitude (at least 0.03):
+    activations carry 8 bits, and a few roundings per layer add up."""
+    if dtype == "float32":
+        return 1e-4
+    return 0.03 * max(1.0, float(np.abs(reference).max()))
+
+
+SCHEDULES = {
+    "whole": schedule_whole,
+    "tail": schedule_tail,
+    "portions": schedule_portions,
+    "mixed": lambda r: schedule_mixed(r, live=4, seed=1),
+}
+
+
+@pytest.fixture(scope="module")
+def plain(model_folders):
+    return {name: {rid: plain_logits(model_folders[name], t) for rid, t in requests_for(name).items()}
+            for name in ("A", "B")}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_every_cutting_gives_the_plain_logits(name, dtype, model_folders, plain, tmp_path):
+    reqs = requests_for(name)
+    results = {}
+    for sname, make in SCHEDULES.items():
+        steps = make(reqs)
+        rows = replay_in_process(model_folders[name], dtype, steps, tmp_path / sname, block_size=PAGE_SIZE[name])
+        assert len(rows) == sum(LENGTHS), f"{sname}: not every position came back"
+        for (rid, pos), row in rows.items():
+            want = plain[name][rid][pos]
+            err = float(np.abs(row - want).max())
+            assert np.isfinite(row).all(), f"{sname}: non-finite logits at {rid}[{pos}] (a stale page was read?)"
+            assert err <= tolerance(dtype, want), f"{sname}: {rid}[{pos}] is off by {err:.3e}"
+        results[sname] = rows
+    # the same position under different cuttings: equal beyond rounding
+    for sname in ("tail", "portions", "mixed"):
+        for key, row in results[sname].items():
+            err = float(np.abs(row - results["whole"][key]).max())
+            bound = 2e-5 if dtype == "float32" else tolerance(dtype, row)
+            assert err <= bound, f"{sname} vs whole: {key} differs by {err:.3e}"
+
+
+def test_mixed_schedule_really_reuses_pages(model_folders):
+    reqs = requests_for("A")
+    steps = schedule_mixed(reqs, live=4, seed=1)
+    assert max_live_tokens(steps) < sum(-(-n // 64) * 64 for n in LENGTHS)        # the pool is smaller than the total
+    assert max(len(s["entries"]) for s in steps) == 4
+    assert any(len(e["tokens"]) == 1 for s in steps for e in s["entries"]) and \
+        any(len(e["tokens"]) == 2 for s in steps for e in s["entries"])
+    assert any({len(e["tokens"]) == 1 for e in s["entries"]} == {True, False} for s in steps)   # decode beside prefill
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(dtype, model_folders, plain, tmp_path):
+    """Eight prompt tokens, then 300 tokens one by one, across many page edges."""
+    vocab = CONFIGS["B"]["vocab_size"]
+    tokens = random_tokens(vocab, 308, 99)
+    steps = schedule_tail({"long": tokens}, tail=300)
+    rows = replay_in_process(model_folders["B"], dtype, steps, tmp_path, block_size=PAGE_SIZE["B"])
+    want = plain_logits(model_folders["B"], tokens)
+    worst = max(float(np.abs(rows[("long", p)] - want[p]).max()) for p in range(308))
+    assert worst <= tolerance(dtype, want), f"off by {worst:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(dtype, model_folders, tmp_path):
+    """Positions 0..3 fed one by one from an empty cache."""
+    vocab = CONFIGS["A"]["vocab_size"]
+    tokens = random_tokens(vocab, 4, 5)
+    steps = schedule_tail({"s": tokens}, tail=3)
+    assert [len(s["entries"][0]["tokens"]) for s in steps] == [1, 1, 1, 1]
+    rows = replay_in_process(model_folders["A"], dtype, steps, tmp_path)
+    want = plain_logits(model_folders["A"], tokens)
+    for p in range(4):
+        assert float(np.abs(rows[("s", p)] - want[p]).max()) <= tolerance(dtype, want)
+
+
+def test_trace_run_program(model_folders, tmp_path):
+    """bin/trace_run as a user starts it: own process, steps on standard input, one
+    ``done`` line per step, logits files, exit code 0."""
+    vocab = CONFIGS["A"]["vocab_size"]
+    a, b = random_tokens(vocab, 20, 1), random_tokens(vocab, 9, 2)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:11], "want": [0, 10]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[11:13], "want": []}, {"id": "b", "tokens": b[:8], "want": [7]}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[8:], "want": [0]}], "end": ["b"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[13:], "want": [6]}], "end": ["a"]},
+    ]
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_folders["A"]),
+                           "--dtype", "float32", "--out", str(out), "--max-tokens", "128"],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+    assert not (out / "1.f32").exists() or (out / "1.f32").stat().st_size == vocab * 4
+    wa, wb = plain_logits(model_folders["A"], a), plain_logits(model_folders["A"], b)
+    got0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(2, vocab)
+    assert np.abs(got0 - wa[[0, 10]]).max() <= 1e-4
+    assert np.abs(np.fromfile(out / "1.f32", dtype="<f4") - wb[7]).max() <= 1e-4
+    assert np.abs(np.fromfile(out / "2.f32", dtype="<f4") - wb[8]).max() <= 1e-4
+    assert np.abs(np.fromfile(out / "3.f32", dtype="<f4") - wa[19]).max() <= 1e-4
