@@ -198,3 +198,67 @@ def sample(out: torch.Tensor, logits: torch.Tensor, n_rows: int, temperature: to
     code = _fn("sampling", "tw_sample")(_ptr(out), _ptr(logits), c_int(n_rows), c_int(logits.shape[1]),
                                         _ptr(temperature), _ptr(seed), _ptr(counter), _stream())
     _check(code, "sample")
+
+
+# ---------------------------------------------------------------------------
+# bf16 tensor-core attention (one compiled library per head size)
+# ---------------------------------------------------------------------------
+DECODE_SCRATCH_UNITS = 1024      # most (request, split) pairs whose partial results fit the scratch buffer
+_SM_COUNT = 148
+
+
+def tensor_core_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+def decode_splits(n_seqs: int, n_kv_heads: int, group: int, max_kv_len: int) -> int:
+    """How many slices the keys of a request are cut into, so that the launch fills the GPU."""
+    head_tiles = (group + 15) // 16
+    tiles = max(1, -(-max_kv_len // 64))
+    target = -(-4 * _SM_COUNT // max(1, n_seqs * n_kv_heads * head_tiles))
+    return max(1, min(tiles, target, DECODE_SCRATCH_UNITS // max(1, n_seqs)))
+
+
+def decode_scratch_floats(n_q_heads: int, head_dim: int) -> int:
+    return DECODE_SCRATCH_UNITS * n_q_heads * (head_dim + 2)
+
+
+def _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim):
+    _need(tensor_core_attention_supported(q.dtype, head_dim),
+          f"tensor-core attention takes bfloat16 and head sizes that are multiples of 16 up to 256, not {q.dtype}/{head_dim}")
+    _need(n_q_heads % n_kv_heads == 0, "attention: query heads must be a multiple of key/value heads")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == q.dtype == k_pages.dtype == v_pages.dtype,
+          "attention: operands must be bfloat16 with unit inner stride")
+    _need(q.stride(0) % 2 == 0 and q.storage_offset() % 2 == 0 and out.stride(0) % 2 == 0, "attention: rows must be 4-byte aligned")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape[3] == head_dim
+          and k_pages.shape[1] == n_kv_heads, "attention: cache pages must be contiguous [pages, kv_heads, page, head_dim]")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: bad block table")
+
+
+def attention_decode(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, n_seqs,
+                     n_q_heads, n_kv_heads, head_dim, window, scale, nsplit, scratch, status) -> None:
+    """Split-KV attention for the requests of the batch that bring one token (others are skipped)."""
+    _cuda(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, scratch, status)
+    _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim)
+    if nsplit > 1:
+        _need(scratch is not None and scratch.dtype == torch.float32
+              and scratch.numel() >= n_seqs * n_q_heads * nsplit * (head_dim + 2), "attention_decode: scratch too small")
+    code = _fn("attention_bf16", "tw_attn_decode", {"TW_HEAD_DIM": head_dim})(
+        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(seq_q_start), _ptr(seq_q_len),
+        _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages),
+        c_int(n_seqs), c_int(n_q_heads), c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]),
+        c_int(window), c_float(scale), c_int(nsplit), _ptr(scratch), _ptr(status), _stream())
+    _check(code, "attention_decode")
+
+
+def attention_prefill(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, n_seqs,
+                      max_q_len, n_q_heads, n_kv_heads, head_dim, window, scale, skip_single, status) -> None:
+    """Flash attention over the paged cache for the requests that bring several tokens."""
+    _cuda(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, status)
+    _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim)
+    code = _fn("attention_bf16", "tw_attn_prefill", {"TW_HEAD_DIM": head_dim})(
+        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(seq_q_start), _ptr(seq_q_len),
+        _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages),
+        c_int(n_seqs), c_int(max_q_len), c_int(n_q_heads), c_int(n_kv_heads), c_int(k_pages.shape[2]),
+        c_int(k_pages.shape[0]), c_int(window), c_float(scale), c_int(1 if skip_single else 0), _ptr(status), _stream())
+    _check(code, "attention_prefill")

@@ -8,7 +8,9 @@ from __future__ import annotations
 
 COMMON_HEAD_DIMS = (16, 32, 64, 128)
 
-_SPECIALISED: dict[str, list[dict]] = {}
+_SPECIALISED: dict[str, list[dict]] = {
+    "attention_bf16": [{"TW_HEAD_DIM": d} for d in COMMON_HEAD_DIMS],
+}
 
 
 def specialise(name: str, variants: list[dict]) -> None:

@@ -83,8 +83,28 @@ class GQAAttention(Mixer):
         matmul_nt(delta, out, self.w_o)
         return delta
 
+    def _attend_tensor_cores(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, cache: PagedView) -> None:
+        """bfloat16: flash attention for requests with several tokens, split-KV attention for
+        requests with one; both read the same flat batch and skip the other's requests."""
+        window = self.window or 0
+        singles = ctx.decode_only or ctx.fixed_shape or any(n == 1 for n in ctx.host_q_len)
+        if not ctx.decode_only:
+            ops.attention_prefill(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
+                                  cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, ctx.max_q_len,
+                                  self.n_heads, self.n_kv_heads, self.head_dim, window, self.scale, singles, ctx.status)
+        if singles:
+            nsplit = ops.decode_splits(ctx.n_seqs, self.n_kv_heads, self.n_heads // self.n_kv_heads, ctx.max_kv_len)
+            scratch = ctx.workspace.get("attn.decode_scratch", (ops.decode_scratch_floats(self.n_heads, self.head_dim),),
+                                        torch.float32)
+            ops.attention_decode(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
+                                 cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, self.n_heads,
+                                 self.n_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, ctx.status)
+
     def _attend(self, ctx: StepContext, out: torch.Tensor, qkv: torch.Tensor, cache: PagedView) -> None:
         q = qkv[:, : self.q_size]
+        if ops.tensor_core_attention_supported(self.runtime.dtype, self.head_dim):
+            self._attend_tensor_cores(ctx, out, q, cache)
+            return
         ops.attention_generic(out, q, ctx.positions, ctx.seq_of_token, ctx.seq_slot, cache.block_table,
                               cache.k_pages, cache.v_pages, ctx.n_tokens, self.n_heads, self.n_kv_heads,
                               self.head_dim, self.window or 0, self.scale, ctx.status)

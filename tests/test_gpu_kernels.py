@@ -277,3 +277,103 @@ def test_sample_greedy_and_temperature():
     ops().sample(out3, dev(row), 4000, dev(torch.ones(4000)), dev(torch.full((4000,), 3)), dev(torch.arange(4000)))
     freq = np.bincount(out3.cpu().numpy(), minlength=5) / 4000
     assert np.abs(freq - torch.softmax(row[0], 0).numpy()).max() < 0.03
+
+
+# ---------------------------------------------------------------------------
+# bf16 tensor-core attention: the same cases through the decode and the prefill kernel
+# ---------------------------------------------------------------------------
+TC_CASES = [(8, 8, 16), (8, 2, 32), (8, 1, 64), (6, 3, 48), (28, 4, 128), (4, 2, 256), (3, 1, 80), (40, 2, 64)]
+
+
+def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None):
+    """rows_of: request -> the consecutive positions it brings; the request holds exactly
+    positions 0..last.  Requests with one row go through the decode kernel."""
+    o = ops()
+    n = sum(len(r) for r in rows_of)
+    qd = dev(q.reshape(n, hq * d), torch.bfloat16)
+    out = torch.full((n, hq * d), float("nan"), device="cuda", dtype=torch.bfloat16)
+    starts, cursor = [], 0
+    for r in rows_of:
+        starts.append(cursor); cursor += len(r)
+    i32 = lambda v: dev(torch.tensor(v, dtype=torch.int32))
+    q_start, q_len, kv_len, slot = i32(starts), i32([len(r) for r in rows_of]), i32([r[-1] + 1 for r in rows_of]), i32(setup["slots"])
+    st = status()
+    singles = any(len(r) == 1 for r in rows_of)
+    if any(len(r) > 1 for r in rows_of):
+        o.attention_prefill(out, qd, q_start, q_len, kv_len, slot, setup["table"], setup["k_pages"], setup["v_pages"],
+                            len(rows_of), max(len(r) for r in rows_of), hq, hkv, d, window, d ** -0.5, singles, st)
+    if singles:
+        max_kv = max(r[-1] + 1 for r in rows_of)
+        ns = nsplit or o.decode_splits(len(rows_of), hkv, hq // hkv, max_kv)
+        scratch = torch.full((o.decode_scratch_floats(hq, d),), float("nan"), device="cuda")
+        o.attention_decode(out, qd, q_start, q_len, kv_len, slot, setup["table"], setup["k_pages"], setup["v_pages"],
+                           len(rows_of), hq, hkv, d, window, d ** -0.5, ns, scratch, st)
+    assert int(st) == 0
+    return out.float().cpu().reshape(n, hq, d), qd.float().cpu().reshape(n, hq, d)
+
+
+@pytest.mark.parametrize("hq,hkv,d", TC_CASES)
+@pytest.mark.parametrize("window", [0, 24])
+def test_tensor_core_attention_mixed_rows(hq, hkv, d, window):
+    """Two decode rows (lengths 1 and 257+) beside two prompt portions, one of which starts in the
+    middle of its request (keys already cached), pages in random order."""
+    lengths = [1, 300, 65, 257]
+    page = 16 if d != 48 else 8
+    setup = paged_setup(lengths, page, hkv, d, torch.bfloat16, seed=hq * 100 + d)
+    rows_of = [[0], [299], list(range(0, 65)), list(range(200, 257))]
+    g = torch.Generator().manual_seed(5)
+    n = sum(len(r) for r in rows_of)
+    q = torch.randn(n, hq, d, generator=g)
+    got, qr = run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window)
+    cursor = 0
+    for i, r in enumerate(rows_of):
+        k = setup["k"][i].to(torch.bfloat16).float(); v = setup["v"][i].to(torch.bfloat16).float()
+        want = dense_attention(qr[cursor:cursor + len(r)], k, v, r, window or None)
+        assert torch.allclose(got[cursor:cursor + len(r)], want, **TOL["bfloat16"]), f"request {i}"
+        cursor += len(r)
+
+
+@pytest.mark.parametrize("nsplit", [1, 2, 7, 64])
+def test_decode_attention_any_split(nsplit):
+    """The split count must not matter, also when most slices are empty."""
+    hq, hkv, d = 14, 2, 64
+    lengths = [5, 64, 65, 1000]
+    setup = paged_setup(lengths, 16, hkv, d, torch.bfloat16, seed=9)
+    rows_of = [[n - 1] for n in lengths]
+    q = torch.randn(4, hq, d, generator=torch.Generator().manual_seed(1))
+    got, qr = run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, 0, nsplit=nsplit)
+    for i, r in enumerate(rows_of):
+        k = setup["k"][i].to(torch.bfloat16).float(); v = setup["v"][i].to(torch.bfloat16).float()
+        assert torch.allclose(got[i:i + 1], dense_attention(qr[i:i + 1], k, v, r), **TOL["bfloat16"]), f"request {i}"
+
+
+@pytest.mark.parametrize("kind", ["decode", "prefill"])
+@pytest.mark.parametrize("where", ["first_of_page", "last_of_page", "position_zero", "tile_edge", "window_edge_inside",
+                                   "window_edge_outside"])
+def test_tensor_core_attention_finds_one_far_key(kind, where):
+    """As above for the fp32 kernel: one dominating key at a page's first or last slot, at a
+    64-key tile's edge, at position 0 and at both sides of a window's edge."""
+    hq, hkv, d, page, n = 4, 2, 32, 16, 400
+    window = 0
+    rows = [n - 1] if kind == "decode" else list(range(n - 5, n))
+    pos = rows[0]
+    target = {"first_of_page": 16 * 7, "last_of_page": 16 * 9 + 15, "position_zero": 0, "tile_edge": 63}.get(where)
+    if where.startswith("window_edge"):
+        window = 100
+        target = pos - window + 1 if where.endswith("inside") else pos - window
+    setup = paged_setup([n], page, hkv, d, torch.bfloat16, seed=3)
+    direction = torch.randn(d, generator=torch.Generator().manual_seed(2)); direction /= direction.norm()
+    q = torch.randn(len(rows), hq, d) * 0.1
+    q[0, :] = direction * 12.0
+    kp, vp = setup["k_pages"], setup["v_pages"]
+    pid = int(setup["table"][setup["slots"][0], target // page])
+    kp[pid, :, target % page] = (direction * 12.0).to(torch.bfloat16).cuda()
+    marker = torch.arange(d, dtype=torch.float32) / d + 2.0
+    vp[pid, :, target % page] = marker.to(torch.bfloat16).cuda()
+    got, qr = run_tensor_core_attention(setup, [rows], q, hq, hkv, d, window)
+    k = setup["k"][0].clone(); v = setup["v"][0].clone()
+    k[target] = direction * 12.0; v[target] = marker
+    want = dense_attention(qr, k.to(torch.bfloat16).float(), v.to(torch.bfloat16).float(), rows, window or None)
+    assert torch.allclose(got, want, **TOL["bfloat16"])
+    hit = (got[0, 0] - marker).abs().max() < 0.5
+    assert bool(hit) == (where != "window_edge_outside")
