@@ -112,7 +112,7 @@ def build_model(layers: int):
     return model, cfg
 
 
-def decode_run(model, cfg, batch: int, context: int, steps: int, warmup: int):
+def decode_run(model, cfg, batch: int, context: int, steps: int, warmup: int, graphs: bool = True):
     """Device-timed decode: ``batch`` requests that already hold ``context - steps - warmup``
     tokens each (cache filled with random keys and values) decode one token per step."""
     import torch
@@ -126,7 +126,7 @@ def decode_run(model, cfg, batch: int, context: int, steps: int, warmup: int):
     for g in cache.groups:
         g.k.normal_(0, 0.5)
         g.v.normal_(0, 0.5)
-    runner = ModelRunner(model, cache, max_step_tokens=batch, max_step_seqs=batch, cuda_graphs=True)
+    runner = ModelRunner(model, cache, max_step_tokens=batch, max_step_seqs=batch, cuda_graphs=graphs)
     leases = [cache.admit(None) for _ in range(batch)]
     for lease in leases:
         cache.ensure(lease, start + total)
@@ -263,6 +263,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--skip-extras", action="store_true", help="only the headline decode measurement")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one small measurement and print its figures (for profiling a kernel on a small case)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU engine")
@@ -277,6 +280,13 @@ def main() -> int:
         return 1
     pk, pk_source = peaks()
     model, cfg = build_model(args.layers)
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "layers": args.layers, **prefill_run(model, cfg, PREFILL_TOKENS, args.steps, args.warmup)}))
+        return 0
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "layers": args.layers,
+                          **decode_run(model, cfg, args.batch, args.context, args.steps, args.warmup, not args.no_graphs)}))
+        return 0
     sampler = ClockSampler()
     sampler.start()
     mark0 = sampler.mark()

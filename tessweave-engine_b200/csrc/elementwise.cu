@@ -47,8 +47,12 @@ TW_EXPORT int tw_embed(void* resid, const void* table, const int* ids, int n_tok
 // the normalised value to the activation type before the multiply by the
 // weight; here the product is formed in fp32 and rounded once.
 // ---------------------------------------------------------------------------
+// The delta is either a dense tensor of the activation type or `nsplit` fp32 slices of a
+// split matrix product ([slice][row][hidden], slices `split_stride` floats apart), which
+// are added here in slice order.
 template <typename T>
 __global__ void add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,
+                                   const float* __restrict__ partial, int nsplit, size_t split_stride,
                                    const float* __restrict__ weight, float eps, int hidden,
                                    const int* __restrict__ rows) {
     __shared__ float scratch[33];
@@ -56,11 +60,19 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resi
     const int src = rows ? rows[r] : r;
     float* x = resid + (size_t)src * hidden;
     const T* d = delta ? delta + (size_t)src * hidden : nullptr;
+    const float* ps = partial ? partial + (size_t)src * hidden : nullptr;
+    const bool has_delta = d || ps;
+    auto delta_at = [&](int i) -> float {
+        if (d) return tw_to_float(d[i]);
+        float s = 0.f;
+        for (int k = 0; k < nsplit; ++k) s += ps[(size_t)k * split_stride + i];
+        return s;
+    };
     float ss = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = x[i];
-        if (d) v += tw_to_float(d[i]);
-        if (!rows && d) x[i] = v;
+        if (has_delta) v += delta_at(i);
+        if (!rows && has_delta) x[i] = v;
         ss += v * v;
     }
     ss = tw_block_sum(ss, scratch);
@@ -68,21 +80,25 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resi
     T* o = out + (size_t)r * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = x[i];
-        if (rows && d) v += tw_to_float(d[i]);
+        if (rows && has_delta) v += delta_at(i);
         o[i] = tw_from_float<T>((v * inv) * weight[i]);
     }
 }
 
-TW_EXPORT int tw_add_rmsnorm(void* out, float* resid, const void* delta, const float* weight, float eps,
-                             int n_rows, int hidden, const int* rows, int dtype, cudaStream_t stream) {
+TW_EXPORT int tw_add_rmsnorm(void* out, float* resid, const void* delta, const float* partial, int nsplit,
+                             long split_stride, const float* weight, float eps, int n_rows, int hidden,
+                             const int* rows, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (delta && partial) return (int)cudaErrorInvalidValue;
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     if (dtype == TW_F32)
-        add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((float*)out, resid, (const float*)delta, weight, eps,
-                                                                  hidden, rows);
+        add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((float*)out, resid, (const float*)delta, partial,
+                                                                  nsplit, (size_t)split_stride, weight, eps, hidden,
+                                                                  rows);
     else
         add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
-            (__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, weight, eps, hidden, rows);
+            (__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, partial, nsplit, (size_t)split_stride, weight,
+            eps, hidden, rows);
     return TW_LAUNCH_CHECK();
 }
 
@@ -99,8 +115,11 @@ TW_EXPORT int tw_add_rmsnorm(void* out, float* resid, const void* delta, const f
 //   page = table[slot_row][pos / P];  element ((page * Hkv + h) * P + pos % P) * D + d
 // Reference: flow_engine/model.py:26-33,184-187; flow_engine/cache.py:93-100.
 // ---------------------------------------------------------------------------
+// The source of a row is the qkv buffer itself or, when the projection was split over k,
+// the sum of `nsplit` fp32 slices [slice][token][width]; q always lands in the qkv buffer.
 template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const float* __restrict__ bias,
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const float* __restrict__ partial,
+                                     int nsplit, size_t split_stride, const float* __restrict__ bias,
                                      const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                      const int* __restrict__ seq_slot, const int* __restrict__ block_table,
                                      int table_stride, const float* __restrict__ inv_freq, T* __restrict__ k_cache,
@@ -112,6 +131,14 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const 
     const int pos = positions[n];
     const int half = D >> 1;
     T* row = qkv + (size_t)n * qkv_stride;
+    const int width = (Hq + 2 * Hkv) * D;
+    const float* prow = partial ? partial + (size_t)n * width : nullptr;
+    auto src_at = [&](int col) -> float {
+        if (!prow) return tw_to_float(row[col]);
+        float s = 0.f;
+        for (int k = 0; k < nsplit; ++k) s += prow[(size_t)k * split_stride + col];
+        return s;
+    };
 
     int page = -1;
     if (write_cache) {
@@ -128,7 +155,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const 
     for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
         const int head = idx / half, i = idx - head * half;
         const int col = head * D + i;
-        float x1 = tw_to_float(row[col]), x2 = tw_to_float(row[col + half]);
+        float x1 = src_at(col), x2 = src_at(col + half);
         if (bias) { x1 += bias[col]; x2 += bias[col + half]; }
         float y1 = x1, y2 = x2;
         if (inv_freq) {
@@ -152,14 +179,15 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const 
         const int voff = (Hq + Hkv) * D;
         for (int idx = threadIdx.x; idx < Hkv * D; idx += blockDim.x) {
             const int kvh = idx / D, d = idx - kvh * D;
-            float v = tw_to_float(row[voff + idx]);
+            float v = src_at(voff + idx);
             if (bias) v += bias[voff + idx];
             v_cache[(((size_t)page * Hkv + kvh) * page_size + in_page) * D + d] = tw_from_float<T>(v);
         }
     }
 }
 
-TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* bias, const int* positions,
+TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, int nsplit, long split_stride,
+                               const float* bias, const int* positions,
                                const int* seq_of_token, const int* seq_slot, const int* block_table, int table_stride,
                                const float* inv_freq, void* k_cache, void* v_cache, int n_tokens, int Hq, int Hkv,
                                int D, int page_size, int num_pages, int write_cache, int dtype, int* status,
@@ -170,12 +198,13 @@ TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* bias, con
     const int threads = work >= 1024 ? 256 : 128;
     if (dtype == TW_F32)
         rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>(
-            (float*)qkv, qkv_stride, bias, positions, seq_of_token, seq_slot, block_table, table_stride, inv_freq,
+            (float*)qkv, qkv_stride, partial, nsplit, (size_t)split_stride, bias, positions, seq_of_token, seq_slot,
+            block_table, table_stride, inv_freq,
             (float*)k_cache, (float*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache, status);
     else
         rope_kv_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-            (__nv_bfloat16*)qkv, qkv_stride, bias, positions, seq_of_token, seq_slot, block_table, table_stride,
-            inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache,
+            (__nv_bfloat16*)qkv, qkv_stride, partial, nsplit, (size_t)split_stride, bias, positions, seq_of_token,
+            seq_slot, block_table, table_stride, inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache,
             status);
     return TW_LAUNCH_CHECK();
 }

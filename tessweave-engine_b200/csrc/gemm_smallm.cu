@@ -1,0 +1,157 @@
+// Matrix products with few rows (decode steps): out[m, n] = sum_k x[m, k] * w[n, k] for
+// m <= 64, bf16 operands, fp32 accumulation.  The product is bound by reading w once, so
+// the kernel streams w straight from global memory into tensor-core fragments.
+//
+// The weights are the 16-row operand of mma.m16n8k16, the (up to 8) tokens of an n-tile the
+// other one ("swap-AB").  A thread reads 16 contiguous bytes (8 values of k) of its two
+// weight rows and of its token row per 32 values of k; since a dot product does not care
+// about the order of k, those 8 values feed two MMAs without any shuffle or shared memory:
+// k-slot (2c + j) of MMA 1 is element j, slot (2c + 8 + j) is element 2 + j, and MMA 2 takes
+// elements 4..7, for the weights and for the tokens alike.
+//
+// When a matrix has too few rows to fill the GPU, k is split over blockIdx.y and each slice
+// writes fp32 partial sums to scratch memory [slice][token][n]; the kernels that consume the
+// result (residual add + norm, bias + rotary + cache write) add the slices in a fixed order.
+//
+// The reference runs these products through a library (nn.Linear: flow_engine/model.py:54,
+// 76-80,201,204).
+#include "common.cuh"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// streaming 16-byte load: the weights are read once, keep them out of L1
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+constexpr int WARPS = 8;
+constexpr int ROWS_PER_BLOCK = WARPS * 16;
+constexpr int UNROLL = 4;
+
+enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_PARTIAL = 2 };
+
+template <int NT>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M, int N, int K, int kper,
+                   void* __restrict__ out, int out_mode, int out_stride) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, c = lane & 3;
+    const int r0 = blockIdx.x * ROWS_PER_BLOCK + warp * 16;
+    if (r0 >= N) return;
+    const int kbeg = blockIdx.y * kper;
+    const int kend = min(K, kbeg + kper);
+    const int ra = r0 + g, rb = r0 + g + 8;
+    const bool va = ra < N, vb = rb < N;
+    const bf16* wa = w + (size_t)(va ? ra : 0) * K;
+    const bf16* wb = w + (size_t)(vb ? rb : 0) * K;
+    const bf16* xr[NT];
+    bool vx[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        vx[t] = t * 8 + g < M;
+        xr[t] = x + (size_t)(vx[t] ? t * 8 + g : 0) * K;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f; }
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+    for (int k = kbeg; k < kend; k += 32 * UNROLL) {
+        uint4 a0[UNROLL], a1[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int kk = k + u * 32 + 8 * c;
+            const bool ok = kk < kend;
+            a0[u] = (ok && va) ? ld_stream(wa + kk) : zero;
+            a1[u] = (ok && vb) ? ld_stream(wb + kk) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int kk = k + u * 32 + 8 * c;
+            const bool ok = kk < kend;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const uint4 b = (ok && vx[t]) ? *reinterpret_cast<const uint4*>(xr[t] + kk) : zero;
+                mma_bf16(acc[t], a0[u].x, a1[u].x, a0[u].y, a1[u].y, b.x, b.y);
+                mma_bf16(acc[t], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b.z, b.w);
+            }
+        }
+    }
+    // acc[t][0..1]: weight row ra, tokens t*8 + 2c, +1;  acc[t][2..3]: weight row rb
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int tok = t * 8 + 2 * c + e;
+            if (tok >= M) continue;
+            if (out_mode == OUT_BF16) {
+                bf16* o = reinterpret_cast<bf16*>(out) + (size_t)tok * out_stride;
+                if (va) o[ra] = __float2bfloat16_rn(acc[t][e]);
+                if (vb) o[rb] = __float2bfloat16_rn(acc[t][2 + e]);
+            } else {
+                float* o = reinterpret_cast<float*>(out) +
+                           (out_mode == OUT_PARTIAL ? ((size_t)blockIdx.y * M + tok) * out_stride : (size_t)tok * out_stride);
+                if (va) o[ra] = acc[t][e];
+                if (vb) o[rb] = acc[t][2 + e];
+            }
+        }
+    }
+}
+
+// Sum of the slices into a dense result (for consumers that cannot add slices themselves).
+template <typename T>
+__global__ void reduce_partial_kernel(T* __restrict__ out, const float* __restrict__ partial, int nsplit, long total) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    float s = 0.f;
+    for (int i = 0; i < nsplit; ++i) s += partial[(size_t)i * total + idx];
+    out[idx] = tw_from_float<T>(s);
+}
+
+}  // namespace
+
+// out_mode 0: bf16 [M, out_stride]; 1: fp32 [M, out_stride]; 2: fp32 partial sums [ksplit, M, out_stride]
+// (then kper < K).  K must be a multiple of 8; kper a multiple of 32.
+TW_EXPORT int tw_gemm_smallm(const void* w, const void* x, int M, int N, int K, int kper, void* out, int out_mode,
+                             int out_stride, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64 || K <= 0 || (K & 7) || kper <= 0 || (kper & 31) || out_mode < 0 || out_mode > 2)
+        return (int)cudaErrorInvalidValue;
+    const int ksplit = (K + kper - 1) / kper;
+    if (ksplit > 1 && out_mode != OUT_PARTIAL) return (int)cudaErrorInvalidValue;
+    dim3 grid((N + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK, ksplit);
+    const bf16* wp = (const bf16*)w;
+    const bf16* xp = (const bf16*)x;
+    if (M <= 8)
+        gemm_smallm_kernel<1><<<grid, WARPS * 32, 0, stream>>>(wp, xp, M, N, K, kper, out, out_mode, out_stride);
+    else if (M <= 16)
+        gemm_smallm_kernel<2><<<grid, WARPS * 32, 0, stream>>>(wp, xp, M, N, K, kper, out, out_mode, out_stride);
+    else if (M <= 32)
+        gemm_smallm_kernel<4><<<grid, WARPS * 32, 0, stream>>>(wp, xp, M, N, K, kper, out, out_mode, out_stride);
+    else
+        gemm_smallm_kernel<8><<<grid, WARPS * 32, 0, stream>>>(wp, xp, M, N, K, kper, out, out_mode, out_stride);
+    return TW_LAUNCH_CHECK();
+}
+
+TW_EXPORT int tw_reduce_partial(void* out, const float* partial, int nsplit, long total, int dtype, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int blocks = (int)((total + 255) / 256);
+    if (dtype == TW_F32)
+        reduce_partial_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, partial, nsplit, total);
+    else
+        reduce_partial_kernel<bf16><<<blocks, 256, 0, stream>>>((bf16*)out, partial, nsplit, total);
+    return TW_LAUNCH_CHECK();
+}

@@ -9,7 +9,8 @@ they order with library matrix products and can be captured in CUDA graphs.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_void_p, c_int, c_float
+from ctypes import c_void_p, c_int, c_float, c_long
+from dataclasses import dataclass
 
 import torch
 
@@ -20,6 +21,22 @@ F32, BF16 = 0, 1
 
 class KernelError(RuntimeError):
     pass
+
+
+@dataclass
+class SplitSum:
+    """The result of a matrix product that was split over k: fp32 slices [slices, rows, width]
+    whose sum (in slice order) is the product.  Kernels that consume it add the slices
+    themselves; ``dense()`` adds them for anyone else."""
+    slices: torch.Tensor
+
+    def dense(self, dtype: torch.dtype, out: torch.Tensor | None = None) -> torch.Tensor:
+        n, rows, width = self.slices.shape
+        out = out if out is not None else torch.empty(rows, width, dtype=dtype, device=self.slices.device)
+        code = _fn("gemm_smallm", "tw_reduce_partial")(_ptr(out), _ptr(self.slices), c_int(n), c_long(rows * width),
+                                                       c_int(dtype_code(dtype)), _stream())
+        _check(code, "reduce_partial")
+        return out
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -84,14 +101,22 @@ def embed(resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, n_tokens:
     _check(code, "embed")
 
 
-def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
+def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Tensor,
                 eps: float, n_rows: int, rows: torch.Tensor | None = None) -> None:
     """resid += delta (in place, fp32) and out = rmsnorm(resid) * weight.
 
-    With ``rows`` (int32 indices) only those rows are normalised, into out[0..n_rows),
-    and the residual stream is left as it was.
+    ``delta`` is None, a tensor of the output's type, or a ``SplitSum`` (fp32 slices of a
+    matrix product split over k, added here in slice order).  With ``rows`` (int32 indices)
+    only those rows are normalised, into out[0..n_rows), and the residual stream is left
+    as it was.
     """
-    _cuda(out, resid, delta, weight, rows)
+    partial, nsplit, split_stride = None, 0, 0
+    if isinstance(delta, SplitSum):
+        partial, nsplit, split_stride = delta.slices, delta.slices.shape[0], delta.slices.stride(0)
+        _need(partial.dtype == torch.float32 and partial.shape[2] == resid.shape[1] and partial[0].is_contiguous(),
+              "rmsnorm: split sum must be fp32 [slices, rows, hidden]")
+        delta = None
+    _cuda(out, resid, delta, weight, rows, partial)
     hidden = resid.shape[1]
     _need(resid.dtype == torch.float32 and resid.is_contiguous(), "rmsnorm: residual stream must be contiguous fp32")
     _need(weight.dtype == torch.float32 and weight.numel() == hidden, "rmsnorm: weight must be fp32 [hidden]")
@@ -103,7 +128,8 @@ def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta: torch.Tensor | No
         _need(rows.dtype == torch.int32 and rows.numel() >= n_rows, "rmsnorm: rows must be int32")
     else:
         _need(resid.shape[0] >= n_rows, "rmsnorm: fewer residual rows than asked")
-    code = _fn("elementwise", "tw_add_rmsnorm")(_ptr(out), _ptr(resid), _ptr(delta), _ptr(weight), c_float(eps),
+    code = _fn("elementwise", "tw_add_rmsnorm")(_ptr(out), _ptr(resid), _ptr(delta), _ptr(partial), c_int(nsplit),
+                                                c_long(split_stride), _ptr(weight), c_float(eps),
                                                 c_int(n_rows), c_int(hidden), _ptr(rows),
                                                 c_int(dtype_code(out.dtype)), _stream())
     _check(code, "add_rmsnorm")
@@ -112,13 +138,20 @@ def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta: torch.Tensor | No
 def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor, seq_of_token: torch.Tensor,
                   seq_slot: torch.Tensor, block_table: torch.Tensor, inv_freq: torch.Tensor | None,
                   k_pages: torch.Tensor, v_pages: torch.Tensor, n_tokens: int, n_q_heads: int, n_kv_heads: int,
-                  head_dim: int, write_cache: bool, status: torch.Tensor) -> None:
+                  head_dim: int, write_cache: bool, status: torch.Tensor, source: "SplitSum | None" = None) -> None:
     """Add the bias, rotate q and k by position, store k and v in their cache pages.
 
-    qkv: [>=n_tokens, (Hq + 2 Hkv) * D]; k_pages/v_pages: [pages, Hkv, page, D].
+    qkv: [>=n_tokens, (Hq + 2 Hkv) * D]; k_pages/v_pages: [pages, Hkv, page, D].  With
+    ``source`` the projection is read from the fp32 slices of a split product instead of
+    ``qkv``; the rotated q is written to ``qkv`` either way.
     """
     _cuda(qkv, bias, positions, seq_of_token, seq_slot, block_table, inv_freq, k_pages, v_pages, status)
     width = (n_q_heads + 2 * n_kv_heads) * head_dim
+    partial, nsplit, split_stride = None, 0, 0
+    if source is not None:
+        partial, nsplit, split_stride = source.slices, source.slices.shape[0], source.slices.stride(0)
+        _need(partial.is_cuda and partial.dtype == torch.float32 and partial.shape[2] == width
+              and partial[0].is_contiguous() and partial.shape[1] >= n_tokens, "rope: bad split source")
     _need(qkv.stride(1) == 1 and qkv.shape[1] == width, "rope: qkv row must be [q | k | v] heads")
     _need(head_dim % 2 == 0, f"rope: head_dim {head_dim} must be even")
     _need(k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype and k_pages.is_contiguous()
@@ -132,7 +165,8 @@ def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch
     if inv_freq is not None:
         _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2, "rope: inv_freq must be fp32 [D/2]")
     code = _fn("elementwise", "tw_rope_kv_write")(
-        _ptr(qkv), c_int(qkv.stride(0)), _ptr(bias), _ptr(positions), _ptr(seq_of_token), _ptr(seq_slot),
+        _ptr(qkv), c_int(qkv.stride(0)), _ptr(partial), c_int(nsplit), c_long(split_stride), _ptr(bias),
+        _ptr(positions), _ptr(seq_of_token), _ptr(seq_slot),
         _ptr(block_table), c_int(block_table.shape[1]), _ptr(inv_freq), _ptr(k_pages), _ptr(v_pages),
         c_int(n_tokens), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(k_pages.shape[2]),
         c_int(k_pages.shape[0]), c_int(1 if write_cache else 0), c_int(dtype_code(qkv.dtype)), _ptr(status), _stream())
@@ -150,7 +184,8 @@ def rotate_heads(rows: torch.Tensor, bias: torch.Tensor | None, positions: torch
     if inv_freq is not None:
         _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2, "rotate_heads: inv_freq fp32 [D/2]")
     code = _fn("elementwise", "tw_rope_kv_write")(
-        _ptr(rows), c_int(rows.stride(0)), _ptr(bias), _ptr(positions), _ptr(seq_of_token), _ptr(None), _ptr(None),
+        _ptr(rows), c_int(rows.stride(0)), _ptr(None), c_int(0), c_long(0), _ptr(bias), _ptr(positions),
+        _ptr(seq_of_token), _ptr(None), _ptr(None),
         c_int(0), _ptr(inv_freq), _ptr(None), _ptr(None), c_int(n_tokens), c_int(n_heads), c_int(0), c_int(head_dim),
         c_int(1), c_int(0), c_int(0), c_int(dtype_code(rows.dtype)), _ptr(None), _stream())
     _check(code, "rotate_heads")
@@ -262,3 +297,47 @@ def attention_prefill(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, bloc
         c_int(n_seqs), c_int(max_q_len), c_int(n_q_heads), c_int(n_kv_heads), c_int(k_pages.shape[2]),
         c_int(k_pages.shape[0]), c_int(window), c_float(scale), c_int(1 if skip_single else 0), _ptr(status), _stream())
     _check(code, "attention_prefill")
+
+
+# ---------------------------------------------------------------------------
+# matrix products with few rows
+# ---------------------------------------------------------------------------
+SMALL_M_LIMIT = 16         # rows up to which the weight-streaming kernel is used
+_TARGET_WARPS = 2400       # warps in flight that keep the memory system busy
+
+
+def small_m_supported(x: torch.Tensor, w: torch.Tensor, m: int) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < m <= SMALL_M_LIMIT
+            and w.shape[1] % 8 == 0 and w.is_contiguous() and x.is_contiguous())
+
+
+def small_m_split(n: int, k: int) -> tuple[int, int]:
+    """(slices, k per slice): enough slices that rows / 16 * slices warps fill the GPU, each
+    slice a multiple of 32 wide and at least 256."""
+    tiles = -(-n // 16)
+    want = max(1, min(16, -(-_TARGET_WARPS // tiles)))
+    kper = max(256, -(-(-(-k // want)) // 32) * 32)
+    kper = min(kper, -(-k // 32) * 32)
+    return -(-k // kper), kper
+
+
+def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kper: int | None = None) -> None:
+    """out[:m] = x[:m] @ w.T for m <= 64 rows.  ``out`` is bf16 or fp32 [>=m, n]; or, when the
+    product is split over k (kper < k), fp32 slices [slices, m, n]."""
+    _cuda(out, x, w)
+    n, k = w.shape
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x.is_contiguous()
+          and x.shape[1] == k and k % 8 == 0 and m <= 64, "gemm_small_m: bf16 operands, k a multiple of 8, m <= 64")
+    kper = kper or -(-k // 32) * 32
+    split = -(-k // kper)
+    if split > 1:
+        _need(out.dtype == torch.float32 and out.dim() == 3 and out.shape[0] == split and out.shape[1] == m
+              and out.shape[2] == n and out.is_contiguous(), "gemm_small_m: split output must be fp32 [slices, m, n]")
+        mode, stride = 2, n
+    else:
+        _need(out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= m and out.shape[1] == n
+              and out.dtype in (torch.bfloat16, torch.float32), "gemm_small_m: bad output")
+        mode, stride = (0 if out.dtype == torch.bfloat16 else 1), out.stride(0)
+    code = _fn("gemm_smallm", "tw_gemm_smallm")(_ptr(w), _ptr(x), c_int(m), c_int(n), c_int(k), c_int(kper), _ptr(out),
+                                                c_int(mode), c_int(stride), _stream())
+    _check(code, "gemm_small_m")

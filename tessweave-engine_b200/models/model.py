@@ -18,6 +18,12 @@ class Model:
         # one buffer, two views when the output matrix is tied (flow_engine/model.py:110-112)
         self.head = self.embedding if spec.tie_word_embeddings else runtime.empty(spec.vocab_size, spec.hidden_size)
         self.graph_safe = all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+        # who consumes each run's output: the first norm of the next run, or the final norm
+        self._split_ok = []
+        for i, entry in enumerate(spec.schedule):
+            nxt = self.blocks[spec.schedule[i + 1].layer] if i + 1 < len(spec.schedule) else None
+            consumer = getattr(nxt, "norm1", None) if nxt is not None else self.final_norm
+            self._split_ok.append(bool(getattr(consumer, "accepts_split_sum", False)))
         self.loaded = False
 
     # ---- weights --------------------------------------------------------
@@ -82,7 +88,9 @@ class Model:
         ops.embed(resid, self.embedding, ctx.token_ids, n, ctx.status)
         stream = ResidualStream(resid)
         for i, entry in enumerate(spec.schedule):
-            self.blocks[entry.layer].forward(ctx, stream, caches[i], write_cache=entry.cache_of is None)
+            block = self.blocks[entry.layer]
+            block.next_norm_accepts_split_sum = self._split_ok[i]
+            block.forward(ctx, stream, caches[i], write_cache=entry.cache_of is None)
         if n_logit_rows > 0:
             y = ctx.workspace.get("model.final", (n_logit_rows, spec.hidden_size), self.runtime.dtype)
             self.final_norm.forward(ctx, y, resid, stream.pending, n_logit_rows, rows=logit_rows)
@@ -91,4 +99,7 @@ class Model:
 
     def head_logits(self, ctx: StepContext, logits: torch.Tensor, y: torch.Tensor, n_rows: int) -> None:
         """logits = y @ head.T in fp32 (reference: flow_engine/model.py:204)."""
-        matmul_nt(logits[:n_rows], y, self.head)
+        if ops.small_m_supported(y, self.head, n_rows):
+            ops.gemm_small_m(logits[:n_rows], y, self.head, n_rows)
+        else:
+            matmul_nt(logits[:n_rows], y, self.head)

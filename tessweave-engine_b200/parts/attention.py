@@ -6,7 +6,7 @@ import torch
 from ..csrc import ops
 from .base import (Mixer, PagedKV, PagedView, PartSpec, Runtime, StepContext, WeightDecl, build_part,
                    register_part)
-from .linear import matmul_nt
+from .linear import SplitSum, linear
 
 
 @register_part("mixer", "gqa_attention")
@@ -62,9 +62,11 @@ class GQAAttention(Mixer):
         if not isinstance(cache, PagedView):
             raise TypeError("gqa_attention needs a paged key/value cache")
         n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
-        qkv = ws.get("attn.qkv", (n, self.qkv_width), dt)
-        matmul_nt(qkv, h, self.w_qkv)
         table = self.position.fused_rotary_table(self.head_dim)
+        qkv = linear(ctx, "attn.qkv", h, self.w_qkv, allow_split=table is not None)
+        source = None
+        if isinstance(qkv, SplitSum):       # the fused kernel below adds the slices itself
+            source, qkv = qkv, ws.get("attn.qkv", (n, self.qkv_width), dt)
         if table is None:
             # generic path: bias, then the position part's own transformation, then the cache write
             if self.b_qkv is not None:
@@ -76,12 +78,10 @@ class GQAAttention(Mixer):
             bias = self.b_qkv
         ops.rope_kv_write(qkv, bias, ctx.positions, ctx.seq_of_token, ctx.seq_slot, cache.block_table, table,
                           cache.k_pages, cache.v_pages, n, self.n_heads, self.n_kv_heads, self.head_dim,
-                          write_cache, ctx.status)
+                          write_cache, ctx.status, source=source)
         out = ws.get("attn.out", (n, self.q_size), dt)
         self._attend(ctx, out, qkv, cache)
-        delta = ws.get("mixer.delta", (n, self.hidden), dt)
-        matmul_nt(delta, out, self.w_o)
-        return delta
+        return linear(ctx, "mixer.delta", out, self.w_o, allow_split=ctx.split_ok)
 
     def _attend_tensor_cores(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, cache: PagedView) -> None:
         """bfloat16: flash attention for requests with several tokens, split-KV attention for

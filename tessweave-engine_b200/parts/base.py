@@ -155,6 +155,7 @@ class StepContext:
     max_kv_len: int = 1
     decode_only: bool = False      # every sequence brings exactly one token
     fixed_shape: bool = False      # the launch is being captured: sizes must not depend on host values of this step
+    split_ok: bool = False         # the consumer of the running sub-layer's output adds split-product slices itself
 
 
 # ---------------------------------------------------------------------------
@@ -185,7 +186,11 @@ class Part:
 
 
 class Norm(Part):
-    """out = norm(resid [+ delta]); updates the fp32 residual stream in place."""
+    """out = norm(resid [+ delta]); updates the fp32 residual stream in place.
+
+    ``delta`` is a tensor of the activation type or, if the norm sets ``accepts_split_sum``,
+    possibly a ``SplitSum`` (fp32 slices of a matrix product split over k)."""
+    accepts_split_sum = False
 
     def forward(self, ctx: StepContext, out: torch.Tensor, resid: torch.Tensor, delta: torch.Tensor | None,
                 n_rows: int, rows: torch.Tensor | None = None) -> None:

@@ -25,6 +25,7 @@ class PreNormBlock(Block):
         self.norm2 = build_part("norm", norm2, runtime)
         self.feed_forward = build_part("feed_forward", feed_forward, runtime)
         self.graph_safe = all(p.graph_safe for p in self.parts().values())
+        self.next_norm_accepts_split_sum = False     # set by the model: the norm that consumes this block's output
 
     def parts(self):
         return {"norm1": self.norm1, "mixer": self.mixer, "norm2": self.norm2, "feed_forward": self.feed_forward}
@@ -48,6 +49,11 @@ class PreNormBlock(Block):
         n = ctx.n_tokens
         h = ctx.workspace.get("block.h", (n, self.hidden), self.runtime.dtype)
         self.norm1.forward(ctx, h, stream.resid, stream.pending, n)
+        # a sub-layer may hand its output over as the slices of a split product if the norm
+        # that consumes it can add them
+        ctx.split_ok = self.norm2.accepts_split_sum
         delta = self.mixer.forward(ctx, h, cache, write_cache)
         self.norm2.forward(ctx, h, stream.resid, delta, n)
+        ctx.split_ok = self.next_norm_accepts_split_sum
         stream.pending = self.feed_forward.forward(ctx, h)
+        ctx.split_ok = False

@@ -5,7 +5,7 @@ import torch
 
 from ..csrc import ops
 from .base import FeedForward, Runtime, StepContext, WeightDecl, register_part
-from .linear import matmul_nt
+from .linear import linear
 
 
 @register_part("feed_forward", "swiglu")
@@ -32,10 +32,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
-        gate_up = ws.get("ffn.gate_up", (n, 2 * self.intermediate), dt)
-        matmul_nt(gate_up, h, self.w_gate_up)
+        gate_up = linear(ctx, "ffn.gate_up", h, self.w_gate_up)
         act = ws.get("ffn.act", (n, self.intermediate), dt)
         ops.silu_mul(act, gate_up, n)
-        delta = ws.get("ffn.delta", (n, self.hidden), dt)
-        matmul_nt(delta, act, self.w_down)
-        return delta
+        return linear(ctx, "ffn.delta", act, self.w_down, allow_split=ctx.split_ok)

@@ -10,6 +10,9 @@ from __future__ import annotations
 
 import torch
 
+from ..csrc import ops
+from ..csrc.ops import SplitSum
+
 _configured = False
 
 
@@ -35,3 +38,30 @@ def matmul_nt(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tens
     else:
         torch.mm(x, w.t(), out=out)
     return out
+
+
+def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+           allow_split: bool = False):
+    """``x @ w.T`` into the workspace buffer ``name``.
+
+    Steps with few rows (decode) in bfloat16 go through the weight-streaming kernel of
+    csrc/gemm_smallm.cu; when the matrix has too few rows to fill the GPU that kernel splits
+    k and, if the caller can take it (``allow_split``), the fp32 slices are returned as a
+    ``SplitSum`` for the consuming kernel to add.  Everything else is a library product.
+    """
+    m, n = x.shape[0], w.shape[0]
+    dtype = out_dtype or x.dtype
+    if x.is_cuda and ops.small_m_supported(x, w, m):
+        split, kper = ops.small_m_split(n, w.shape[1])
+        if split > 1 and allow_split:
+            slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
+            ops.gemm_small_m(slices, x, w, m, kper)
+            return SplitSum(slices)
+        if split > 1:
+            slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
+            ops.gemm_small_m(slices, x, w, m, kper)
+            return SplitSum(slices).dense(dtype, ctx.workspace.get(name, (m, n), dtype))
+        out = ctx.workspace.get(name, (m, n), dtype)
+        ops.gemm_small_m(out, x, w, m)
+        return out
+    return matmul_nt(ctx.workspace.get(name, (m, n), dtype), x, w)

@@ -14,6 +14,7 @@ class RMSNorm(Norm):
     Reference: flow_engine/model.py:15-23.  The pending delta of the previous
     sub-layer is added to the residual stream in the same kernel.
     """
+    accepts_split_sum = True
 
     def __init__(self, runtime: Runtime, size: int, eps: float, weight_name: str = "weight"):
         super().__init__(runtime)

@@ -377,3 +377,44 @@ def test_tensor_core_attention_finds_one_far_key(kind, where):
     assert torch.allclose(got, want, **TOL["bfloat16"])
     hit = (got[0, 0] - marker).abs().max() < 0.5
     assert bool(hit) == (where != "window_edge_outside")
+
+
+# ---------------------------------------------------------------------------
+# matrix products with few rows
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("n,k", [(100, 64), (37, 200), (4608, 3584), (1000, 18944)])
+def test_gemm_small_m(m, n, k):
+    """Weight-streaming product against fp32 torch, whole and split over k; n and k with ragged
+    tails (n no multiple of 16, k no multiple of 32)."""
+    torch.manual_seed(m * 1000 + n)
+    x = dev(torch.randn(m, k) * 0.5, torch.bfloat16)
+    w = dev(torch.randn(n, k) * 0.05, torch.bfloat16)
+    want = x.float() @ w.float().t()
+    tol = dict(atol=2e-3 * max(1.0, float(want.abs().max())), rtol=0)
+    out32 = torch.full((m, n), float("nan"), device="cuda")
+    ops().gemm_small_m(out32, x, w, m)
+    assert torch.allclose(out32, want, **tol)
+    out16 = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    ops().gemm_small_m(out16, x, w, m)
+    assert torch.allclose(out16.float(), want, atol=tol["atol"] + 8e-3 * float(want.abs().max()), rtol=0)
+    for kper in (32, 256, 416):
+        if kper >= k:
+            continue
+        split = -(-k // kper)
+        slices = torch.full((split, m, n), float("nan"), device="cuda")
+        ops().gemm_small_m(slices, x, w, m, kper)
+        assert torch.allclose(slices.sum(0), want, **tol)
+        from tessweave_engine_b200.csrc.ops import SplitSum
+        dense = SplitSum(slices).dense(torch.float32)
+        assert torch.allclose(dense, want, **tol)
+        # consumers that add the slices themselves
+        if n == 1000:
+            resid = dev(torch.randn(m, n))
+            weight = dev(1 + 0.1 * torch.randn(n))
+            out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+            r = resid.clone()
+            ops().add_rmsnorm(out, r, SplitSum(slices), weight, 1e-6, m)
+            assert torch.allclose(r, resid + dense, atol=1e-5)
+            assert torch.allclose(out.float().cpu(), plain_qwen2.rms_norm((resid + dense).cpu(), weight.cpu(), 1e-6),
+                                  **TOL["bfloat16"])
