@@ -44,6 +44,7 @@ class Lease:
     tables: list[list[int]]                 # per group: logical block -> page, -1 = none
     promised: list[int]                     # per group: pages promised but not yet taken
     first_live_block: list[int]             # per group: blocks before this were given back
+    ensured_blocks: list[int] = field(default_factory=list)   # per group: every block below this has been handled
     cached_tokens: int = 0                  # tokens covered by shared prefix pages at admission
     published_blocks: int = 0
     reserved: bool = False                  # pages were promised at admission
@@ -265,11 +266,17 @@ class CacheManager:
         blocks = math.ceil(n_tokens / self.page_size)
         if blocks > self.max_blocks:
             raise CapacityError("the request has outgrown the configured context")
+        if not lease.ensured_blocks:
+            lease.ensured_blocks = [0] * len(self.groups)
         for gi, g in enumerate(self.groups):
+            if blocks <= lease.ensured_blocks[gi]:
+                continue
             table = lease.tables[gi]
             if len(table) < blocks:
                 table.extend([-1] * (blocks - len(table)))
-            want = [b for b in range(lease.first_live_block[gi], blocks) if table[b] < 0]
+            start = max(lease.first_live_block[gi], lease.ensured_blocks[gi])
+            want = [b for b in range(start, blocks) if table[b] < 0]
+            lease.ensured_blocks[gi] = blocks
             if not want:
                 continue
             from_promise = min(lease.promised[gi], len(want))

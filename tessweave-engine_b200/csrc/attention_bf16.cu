@@ -6,7 +6,7 @@
 //     slice of the keys); all query heads of the group are the rows of one MMA tile, so keys
 //     and values are read once for the whole group.  The keys are split over blocks
 //     ("split-KV"); partial results (fp32 accumulator, running maximum, sum) go to scratch
-//     memory and a second kernel merges them.
+//     memory, and the block that finishes last merges them in slice order.
 //   * prefill: requests that bring several tokens.  A block serves 64 rows, a row being a
 //     (token, query head of the group) pair, and walks the keys up to the last visible one.
 // Scores, softmax statistics and the accumulator are fp32; probabilities are rounded to
@@ -83,8 +83,12 @@ __device__ __forceinline__ long long key_offset(int p, int limit, const int* tab
 // ---------------------------------------------------------------------------------------
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_TILE = 64;                                  // keys per block and iteration (16 per warp)
+constexpr int DEC_STAGES = 3;                                 // tiles of a warp in shared memory (2 in flight)
 constexpr int DEC_STAGE = 2 * 16 * DP;                        // elements of one warp stage: K then V
-constexpr int DEC_SMEM = DEC_WARPS * 2 * DEC_STAGE * 2 + DEC_WARPS * 16 * 8 * 2;   // stages + row offsets (2 stages)
+constexpr int DEC_PAGE_CACHE = 1024;                          // block-table entries kept in shared memory
+constexpr int DEC_SMEM_STAGES = DEC_WARPS * DEC_STAGES * DEC_STAGE * 2;
+constexpr int DEC_SMEM_OFFS = DEC_WARPS * DEC_STAGES * 16 * 8;  // row offsets of the tiles in flight
+constexpr int DEC_SMEM = DEC_SMEM_STAGES + DEC_SMEM_OFFS + DEC_PAGE_CACHE * 4;
 
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
@@ -93,8 +97,10 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
                    const int* __restrict__ block_table, int table_stride, const bf16* __restrict__ k_cache,
                    const bf16* __restrict__ v_cache, int Hq, int Hkv, int page_size, int num_pages, int window,
                    float scale_log2e, int nsplit, float* __restrict__ partial_o, float* __restrict__ partial_ml,
-                   int* status) {
+                   int* __restrict__ counters, int* status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int s_is_last;
+    __shared__ float s_row_max[16];
     const int s = blockIdx.z, kvh = blockIdx.y;
     const int split = blockIdx.x % nsplit, ht = blockIdx.x / nsplit;
     if (seq_q_len[s] != 1) return;
@@ -111,8 +117,19 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
     const int g = lane >> 2, c = lane & 3;
     const int* table = block_table + (size_t)seq_slot[s] * table_stride;
 
-    bf16* stage_base = reinterpret_cast<bf16*>(smem_raw) + warp * 2 * DEC_STAGE;
-    long long* offs_base = reinterpret_cast<long long*>(smem_raw + DEC_WARPS * 2 * DEC_STAGE * 2) + warp * 2 * 16;
+    bf16* stage_base = reinterpret_cast<bf16*>(smem_raw) + warp * DEC_STAGES * DEC_STAGE;
+    long long* offs_base = reinterpret_cast<long long*>(smem_raw + DEC_SMEM_STAGES) + warp * DEC_STAGES * 16;
+    int* page_cache = reinterpret_cast<int*>(smem_raw + DEC_SMEM_STAGES + DEC_SMEM_OFFS);
+
+    // the block-table entries of this block's keys, read once
+    const int first_blk = k_begin / page_size;
+    if (k_begin < k_end) {
+        const int last_blk = (k_end - 1) / page_size;
+        const int nblk = min(DEC_PAGE_CACHE, last_blk - first_blk + 1);
+        for (int i = threadIdx.x; i < nblk; i += DEC_WARPS * 32)
+            page_cache[i] = first_blk + i < table_stride ? table[first_blk + i] : -1;
+    }
+    __syncthreads();
 
     // query fragments: rows g and g + 8 are heads h0 + g and h0 + g + 8 of this group
     uint32_t qf[KSTEPS][4];
@@ -137,35 +154,45 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
 
     const int ntiles = k_begin < k_end ? (k_end - k_begin + DEC_TILE - 1) / DEC_TILE : 0;
 
+    // lanes 0..15 find the row offsets of the warp's 16 keys from the cached block-table entries
     auto load_tile = [&](int t, int st) {
-        const int kb = k_begin + t * DEC_TILE + warp * 16;
-        long long* offs = offs_base + st * 16;
-        if (lane < 16)
-            offs[lane] = key_offset(kb + lane, k_end, table, table_stride, page_size, num_pages, Hkv, kvh, status);
-        __syncwarp();
-        bf16* ks_ = stage_base + st * DEC_STAGE;
-        bf16* vs_ = ks_ + 16 * DP;
+        if (t < ntiles) {
+            const int kb = k_begin + t * DEC_TILE + warp * 16;
+            long long* offs = offs_base + st * 16;
+            if (lane < 16) {
+                const int p = kb + lane;
+                long long off = -1;
+                if (p < k_end) {
+                    const int blk = p / page_size;
+                    const int page = blk - first_blk < DEC_PAGE_CACHE ? page_cache[blk - first_blk]
+                                                                      : (blk < table_stride ? table[blk] : -1);
+                    if (page < 0 || page >= num_pages) atomicOr(status, TW_ERR_PAGE);
+                    else off = (((long long)page * Hkv + kvh) * page_size + (p - blk * page_size)) * D;
+                }
+                offs[lane] = off;
+            }
+            __syncwarp();
+            bf16* ks_ = stage_base + st * DEC_STAGE;
+            bf16* vs_ = ks_ + 16 * DP;
 #pragma unroll
-        for (int i = lane; i < 16 * CHUNKS; i += 32) {
-            const int row = i / CHUNKS, col = i - row * CHUNKS;
-            const long long off = offs[row];
-            const int bytes = off >= 0 ? 16 : 0;
-            const long long src = off >= 0 ? off + col * 8 : 0;
-            cp_async16(ks_ + row * DP + col * 8, k_cache + src, bytes);
-            cp_async16(vs_ + row * DP + col * 8, v_cache + src, bytes);
+            for (int i = lane; i < 16 * CHUNKS; i += 32) {
+                const int row = i / CHUNKS, col = i - row * CHUNKS;
+                const long long off = offs[row];
+                const int bytes = off >= 0 ? 16 : 0;
+                const long long src = off >= 0 ? off + col * 8 : 0;
+                cp_async16(ks_ + row * DP + col * 8, k_cache + src, bytes);
+                cp_async16(vs_ + row * DP + col * 8, v_cache + src, bytes);
+            }
         }
-        cp_async_commit();
+        cp_async_commit();      // one group per tile slot, empty past the end, so the wait count is constant
     };
 
-    if (ntiles > 0) load_tile(0, 0);
+#pragma unroll
+    for (int t = 0; t < DEC_STAGES - 1; ++t) load_tile(t, t);
     for (int t = 0; t < ntiles; ++t) {
-        const int st = t & 1;
-        if (t + 1 < ntiles) {
-            load_tile(t + 1, st ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int st = t % DEC_STAGES;
+        load_tile(t + DEC_STAGES - 1, (t + DEC_STAGES - 1) % DEC_STAGES);
+        cp_async_wait<DEC_STAGES - 1>();
         __syncwarp();
         const int kb = k_begin + t * DEC_TILE + warp * 16;
         if (kb < k_end) {
@@ -233,6 +260,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         }
         __syncwarp();
     }
+    cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -279,30 +307,61 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
             if (d == 0) { partial_ml[base * 2] = M; partial_ml[base * 2 + 1] = L; }
         }
     }
-}
+    if (nsplit == 1) return;
 
-// Merge of the split results: out = sum_i o_i 2^(m_i - M) / sum_i l_i 2^(m_i - M).
-__global__ void attn_decode_merge_kernel(bf16* __restrict__ out, int out_stride, const int* __restrict__ seq_q_start,
-                                         const int* __restrict__ seq_q_len, int Hq, int nsplit,
-                                         const float* __restrict__ partial_o, const float* __restrict__ partial_ml) {
-    const int s = blockIdx.x, head = blockIdx.y;
-    if (seq_q_len[s] != 1) return;
-    const int n = seq_q_start[s];
-    const size_t base = ((size_t)s * Hq + head) * nsplit;
-    float M = NEG_INF;
-    for (int i = 0; i < nsplit; ++i) M = fmaxf(M, partial_ml[(base + i) * 2]);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float L = 0.f, o = 0.f;
-        if (M != NEG_INF) {
-            for (int i = 0; i < nsplit; ++i) {
-                const float mi = partial_ml[(base + i) * 2];
-                if (mi == NEG_INF) continue;
-                const float f = exp2f(mi - M);
-                L += partial_ml[(base + i) * 2 + 1] * f;
-                o += partial_o[(base + i) * D + d] * f;
-            }
+    // The block that finishes last among the slices of this (request, head tile) merges them, in
+    // slice order, so the result does not depend on which block that is:
+    //   out = sum_i o_i 2^(m_i - M) / sum_i l_i 2^(m_i - M)
+    __threadfence();
+    __syncthreads();
+    int* counter = counters + ((size_t)s * Hkv + kvh) * (gridDim.x / nsplit) + ht;
+    if (threadIdx.x == 0) {
+        const int done = atomicAdd(counter, 1);
+        s_is_last = done == nsplit - 1;
+        if (s_is_last) *counter = 0;         // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_is_last) return;
+    __threadfence();
+    // factors 2^(m_i - M) and weighted sums l_i 2^(m_i - M) of every (head, slice), loaded in parallel
+    float* fac = reinterpret_cast<float*>(smem_raw);              // [nheads][nsplit]
+    float* lsum = fac + 16 * nsplit;                              // [nheads][nsplit]
+    const size_t group_base = ((size_t)s * Hq + kvh * G + h0) * nsplit;      // slices of head h0 start here
+    for (int idx = threadIdx.x; idx < nheads * nsplit; idx += DEC_WARPS * 32) {
+        fac[idx] = __ldcg(partial_ml + (group_base + idx) * 2);
+        lsum[idx] = __ldcg(partial_ml + (group_base + idx) * 2 + 1);
+    }
+    __syncthreads();
+    if (threadIdx.x < nheads) {
+        float M = NEG_INF;
+        for (int i = 0; i < nsplit; ++i) M = fmaxf(M, fac[threadIdx.x * nsplit + i]);
+        s_row_max[threadIdx.x] = M;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nheads * nsplit; idx += DEC_WARPS * 32) {
+        const float M = s_row_max[idx / nsplit];
+        const float mi = fac[idx];
+        const float f = (mi == NEG_INF || M == NEG_INF) ? 0.f : exp2f(mi - M);
+        fac[idx] = f;
+        lsum[idx] *= f;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nheads * D; idx += DEC_WARPS * 32) {
+        const int row = idx / D, d = idx - row * D;
+        const float* f = fac + row * nsplit;
+        const float* po = partial_o + (group_base + (size_t)row * nsplit) * D + d;
+        float L = 0.f, o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+        for (int i = 0; i < nsplit; ++i) L += lsum[row * nsplit + i];
+        int i = 0;
+        for (; i + 4 <= nsplit; i += 4) {          // four independent loads in flight; fixed order of the sums
+            o0 += __ldcg(po + (size_t)i * D) * f[i];
+            o1 += __ldcg(po + (size_t)(i + 1) * D) * f[i + 1];
+            o2 += __ldcg(po + (size_t)(i + 2) * D) * f[i + 2];
+            o3 += __ldcg(po + (size_t)(i + 3) * D) * f[i + 3];
         }
-        out[(size_t)n * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+        for (; i < nsplit; ++i) o0 += __ldcg(po + (size_t)i * D) * f[i];
+        const float o = (o0 + o1) + (o2 + o3);
+        out[(size_t)n * out_stride + (size_t)(kvh * G + h0 + row) * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
     }
 }
 
@@ -515,6 +574,8 @@ int set_attrs() {
 TW_EXPORT int tw_attn_head_dim() { return D; }
 
 // Scratch floats the decode kernel needs for `n_seqs` requests: partial accumulators, then (max, sum) pairs.
+// Beside them it needs one int32 counter per (request, key/value head, tile of 16 heads), zero before the
+// first launch; the kernel leaves them zero.
 TW_EXPORT long long tw_attn_decode_scratch_floats(int n_seqs, int Hq, int nsplit) {
     return (long long)n_seqs * Hq * nsplit * (D + 2);
 }
@@ -523,9 +584,9 @@ TW_EXPORT int tw_attn_decode(void* out, int out_stride, const void* q, int q_str
                              const int* seq_q_len, const int* seq_kv_len, const int* seq_slot, const int* block_table,
                              int table_stride, const void* k_cache, const void* v_cache, int n_seqs, int Hq, int Hkv,
                              int page_size, int num_pages, int window, float scale, int nsplit, float* scratch,
-                             int* status, cudaStream_t stream) {
+                             int* counters, int* status, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
-    if (Hkv <= 0 || Hq % Hkv || nsplit < 1 || (nsplit > 1 && !scratch)) return (int)cudaErrorInvalidValue;
+    if (Hkv <= 0 || Hq % Hkv || nsplit < 1 || (nsplit > 1 && (!scratch || !counters))) return (int)cudaErrorInvalidValue;
     if (int e = set_attrs()) return e;
     const int G = Hq / Hkv, htiles = (G + 15) / 16;
     float* partial_o = scratch;
@@ -534,12 +595,7 @@ TW_EXPORT int tw_attn_decode(void* out, int out_stride, const void* q, int q_str
     attn_decode_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, stream>>>(
         (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
-        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, status);
-    if (nsplit > 1) {
-        dim3 mgrid(n_seqs, Hq);
-        attn_decode_merge_kernel<<<mgrid, D < 32 ? 32 : (D > 128 ? 128 : D), 0, stream>>>(
-            (bf16*)out, out_stride, seq_q_start, seq_q_len, Hq, nsplit, partial_o, partial_ml);
-    }
+        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status);
     return TW_LAUNCH_CHECK();
 }
 

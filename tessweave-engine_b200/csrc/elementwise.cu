@@ -5,6 +5,9 @@
 // All statistics, angles and sums are fp32; `T` is the storage type of
 // activations and cache (float or bf16).  Every kernel takes any row width.
 #include "common.cuh"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 // ---------------------------------------------------------------------------
 // Embedding: resid[n, :] = float(table[ids[n], :]).  No scaling
@@ -50,11 +53,14 @@ TW_EXPORT int tw_embed(void* resid, const void* table, const int* ids, int n_tok
 // The delta is either a dense tensor of the activation type or `nsplit` fp32 slices of a
 // split matrix product ([slice][row][hidden], slices `split_stride` floats apart), which
 // are added here in slice order.
-template <typename T>
-__global__ void add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,
-                                   const float* __restrict__ partial, int nsplit, size_t split_stride,
-                                   const float* __restrict__ weight, float eps, int hidden,
-                                   const int* __restrict__ rows) {
+#define TW_NORM_THREADS 512
+#define TW_NORM_MAXV 16          // values a thread keeps in registers: rows up to 512 * 16 wide take the one-pass path
+
+template <typename T, bool ONE_PASS>
+__global__ void __launch_bounds__(TW_NORM_THREADS)
+add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,
+                   const float* __restrict__ partial, int nsplit, size_t split_stride,
+                   const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -64,25 +70,153 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resi
     const bool has_delta = d || ps;
     auto delta_at = [&](int i) -> float {
         if (d) return tw_to_float(d[i]);
-        float s = 0.f;
-        for (int k = 0; k < nsplit; ++k) s += ps[(size_t)k * split_stride + i];
-        return s;
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;      // fixed order: ((s0 + s1) + (s2 + s3)) over interleaved slices
+        int k = 0;
+        for (; k + 4 <= nsplit; k += 4) {
+            s0 += ps[(size_t)k * split_stride + i];
+            s1 += ps[(size_t)(k + 1) * split_stride + i];
+            s2 += ps[(size_t)(k + 2) * split_stride + i];
+            s3 += ps[(size_t)(k + 3) * split_stride + i];
+        }
+        for (; k < nsplit; ++k) s0 += ps[(size_t)k * split_stride + i];
+        return (s0 + s1) + (s2 + s3);
     };
+    T* o = out + (size_t)r * hidden;
+    if (ONE_PASS) {
+        float v[TW_NORM_MAXV];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < TW_NORM_MAXV; ++j) {
+            const int i = threadIdx.x + j * TW_NORM_THREADS;
+            v[j] = 0.f;
+            if (i < hidden) {
+                v[j] = x[i];
+                if (has_delta) v[j] += delta_at(i);
+                if (!rows && has_delta) x[i] = v[j];
+                ss += v[j] * v[j];
+            }
+        }
+        ss = tw_block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+        for (int j = 0; j < TW_NORM_MAXV; ++j) {
+            const int i = threadIdx.x + j * TW_NORM_THREADS;
+            if (i < hidden) o[i] = tw_from_float<T>((v[j] * inv) * weight[i]);
+        }
+    } else {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v = x[i];
+            if (has_delta) v += delta_at(i);
+            if (!rows && has_delta) x[i] = v;
+            ss += v * v;
+        }
+        ss = tw_block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v = x[i];
+            if (rows && has_delta) v += delta_at(i);
+            o[i] = tw_from_float<T>((v * inv) * weight[i]);
+        }
+    }
+}
+
+// The same for steps with few rows: a cluster of CTAs shares one row, each CTA owning a
+// range of columns, and the partial sums of squares meet in distributed shared memory
+// (added in rank order, so the result does not depend on timing).  With one CTA per row a
+// decode step of 8 rows would keep only 8 SMs busy.
+#define TW_NORM_CLUSTER 8
+#define TW_NORM_CTHREADS 256
+#define TW_NORM_CMAXV 4
+
+template <typename T>
+__global__ void __launch_bounds__(TW_NORM_CTHREADS)
+add_rmsnorm_cluster_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,
+                           const float* __restrict__ partial, int nsplit, size_t split_stride,
+                           const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
+    __shared__ float scratch[33];
+    __shared__ float my_ss;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int r = blockIdx.x / TW_NORM_CLUSTER;
+    const int src = rows ? rows[r] : r;
+    const int chunk = (hidden + TW_NORM_CLUSTER - 1) / TW_NORM_CLUSTER;
+    const int c0 = rank * chunk, c1 = min(hidden, c0 + chunk);
+    float* x = resid + (size_t)src * hidden;
+    const T* d = delta ? delta + (size_t)src * hidden : nullptr;
+    const float* ps = partial ? partial + (size_t)src * hidden : nullptr;
+    const bool has_delta = d || ps;
+    float v[TW_NORM_CMAXV];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v = x[i];
-        if (has_delta) v += delta_at(i);
-        if (!rows && has_delta) x[i] = v;
-        ss += v * v;
+#pragma unroll
+    for (int j = 0; j < TW_NORM_CMAXV; ++j) {
+        const int i = c0 + threadIdx.x + j * TW_NORM_CTHREADS;
+        v[j] = 0.f;
+        if (i < c1) {
+            float dv = 0.f;
+            if (d) {
+                dv = tw_to_float(d[i]);
+            } else if (ps) {
+                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+                int k = 0;
+                for (; k + 4 <= nsplit; k += 4) {
+                    s0 += ps[(size_t)k * split_stride + i];
+                    s1 += ps[(size_t)(k + 1) * split_stride + i];
+                    s2 += ps[(size_t)(k + 2) * split_stride + i];
+                    s3 += ps[(size_t)(k + 3) * split_stride + i];
+                }
+                for (; k < nsplit; ++k) s0 += ps[(size_t)k * split_stride + i];
+                dv = (s0 + s1) + (s2 + s3);
+            }
+            v[j] = x[i] + dv;
+            if (!rows && has_delta) x[i] = v[j];
+            ss += v[j] * v[j];
+        }
     }
     ss = tw_block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    if (threadIdx.x == 0) my_ss = ss;
+    cluster.sync();
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < TW_NORM_CLUSTER; ++k) total += *cluster.map_shared_rank(&my_ss, k);
+    cluster.sync();      // nobody leaves while a neighbour may still read its shared memory
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
     T* o = out + (size_t)r * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v = x[i];
-        if (rows && has_delta) v += delta_at(i);
-        o[i] = tw_from_float<T>((v * inv) * weight[i]);
+#pragma unroll
+    for (int j = 0; j < TW_NORM_CMAXV; ++j) {
+        const int i = c0 + threadIdx.x + j * TW_NORM_CTHREADS;
+        if (i < c1) o[i] = tw_from_float<T>((v[j] * inv) * weight[i]);
     }
+}
+
+template <typename T>
+static int launch_add_rmsnorm(T* out, float* resid, const T* delta, const float* partial, int nsplit,
+                              size_t split_stride, const float* weight, float eps, int n_rows, int hidden,
+                              const int* rows, cudaStream_t stream) {
+    if (n_rows <= 64 && hidden >= 1024 && hidden <= TW_NORM_CLUSTER * TW_NORM_CTHREADS * TW_NORM_CMAXV) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(n_rows * TW_NORM_CLUSTER);
+        cfg.blockDim = dim3(TW_NORM_CTHREADS);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = TW_NORM_CLUSTER;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, add_rmsnorm_cluster_kernel<T>, out, resid, delta, partial, nsplit,
+                                           split_stride, weight, eps, hidden, rows);
+        return e != cudaSuccess ? (int)e : TW_LAUNCH_CHECK();
+    }
+    if (hidden <= TW_NORM_THREADS * TW_NORM_MAXV)
+        add_rmsnorm_kernel<T, true><<<n_rows, TW_NORM_THREADS, 0, stream>>>(out, resid, delta, partial, nsplit,
+                                                                            split_stride, weight, eps, hidden, rows);
+    else
+        add_rmsnorm_kernel<T, false><<<n_rows, TW_NORM_THREADS, 0, stream>>>(out, resid, delta, partial, nsplit,
+                                                                             split_stride, weight, eps, hidden, rows);
+    return TW_LAUNCH_CHECK();
 }
 
 TW_EXPORT int tw_add_rmsnorm(void* out, float* resid, const void* delta, const float* partial, int nsplit,
@@ -90,16 +224,11 @@ TW_EXPORT int tw_add_rmsnorm(void* out, float* resid, const void* delta, const f
                              const int* rows, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (delta && partial) return (int)cudaErrorInvalidValue;
-    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     if (dtype == TW_F32)
-        add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((float*)out, resid, (const float*)delta, partial,
-                                                                  nsplit, (size_t)split_stride, weight, eps, hidden,
-                                                                  rows);
-    else
-        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
-            (__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, partial, nsplit, (size_t)split_stride, weight,
-            eps, hidden, rows);
-    return TW_LAUNCH_CHECK();
+        return launch_add_rmsnorm<float>((float*)out, resid, (const float*)delta, partial, nsplit, (size_t)split_stride,
+                                         weight, eps, n_rows, hidden, rows, stream);
+    return launch_add_rmsnorm<__nv_bfloat16>((__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, partial, nsplit,
+                                             (size_t)split_stride, weight, eps, n_rows, hidden, rows, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -117,14 +246,16 @@ TW_EXPORT int tw_add_rmsnorm(void* out, float* resid, const void* delta, const f
 // ---------------------------------------------------------------------------
 // The source of a row is the qkv buffer itself or, when the projection was split over k,
 // the sum of `nsplit` fp32 slices [slice][token][width]; q always lands in the qkv buffer.
+#define TW_ROPE_THREADS 128
+
 template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const float* __restrict__ partial,
-                                     int nsplit, size_t split_stride, const float* __restrict__ bias,
-                                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                                     const int* __restrict__ seq_slot, const int* __restrict__ block_table,
-                                     int table_stride, const float* __restrict__ inv_freq, T* __restrict__ k_cache,
-                                     T* __restrict__ v_cache, int Hq, int Hkv, int D, int page_size, int num_pages,
-                                     int write_cache, int* status) {
+__global__ void __launch_bounds__(TW_ROPE_THREADS)
+rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const float* __restrict__ partial, int nsplit,
+                     size_t split_stride, const float* __restrict__ bias, const int* __restrict__ positions,
+                     const int* __restrict__ seq_of_token, const int* __restrict__ seq_slot,
+                     const int* __restrict__ block_table, int table_stride, const float* __restrict__ inv_freq,
+                     T* __restrict__ k_cache, T* __restrict__ v_cache, int Hq, int Hkv, int D, int page_size,
+                     int num_pages, int write_cache, int* status) {
     const int n = blockIdx.x;
     const int s = seq_of_token[n];
     if (s < 0) return;  // padding row of a fixed-size batch
@@ -135,9 +266,16 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const 
     const float* prow = partial ? partial + (size_t)n * width : nullptr;
     auto src_at = [&](int col) -> float {
         if (!prow) return tw_to_float(row[col]);
-        float s = 0.f;
-        for (int k = 0; k < nsplit; ++k) s += prow[(size_t)k * split_stride + col];
-        return s;
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        int k = 0;
+        for (; k + 4 <= nsplit; k += 4) {
+            s0 += prow[(size_t)k * split_stride + col];
+            s1 += prow[(size_t)(k + 1) * split_stride + col];
+            s2 += prow[(size_t)(k + 2) * split_stride + col];
+            s3 += prow[(size_t)(k + 3) * split_stride + col];
+        }
+        for (; k < nsplit; ++k) s0 += prow[(size_t)k * split_stride + col];
+        return (s0 + s1) + (s2 + s3);
     };
 
     int page = -1;
@@ -145,14 +283,15 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const 
         const int blk = pos / page_size;
         page = blk < table_stride ? block_table[(size_t)seq_slot[s] * table_stride + blk] : -1;
         if (page < 0 || page >= num_pages) {
-            if (threadIdx.x == 0) atomicOr(status, TW_ERR_PAGE);
+            if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, TW_ERR_PAGE);
             page = -1;
         }
     }
     const int in_page = pos % page_size;
-    const int rot_heads = write_cache ? Hq + Hkv : Hq;
-
-    for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
+    const int rot_pairs = (write_cache ? Hq + Hkv : Hq) * half;     // rotated (q, then k) pairs
+    const int v_pairs = write_cache ? Hkv * half : 0;               // v is copied pair-wise, unrotated
+    const int idx = blockIdx.y * TW_ROPE_THREADS + threadIdx.x;
+    if (idx < rot_pairs) {
         const int head = idx / half, i = idx - head * half;
         const int col = head * D + i;
         float x1 = src_at(col), x2 = src_at(col + half);
@@ -174,15 +313,15 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const 
             dst[i] = tw_from_float<T>(y1);
             dst[i + half] = tw_from_float<T>(y2);
         }
-    }
-    if (page >= 0) {
-        const int voff = (Hq + Hkv) * D;
-        for (int idx = threadIdx.x; idx < Hkv * D; idx += blockDim.x) {
-            const int kvh = idx / D, d = idx - kvh * D;
-            float v = src_at(voff + idx);
-            if (bias) v += bias[voff + idx];
-            v_cache[(((size_t)page * Hkv + kvh) * page_size + in_page) * D + d] = tw_from_float<T>(v);
-        }
+    } else if (idx < rot_pairs + v_pairs && page >= 0) {
+        const int j = idx - rot_pairs;
+        const int kvh = j / half, i = j - kvh * half;
+        const int col = (Hq + Hkv) * D + kvh * D + i;
+        float v1 = src_at(col), v2 = src_at(col + half);
+        if (bias) { v1 += bias[col]; v2 += bias[col + half]; }
+        T* dst = v_cache + (((size_t)page * Hkv + kvh) * page_size + in_page) * D;
+        dst[i] = tw_from_float<T>(v1);
+        dst[i + half] = tw_from_float<T>(v2);
     }
 }
 
@@ -194,15 +333,16 @@ TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, 
                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (D <= 0 || (D & 1)) return (int)cudaErrorInvalidValue;
-    const int work = (Hq + Hkv) * (D / 2);
-    const int threads = work >= 1024 ? 256 : 128;
+    const int work = (Hq + 2 * Hkv) * (D / 2);
+    const dim3 grid(n_tokens, (work + TW_ROPE_THREADS - 1) / TW_ROPE_THREADS);
+    const int threads = TW_ROPE_THREADS;
     if (dtype == TW_F32)
-        rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>(
+        rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(
             (float*)qkv, qkv_stride, partial, nsplit, (size_t)split_stride, bias, positions, seq_of_token, seq_slot,
             block_table, table_stride, inv_freq,
             (float*)k_cache, (float*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache, status);
     else
-        rope_kv_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
             (__nv_bfloat16*)qkv, qkv_stride, partial, nsplit, (size_t)split_stride, bias, positions, seq_of_token,
             seq_slot, block_table, table_stride, inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache,
             status);
@@ -214,29 +354,37 @@ TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, 
 // with gate = gate_up[n, i] and up = gate_up[n, I + i] (rows packed [gate; up]).
 // Reference: flow_engine/model.py:76-80.
 // ---------------------------------------------------------------------------
+// With `interleaved` the columns come in groups of 16: eight gates, then their eight ups
+// (the packing the fused small-batch kernel wants); otherwise all gates, then all ups.
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, long total) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, long total,
+                                int interleaved) {
     long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     const long step = (long)gridDim.x * blockDim.x;
     for (; idx < total; idx += step) {
         const long n = idx / inter;
         const int i = (int)(idx - n * inter);
-        const float g = tw_to_float(gate_up[n * 2 * inter + i]);
-        const float u = tw_to_float(gate_up[n * 2 * inter + inter + i]);
+        const int gcol = interleaved ? ((i >> 3) << 4) + (i & 7) : i;
+        const int ucol = interleaved ? gcol + 8 : inter + i;
+        const float g = tw_to_float(gate_up[n * 2 * inter + gcol]);
+        const float u = tw_to_float(gate_up[n * 2 * inter + ucol]);
         const float act = g / (1.0f + expf(-g));
         out[idx] = tw_from_float<T>(act * u);
     }
 }
 
-TW_EXPORT int tw_silu_mul(void* out, const void* gate_up, int n_rows, int inter, int dtype, cudaStream_t stream) {
+TW_EXPORT int tw_silu_mul(void* out, const void* gate_up, int n_rows, int inter, int interleaved, int dtype,
+                          cudaStream_t stream) {
     const long total = (long)n_rows * inter;
     if (total <= 0) return 0;
     long blocks = (total + 255) / 256;
     if (blocks > 148L * 16) blocks = 148L * 16;
     if (dtype == TW_F32)
-        silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
+        silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)out, (const float*)gate_up, inter, total,
+                                                                interleaved);
     else
         silu_mul_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)out,
-                                                                        (const __nv_bfloat16*)gate_up, inter, total);
+                                                                        (const __nv_bfloat16*)gate_up, inter, total,
+                                                                        interleaved);
     return TW_LAUNCH_CHECK();
 }

@@ -5,9 +5,10 @@
 // The weights are the 16-row operand of mma.m16n8k16, the (up to 8) tokens of an n-tile the
 // other one ("swap-AB").  A thread reads 16 contiguous bytes (8 values of k) of its two
 // weight rows and of its token row per 32 values of k; since a dot product does not care
-// about the order of k, those 8 values feed two MMAs without any shuffle or shared memory:
-// k-slot (2c + j) of MMA 1 is element j, slot (2c + 8 + j) is element 2 + j, and MMA 2 takes
-// elements 4..7, for the weights and for the tokens alike.
+// about the order of k, each group of 4 values feeds one MMA without any shuffle or shared
+// memory: k-slot (2c + j) is element j of the group and slot (2c + 8 + j) is element 2 + j, for
+// the weights and for the tokens alike.  (The kernel reads 32 bytes per row and step, so that
+// the four threads of a row cover a whole 128-byte line, and keeps two steps in flight.)
 //
 // When a matrix has too few rows to fill the GPU, k is split over blockIdx.y and each slice
 // writes fp32 partial sums to scratch memory [slice][token][n]; the kernels that consume the
@@ -39,9 +40,13 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
 
 constexpr int WARPS = 8;
 constexpr int ROWS_PER_BLOCK = WARPS * 16;
-constexpr int UNROLL = 4;
+constexpr int CHUNK = 64;      // values of k per step: a thread reads 32 contiguous bytes of each of its rows
 
-enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_PARTIAL = 2 };
+enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_PARTIAL = 2, OUT_SILU_MUL = 3 };
+
+struct Frag {          // 16 consecutive values of k of one row
+    uint4 lo, hi;
+};
 
 template <int NT>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -69,26 +74,37 @@ gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M
     for (int t = 0; t < NT; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f; }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
-    for (int k = kbeg; k < kend; k += 32 * UNROLL) {
-        uint4 a0[UNROLL], a1[UNROLL];
+    // kk .. kk + 15 are this thread's values of k in the step that starts at k0
+    auto load_w = [&](const bf16* row, bool valid, int k0) -> Frag {
+        const int kk = k0 + 16 * c;
+        Frag f;
+        f.lo = (valid && kk < kend) ? ld_stream(row + kk) : zero;
+        f.hi = (valid && kk + 8 < kend) ? ld_stream(row + kk + 8) : zero;
+        return f;
+    };
+    auto load_x = [&](const bf16* row, bool valid, int k0) -> Frag {
+        const int kk = k0 + 16 * c;
+        Frag f;
+        f.lo = (valid && kk < kend) ? *reinterpret_cast<const uint4*>(row + kk) : zero;
+        f.hi = (valid && kk + 8 < kend) ? *reinterpret_cast<const uint4*>(row + kk + 8) : zero;
+        return f;
+    };
+
+    Frag a_cur = load_w(wa, va, kbeg), b_cur = load_w(wb, vb, kbeg);
+    Frag a_nxt = load_w(wa, va, kbeg + CHUNK), b_nxt = load_w(wb, vb, kbeg + CHUNK);
+    for (int k = kbeg; k < kend; k += CHUNK) {
+        // two steps ahead: the loads of step k + 2 CHUNK are in flight while step k is multiplied
+        const Frag a_far = load_w(wa, va, k + 2 * CHUNK), b_far = load_w(wb, vb, k + 2 * CHUNK);
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int kk = k + u * 32 + 8 * c;
-            const bool ok = kk < kend;
-            a0[u] = (ok && va) ? ld_stream(wa + kk) : zero;
-            a1[u] = (ok && vb) ? ld_stream(wb + kk) : zero;
+        for (int t = 0; t < NT; ++t) {
+            const Frag xf = load_x(xr[t], vx[t], k);
+            mma_bf16(acc[t], a_cur.lo.x, b_cur.lo.x, a_cur.lo.y, b_cur.lo.y, xf.lo.x, xf.lo.y);
+            mma_bf16(acc[t], a_cur.lo.z, b_cur.lo.z, a_cur.lo.w, b_cur.lo.w, xf.lo.z, xf.lo.w);
+            mma_bf16(acc[t], a_cur.hi.x, b_cur.hi.x, a_cur.hi.y, b_cur.hi.y, xf.hi.x, xf.hi.y);
+            mma_bf16(acc[t], a_cur.hi.z, b_cur.hi.z, a_cur.hi.w, b_cur.hi.w, xf.hi.z, xf.hi.w);
         }
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int kk = k + u * 32 + 8 * c;
-            const bool ok = kk < kend;
-#pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                const uint4 b = (ok && vx[t]) ? *reinterpret_cast<const uint4*>(xr[t] + kk) : zero;
-                mma_bf16(acc[t], a0[u].x, a1[u].x, a0[u].y, a1[u].y, b.x, b.y);
-                mma_bf16(acc[t], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b.z, b.w);
-            }
-        }
+        a_cur = a_nxt; b_cur = b_nxt;
+        a_nxt = a_far; b_nxt = b_far;
     }
     // acc[t][0..1]: weight row ra, tokens t*8 + 2c, +1;  acc[t][2..3]: weight row rb
 #pragma unroll
@@ -97,7 +113,15 @@ gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M
         for (int e = 0; e < 2; ++e) {
             const int tok = t * 8 + 2 * c + e;
             if (tok >= M) continue;
-            if (out_mode == OUT_BF16) {
+            if (out_mode == OUT_SILU_MUL) {
+                // weight rows come in groups of 16: eight gate rows, then the eight up rows that belong to
+                // them, so row ra is a gate and row rb its up: out[tok, r0 / 2 + g] = silu(gate) * up
+                if (vb) {
+                    const float gt = acc[t][e], up = acc[t][2 + e];
+                    reinterpret_cast<bf16*>(out)[(size_t)tok * out_stride + (r0 >> 1) + g] =
+                        __float2bfloat16_rn(gt / (1.0f + expf(-gt)) * up);
+                }
+            } else if (out_mode == OUT_BF16) {
                 bf16* o = reinterpret_cast<bf16*>(out) + (size_t)tok * out_stride;
                 if (va) o[ra] = __float2bfloat16_rn(acc[t][e]);
                 if (vb) o[rb] = __float2bfloat16_rn(acc[t][2 + e]);
@@ -124,11 +148,12 @@ __global__ void reduce_partial_kernel(T* __restrict__ out, const float* __restri
 }  // namespace
 
 // out_mode 0: bf16 [M, out_stride]; 1: fp32 [M, out_stride]; 2: fp32 partial sums [ksplit, M, out_stride]
-// (then kper < K).  K must be a multiple of 8; kper a multiple of 32.
+// (then kper < K); 3: bf16 [M, out_stride] = silu(gate) * up for weights whose rows alternate between eight
+// gate rows and their eight up rows (N a multiple of 16, no split).  K must be a multiple of 8; kper of 32.
 TW_EXPORT int tw_gemm_smallm(const void* w, const void* x, int M, int N, int K, int kper, void* out, int out_mode,
                              int out_stride, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 64 || K <= 0 || (K & 7) || kper <= 0 || (kper & 31) || out_mode < 0 || out_mode > 2)
+    if (M > 64 || K <= 0 || (K & 7) || kper <= 0 || (kper & 31) || out_mode < 0 || out_mode > 3 || (out_mode == OUT_SILU_MUL && (N & 15)))
         return (int)cudaErrorInvalidValue;
     const int ksplit = (K + kper - 1) / kper;
     if (ksplit > 1 && out_mode != OUT_PARTIAL) return (int)cudaErrorInvalidValue;

@@ -52,7 +52,9 @@ def _ptr(t: torch.Tensor | None) -> c_void_p:
 
 
 def _stream() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the raw handle of torch's current stream (what torch.cuda.current_stream().cuda_stream gives, without
+    # building a Stream object for every launch)
+    return c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 def _need(cond: bool, message: str) -> None:
@@ -191,14 +193,16 @@ def rotate_heads(rows: torch.Tensor, bias: torch.Tensor | None, positions: torch
     _check(code, "rotate_heads")
 
 
-def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, n_rows: int) -> None:
-    """out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]."""
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, n_rows: int, interleaved: bool = False) -> None:
+    """out[n, i] = silu(gate[n, i]) * up[n, i].  Columns of ``gate_up`` are [all gates | all ups],
+    or with ``interleaved`` groups of 16: eight gates followed by their eight ups."""
     _cuda(out, gate_up)
     inter = out.shape[1]
     _need(gate_up.shape[1] == 2 * inter and gate_up.is_contiguous() and out.is_contiguous()
           and gate_up.dtype == out.dtype, "silu_mul: gate_up must be contiguous [n, 2I] of the output type")
+    _need(not interleaved or inter % 8 == 0, "silu_mul: interleaved columns need a multiple of 8")
     code = _fn("elementwise", "tw_silu_mul")(_ptr(out), _ptr(gate_up), c_int(n_rows), c_int(inter),
-                                             c_int(dtype_code(out.dtype)), _stream())
+                                             c_int(1 if interleaved else 0), c_int(dtype_code(out.dtype)), _stream())
     _check(code, "silu_mul")
 
 
@@ -251,11 +255,17 @@ def decode_splits(n_seqs: int, n_kv_heads: int, group: int, max_kv_len: int) -> 
     head_tiles = (group + 15) // 16
     tiles = max(1, -(-max_kv_len // 64))
     target = -(-4 * _SM_COUNT // max(1, n_seqs * n_kv_heads * head_tiles))
-    return max(1, min(tiles, target, DECODE_SCRATCH_UNITS // max(1, n_seqs)))
+    return max(1, min(tiles, target, 128, DECODE_SCRATCH_UNITS // max(1, n_seqs)))
 
 
 def decode_scratch_floats(n_q_heads: int, head_dim: int) -> int:
     return DECODE_SCRATCH_UNITS * n_q_heads * (head_dim + 2)
+
+
+def decode_counter_ints(n_seqs: int, n_kv_heads: int, group: int) -> int:
+    """int32 counters (zero before the first launch, left zero by every launch) the split
+    decode kernel uses to find the block that finishes last."""
+    return max(n_seqs, DECODE_SCRATCH_UNITS) * n_kv_heads * ((group + 15) // 16)
 
 
 def _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim):
@@ -271,18 +281,23 @@ def _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_h
 
 
 def attention_decode(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, n_seqs,
-                     n_q_heads, n_kv_heads, head_dim, window, scale, nsplit, scratch, status) -> None:
-    """Split-KV attention for the requests of the batch that bring one token (others are skipped)."""
-    _cuda(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, scratch, status)
+                     n_q_heads, n_kv_heads, head_dim, window, scale, nsplit, scratch, counters, status) -> None:
+    """Split-KV attention for the requests of the batch that bring one token (others are skipped).
+    ``scratch`` (fp32) takes the slices' partial results, ``counters`` (int32, all zero) finds the
+    block that merges them; both are only needed when ``nsplit`` > 1."""
+    _cuda(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, scratch, counters, status)
     _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim)
     if nsplit > 1:
         _need(scratch is not None and scratch.dtype == torch.float32
               and scratch.numel() >= n_seqs * n_q_heads * nsplit * (head_dim + 2), "attention_decode: scratch too small")
+        _need(counters is not None and counters.dtype == torch.int32
+              and counters.numel() >= n_seqs * n_kv_heads * ((n_q_heads // n_kv_heads + 15) // 16),
+              "attention_decode: too few counters")
     code = _fn("attention_bf16", "tw_attn_decode", {"TW_HEAD_DIM": head_dim})(
         _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(seq_q_start), _ptr(seq_q_len),
         _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages),
         c_int(n_seqs), c_int(n_q_heads), c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]),
-        c_int(window), c_float(scale), c_int(nsplit), _ptr(scratch), _ptr(status), _stream())
+        c_int(window), c_float(scale), c_int(nsplit), _ptr(scratch), _ptr(counters), _ptr(status), _stream())
     _check(code, "attention_decode")
 
 
@@ -302,7 +317,7 @@ def attention_prefill(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, bloc
 # ---------------------------------------------------------------------------
 # matrix products with few rows
 # ---------------------------------------------------------------------------
-SMALL_M_LIMIT = 16         # rows up to which the weight-streaming kernel is used
+SMALL_M_LIMIT = 8          # rows up to which the weight-streaming kernel is used
 _TARGET_WARPS = 2400       # warps in flight that keep the memory system busy
 
 
@@ -315,22 +330,30 @@ def small_m_split(n: int, k: int) -> tuple[int, int]:
     """(slices, k per slice): enough slices that rows / 16 * slices warps fill the GPU, each
     slice a multiple of 32 wide and at least 256."""
     tiles = -(-n // 16)
-    want = max(1, min(16, -(-_TARGET_WARPS // tiles)))
+    if tiles >= 1024:          # enough rows to fill the GPU without slices
+        return 1, -(-k // 32) * 32
+    want = max(1, min(12, -(-_TARGET_WARPS // tiles)))
     kper = max(256, -(-(-(-k // want)) // 32) * 32)
     kper = min(kper, -(-k // 32) * 32)
     return -(-k // kper), kper
 
 
-def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kper: int | None = None) -> None:
+def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kper: int | None = None,
+                 silu_mul_pairs: bool = False) -> None:
     """out[:m] = x[:m] @ w.T for m <= 64 rows.  ``out`` is bf16 or fp32 [>=m, n]; or, when the
-    product is split over k (kper < k), fp32 slices [slices, m, n]."""
+    product is split over k (kper < k), fp32 slices [slices, m, n]; or, with ``silu_mul_pairs``
+    (rows of w in groups of eight gates and their eight ups), bf16 [>=m, n / 2] = silu(gate) * up."""
     _cuda(out, x, w)
     n, k = w.shape
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x.is_contiguous()
           and x.shape[1] == k and k % 8 == 0 and m <= 64, "gemm_small_m: bf16 operands, k a multiple of 8, m <= 64")
     kper = kper or -(-k // 32) * 32
     split = -(-k // kper)
-    if split > 1:
+    if silu_mul_pairs:
+        _need(split == 1 and n % 16 == 0 and out.dtype == torch.bfloat16 and out.dim() == 2 and out.stride(1) == 1
+              and out.shape[0] >= m and out.shape[1] == n // 2, "gemm_small_m: bad fused silu output")
+        mode, stride = 3, out.stride(0)
+    elif split > 1:
         _need(out.dtype == torch.float32 and out.dim() == 3 and out.shape[0] == split and out.shape[1] == m
               and out.shape[2] == n and out.is_contiguous(), "gemm_small_m: split output must be fp32 [slices, m, n]")
         mode, stride = 2, n

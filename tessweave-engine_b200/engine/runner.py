@@ -70,6 +70,11 @@ class ModelRunner:
         self._host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
         self._dev = torch.zeros(total, dtype=torch.int32, device=self.device)
         self._h = {k: self._host[o:o + sz] for k, (o, sz) in self._offsets.items()}
+        host_np = self._host.numpy()              # same memory; numpy assigns Python lists much faster
+        self._n = {k: host_np[o:o + sz] for k, (o, sz) in self._offsets.items()}
+        self._n["temperature"] = self._n["temperature"].view("float32")
+        self._n["seed"] = self._n["seed"].view("int64")
+        self._n["counter"] = self._n["counter"].view("int64")
         self._d = {k: self._dev[o:o + sz] for k, (o, sz) in self._offsets.items()}
         self.sampled = torch.zeros(m + 1, dtype=torch.int32, device=self.device)   # ids, then the status word
         self._sampled_host = torch.zeros(m + 1, dtype=torch.int32, pin_memory=True)
@@ -84,7 +89,7 @@ class ModelRunner:
     def _stage(self, entries: list[StepEntry], pad_to: int = 0, all_rows: bool = False) -> tuple[StepContext, int]:
         """Fill the staging buffer for ``entries`` and copy it to the device.  ``pad_to`` pads the
         batch with rows that belong to no request; ``all_rows`` asks for the logits of every row."""
-        h = self._h
+        h = self._n
         self._staged.synchronize()       # the previous step's copy has read the pinned buffer
         n = sum(len(e.tokens) for e in entries)
         s = len(entries)
@@ -116,17 +121,22 @@ class ModelRunner:
         m = len(rows)
         if m > self.max_rows:
             raise ValueError(f"{m} wanted rows exceed the runner's limit of {self.max_rows}")
-        pad = rows_total - n
-        h["token_ids"][:rows_total] = torch.tensor(ids + [0] * pad, dtype=torch.int32)
-        h["positions"][:rows_total] = torch.tensor(pos + [0] * pad, dtype=torch.int32)
-        h["seq_of_token"][:rows_total] = torch.tensor(sot + [-1] * pad, dtype=torch.int32)
-        spad = seqs_total - s
-        h["seq_slot"][:seqs_total] = torch.tensor(slot + [0] * spad, dtype=torch.int32)
-        h["seq_q_start"][:seqs_total] = torch.tensor(qs + [0] * spad, dtype=torch.int32)
-        h["seq_q_len"][:seqs_total] = torch.tensor(ql + [0] * spad, dtype=torch.int32)
-        h["seq_kv_len"][:seqs_total] = torch.tensor(kl + [0] * spad, dtype=torch.int32)
+        h["token_ids"][:n] = ids
+        h["positions"][:n] = pos
+        h["seq_of_token"][:n] = sot
+        if rows_total > n:
+            h["token_ids"][n:rows_total] = 0
+            h["positions"][n:rows_total] = 0
+            h["seq_of_token"][n:rows_total] = -1
+        h["seq_slot"][:s] = slot
+        h["seq_q_start"][:s] = qs
+        h["seq_q_len"][:s] = ql
+        h["seq_kv_len"][:s] = kl
+        if seqs_total > s:
+            for key in ("seq_slot", "seq_q_start", "seq_q_len", "seq_kv_len"):
+                h[key][s:seqs_total] = 0
         if m:
-            h["logit_rows"][:m] = torch.tensor(rows, dtype=torch.int32)
+            h["logit_rows"][:m] = rows
         self._dev.copy_(self._host, non_blocking=True)
         self._staged.record()
         self.cache.sync_tables()
@@ -143,7 +153,7 @@ class ModelRunner:
 
     def _padding_context(self, rows: int, logit_rows: int) -> StepContext:
         """A step of ``rows`` padding rows: every kernel runs, none touches the cache."""
-        h = self._h
+        h = self._n
         self._staged.synchronize()
         h["token_ids"][:rows] = 0
         h["positions"][:rows] = 0
@@ -151,7 +161,7 @@ class ModelRunner:
         seqs = min(rows, self.max_seqs)
         for key in ("seq_slot", "seq_q_start", "seq_q_len", "seq_kv_len"):
             h[key][:seqs] = 0
-        h["logit_rows"][:logit_rows] = torch.arange(logit_rows, dtype=torch.int32) % rows
+        h["logit_rows"][:logit_rows] = [i % rows for i in range(logit_rows)]
         self._dev.copy_(self._host, non_blocking=True)
         self._staged.record()
         d = self._d
@@ -235,9 +245,9 @@ class ModelRunner:
         before ``step`` of the same batch, as it travels in the same copy."""
         m = len(temperature)
         self._staged.synchronize()
-        self._h["temperature"].view(torch.float32)[:m] = torch.tensor(temperature, dtype=torch.float32)
-        self._h["seed"].view(torch.int64)[:m] = torch.tensor(seed, dtype=torch.int64)
-        self._h["counter"].view(torch.int64)[:m] = torch.tensor(counter, dtype=torch.int64)
+        self._n["temperature"][:m] = temperature
+        self._n["seed"][:m] = seed
+        self._n["counter"][:m] = counter
 
     @torch.inference_mode()
     def sample(self, logits: torch.Tensor, greedy_only: bool = False) -> list[int]:

@@ -96,9 +96,13 @@ class GQAAttention(Mixer):
             nsplit = ops.decode_splits(ctx.n_seqs, self.n_kv_heads, self.n_heads // self.n_kv_heads, ctx.max_kv_len)
             scratch = ctx.workspace.get("attn.decode_scratch", (ops.decode_scratch_floats(self.n_heads, self.head_dim),),
                                         torch.float32)
+            counters = ctx.workspace.get(
+                "attn.decode_counters", (ops.decode_counter_ints(ctx.n_seqs, self.n_kv_heads, self.n_heads // self.n_kv_heads),),
+                torch.int32, zero=True)
             ops.attention_decode(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
                                  cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, self.n_heads,
-                                 self.n_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, ctx.status)
+                                 self.n_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, counters,
+                                 ctx.status)
 
     def _attend(self, ctx: StepContext, out: torch.Tensor, qkv: torch.Tensor, cache: PagedView) -> None:
         q = qkv[:, : self.q_size]

@@ -91,7 +91,9 @@ class Workspace:
         self._buffers: dict[str, torch.Tensor] = {}
         self.frozen = False
 
-    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """The buffer ``name`` with at least ``shape`` elements.  ``zero`` fills it with zeros when it
+        is (re)allocated -- for state that kernels keep zero between launches, such as counters."""
         numel = 1
         for s in shape:
             numel *= int(s)
@@ -99,7 +101,8 @@ class Workspace:
         if buf is None or buf.dtype != dtype or buf.numel() < numel:
             if self.frozen:
                 raise RuntimeError(f"workspace buffer {name!r} would have to grow while a CUDA graph holds its address")
-            buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            make = torch.zeros if zero else torch.empty
+            buf = make(max(numel, 1), dtype=dtype, device=self.device)
             self._buffers[name] = buf
         return buf[:numel].view(*shape)
 

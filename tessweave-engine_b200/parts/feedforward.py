@@ -12,8 +12,12 @@ from .linear import linear
 class SwiGLU(FeedForward):
     """delta = (silu(h @ Wg.T) * (h @ Wu.T)) @ Wd.T, no biases.
 
-    gate and up are one product with rows packed [Wg; Wu]; the activation runs in
-    fp32.  Reference: flow_engine/model.py:68-85.
+    gate and up are one product.  The reference packs the rows [Wg; Wu]
+    (flow_engine/model.py:82-85); here, when the intermediate size is a multiple of 8, the rows
+    alternate between eight gate rows and their eight up rows -- an exact permutation -- so
+    that a tensor-core tile of the small-batch kernel holds a gate and its up in one thread and
+    writes silu(gate) * up directly.  The activation runs in fp32.
+    Reference: flow_engine/model.py:68-85.
     """
 
     def __init__(self, runtime: Runtime, hidden: int, intermediate: int):
@@ -23,16 +27,25 @@ class SwiGLU(FeedForward):
         self.hidden, self.intermediate = hidden, intermediate
         self.w_gate_up = runtime.empty(2 * intermediate, hidden)
         self.w_down = runtime.empty(hidden, intermediate)
+        self.interleaved = intermediate % 8 == 0
 
     def weights(self) -> list[WeightDecl]:
         i = self.intermediate
-        return [WeightDecl("gate_proj.weight", (i, self.hidden), dest=self.w_gate_up[:i]),
-                WeightDecl("up_proj.weight", (i, self.hidden), dest=self.w_gate_up[i:]),
+        if self.interleaved:
+            groups = self.w_gate_up.view(i // 8, 2, 8, self.hidden)
+            gate, up = groups[:, 0], groups[:, 1]          # [i / 8, 8, hidden] views; the loader reshapes the source
+        else:
+            gate, up = self.w_gate_up[:i], self.w_gate_up[i:]
+        return [WeightDecl("gate_proj.weight", (i, self.hidden), dest=gate),
+                WeightDecl("up_proj.weight", (i, self.hidden), dest=up),
                 WeightDecl("down_proj.weight", (self.hidden, i), dest=self.w_down)]
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
-        gate_up = linear(ctx, "ffn.gate_up", h, self.w_gate_up)
         act = ws.get("ffn.act", (n, self.intermediate), dt)
-        ops.silu_mul(act, gate_up, n)
+        if self.interleaved and ops.small_m_supported(h, self.w_gate_up, n):
+            ops.gemm_small_m(act, h, self.w_gate_up, n, silu_mul_pairs=True)
+        else:
+            gate_up = linear(ctx, "ffn.gate_up", h, self.w_gate_up)
+            ops.silu_mul(act, gate_up, n, self.interleaved)
         return linear(ctx, "ffn.delta", act, self.w_down, allow_split=ctx.split_ok)

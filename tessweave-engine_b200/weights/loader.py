@@ -71,7 +71,9 @@ def fill_weights(model: Model, folder) -> None:
                     wrong_shape.append(f"{key}: an integer table is expected, checkpoint holds {tensor.dtype}")
                     continue
                 with torch.no_grad():
-                    decl.dest.copy_(tensor)   # casts to the destination's type and moves to its device
+                    # casts to the destination's type and moves to its device; a destination may be a
+                    # strided view of a packed buffer with the same elements in another shape
+                    decl.dest.copy_(tensor.view(decl.dest.shape))
     missing = sorted(set(decls) - seen)
     if missing or unexpected or duplicate or wrong_shape:
         parts = [f"checkpoint {folder} does not fit architecture {spec.architecture}:"]

@@ -86,7 +86,7 @@ def fill_random(model: Model, seed: int = 0, std: float | None = None) -> Model:
         if decl.role == "table_int":
             decl.dest.copy_(torch.randint(0, 2 ** 15, decl.shape, generator=g, device=device, dtype=torch.int32))
             continue
-        rows = decl.shape[0]
+        rows = decl.dest.shape[0]
         step = max(1, (64 << 20) // max(1, decl.dest[0].numel() if decl.dest.dim() > 1 else 1))
         for begin in range(0, rows, step):      # in slabs, so no second full-size copy is alive
             part = decl.dest[begin:begin + step]

@@ -83,6 +83,11 @@ def test_silu_mul(dtype):
     ops().silu_mul(out, gu, n)
     g, u = gu.float().cpu()[:, :inter], gu.float().cpu()[:, inter:]
     assert torch.allclose(out.float().cpu(), g * torch.sigmoid(g) * u, **TOL[dtype])
+    # columns in groups of eight gates and their eight ups
+    ops().silu_mul(out, gu, n, interleaved=True)
+    pairs = gu.float().cpu().reshape(n, inter // 8, 2, 8)
+    g, u = pairs[:, :, 0].reshape(n, inter), pairs[:, :, 1].reshape(n, inter)
+    assert torch.allclose(out.float().cpu(), g * torch.sigmoid(g) * u, **TOL[dtype])
 
 
 def paged_setup(lengths, page, kv_heads, head_dim, dtype, seed=0, extra_pages=5):
@@ -306,8 +311,12 @@ def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None
         max_kv = max(r[-1] + 1 for r in rows_of)
         ns = nsplit or o.decode_splits(len(rows_of), hkv, hq // hkv, max_kv)
         scratch = torch.full((o.decode_scratch_floats(hq, d),), float("nan"), device="cuda")
-        o.attention_decode(out, qd, q_start, q_len, kv_len, slot, setup["table"], setup["k_pages"], setup["v_pages"],
-                           len(rows_of), hq, hkv, d, window, d ** -0.5, ns, scratch, st)
+        counters = torch.zeros(o.decode_counter_ints(len(rows_of), hkv, hq // hkv), dtype=torch.int32, device="cuda")
+        for _ in range(2):      # twice: the counters must come back to zero
+            out.fill_(float("nan")) if not any(len(r) > 1 for r in rows_of) else None
+            o.attention_decode(out, qd, q_start, q_len, kv_len, slot, setup["table"], setup["k_pages"], setup["v_pages"],
+                               len(rows_of), hq, hkv, d, window, d ** -0.5, ns, scratch, counters, st)
+        assert int(counters.abs().sum()) == 0
     assert int(st) == 0
     return out.float().cpu().reshape(n, hq, d), qd.float().cpu().reshape(n, hq, d)
 
@@ -418,3 +427,19 @@ def test_gemm_small_m(m, n, k):
             assert torch.allclose(r, resid + dense, atol=1e-5)
             assert torch.allclose(out.float().cpu(), plain_qwen2.rms_norm((resid + dense).cpu(), weight.cpu(), 1e-6),
                                   **TOL["bfloat16"])
+
+
+@pytest.mark.parametrize("m", [1, 5, 8])
+def test_gemm_small_m_fused_silu(m):
+    """gate/up rows in groups of eight: the kernel writes silu(gate) * up directly."""
+    torch.manual_seed(m)
+    inter, k = 200, 96
+    x = dev(torch.randn(m, k), torch.bfloat16)
+    wg, wu = torch.randn(inter, k) * 0.2, torch.randn(inter, k) * 0.2
+    packed = torch.stack((wg.reshape(inter // 8, 8, k), wu.reshape(inter // 8, 8, k)), 1).reshape(2 * inter, k)
+    w = dev(packed, torch.bfloat16)
+    out = torch.full((m, inter), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops().gemm_small_m(out, x, w, m, silu_mul_pairs=True)
+    g = x.float().cpu() @ wg.to(torch.bfloat16).float().t()
+    u = x.float().cpu() @ wu.to(torch.bfloat16).float().t()
+    assert torch.allclose(out.float().cpu(), g * torch.sigmoid(g) * u, **TOL["bfloat16"])

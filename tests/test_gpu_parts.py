@@ -121,7 +121,7 @@ def build(spec, dtype=torch.float32, page=8, pages=40, requests=3, graphs=False)
     tw.fill_random(model, seed=3)
     cache = tw.CacheManager(model.cache_needs(), page, pages, requests, 256, dtype, model.runtime.device, prefix_cache=False)
     runner = ModelRunner(model, cache, 256, requests, cuda_graphs=graphs)
-    weights = {k: d.dest.detach().float().cpu() for k, d in model.weight_decls().items()}
+    weights = {k: d.dest.detach().float().cpu().reshape(d.shape) for k, d in model.weight_decls().items()}
     return model, cache, runner, weights
 
 
@@ -289,10 +289,10 @@ def test_builtin_parts_alone(dtype):
     # feed-forward
     ffn = build_part("feed_forward", PartSpec("swiglu", {"hidden": 200, "intermediate": 136}), rt)
     for d in ffn.weights():
-        d.dest.copy_(torch.randn(d.shape) * 0.1)
+        d.dest.copy_((torch.randn(d.shape) * 0.1).view(d.dest.shape))
     x = (torch.randn(n, 200, device="cuda") * 0.5).to(dtype)
     ws = Workspace(torch.device("cuda"))
     ctx = type("Ctx", (), {"n_tokens": n, "workspace": ws, "split_ok": False})()
     got = ffn.forward(ctx, x).float().cpu()
-    w = {f"m.{d.name}": d.dest.float().cpu() for d in ffn.weights()}
+    w = {f"m.{d.name}": d.dest.float().cpu().reshape(d.shape) for d in ffn.weights()}
     assert torch.allclose(got, plain_qwen2.swiglu(w, "m", x.float().cpu()), **tol)

@@ -48,7 +48,10 @@ def test_load_keeps_matrices_in_run_type_and_vectors_in_fp32(tmp_path):
         v = stored["model.layers.0.self_attn.v_proj.weight"].to(dtype)
         assert torch.equal(attn.w_qkv[-v.shape[0]:], v)
         up = stored["model.layers.0.mlp.up_proj.weight"].to(dtype)
-        assert torch.equal(model.blocks[0].feed_forward.w_gate_up[up.shape[0]:], up)
+        gate = stored["model.layers.0.mlp.gate_proj.weight"].to(dtype)
+        packed = model.blocks[0].feed_forward.w_gate_up          # groups of eight gate rows and their eight up rows
+        assert torch.equal(packed[:8], gate[:8]) and torch.equal(packed[8:16], up[:8])
+        assert torch.equal(packed[-8:], up[-8:]) and torch.equal(packed[-16:-8], gate[-8:])
     tied = tw.load_model(make_folder(tmp_path, "A"), "float32", "cpu")
     assert tied.head.data_ptr() == tied.embedding.data_ptr()
 
