@@ -243,7 +243,8 @@ def e2e_run(model, cfg, batch: int, context: int, steps: int, warmup: int):
 def reference_arm(args) -> int:
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "flow_engine").exists():
-        print(json.dumps({"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}))
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref "
+                          "(pip install --no-index --no-deps --target baseline/_ref <reference>)"}))
         return 0
     try:
         from baseline.run_reference import run
