@@ -615,3 +615,74 @@ TW_EXPORT int tw_attn_prefill(void* out, int out_stride, const void* q, int q_st
         scale * 1.4426950408889634f, skip_single, status);
     return TW_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------------------------------
+// The same decode attention for callers that must not allocate: scratch in the device image.
+// See attention_no_alloc.h for what a caller has to know.
+// ---------------------------------------------------------------------------------------
+#include "attention_no_alloc.h"
+#include <stdio.h>
+
+// Counters first (they must be zero when a launch starts), then the partial results.  In host
+// code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char tw_attn_static_scratch[TW_ATTN_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+unsigned char* g_static_scratch_ptr[kMaxDevices] = {};     // device address of the array, per GPU
+thread_local char g_static_error[256] = "";
+}  // namespace
+
+TW_EXPORT const char* tw_attn_decode_static_last_error(void) { return g_static_error; }
+
+TW_EXPORT int tw_attn_decode_static(void* out, int out_stride, const void* q, int q_stride, const int* seq_q_start,
+                                    const int* seq_q_len, const int* seq_kv_len, const int* seq_slot,
+                                    const int* block_table, int table_stride, const void* k_cache, const void* v_cache,
+                                    int n_seqs, int Hq, int Hkv, int page_size, int num_pages, int window, float scale,
+                                    int nsplit, int* status, cudaStream_t stream) {
+    g_static_error[0] = 0;
+    if (n_seqs <= 0) return 0;
+    if (Hkv <= 0 || Hq % Hkv || nsplit < 1) return (int)cudaErrorInvalidValue;
+    const int G = Hq / Hkv, htiles = (G + 15) / 16;
+    const size_t partial_bytes = sizeof(float) * (size_t)n_seqs * Hq * nsplit * (D + 2);
+    const size_t counter_bytes = sizeof(int) * (size_t)n_seqs * Hkv * htiles;
+    if (counter_bytes > TW_ATTN_STATIC_COUNTER_BYTES ||
+        partial_bytes > TW_ATTN_STATIC_SCRATCH_BYTES - TW_ATTN_STATIC_COUNTER_BYTES) {
+        snprintf(g_static_error, sizeof(g_static_error),
+                 "tw_attn_decode_static: %d requests x %d heads x %d slices need %zu bytes of partial results and "
+                 "%zu bytes of counters; the static array holds %u and %u",
+                 n_seqs, Hq, nsplit, partial_bytes, counter_bytes,
+                 TW_ATTN_STATIC_SCRATCH_BYTES - TW_ATTN_STATIC_COUNTER_BYTES, TW_ATTN_STATIC_COUNTER_BYTES);
+        return TW_ATTN_STATIC_TOO_LARGE;
+    }
+    // set-up, once per GPU, with that GPU current: the device address of the array
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+    if (!g_static_scratch_ptr[device]) {
+        unsigned char* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, tw_attn_static_scratch);
+        if (e != cudaSuccess || !ptr) {
+            snprintf(g_static_error, sizeof(g_static_error),
+                     "tw_attn_decode_static: cudaGetSymbolAddress failed on device %d: %s", device,
+                     cudaGetErrorString(e));
+            return TW_ATTN_STATIC_NO_SYMBOL;
+        }
+        g_static_scratch_ptr[device] = ptr;
+    }
+    unsigned char* base = g_static_scratch_ptr[device];
+    int* counters = reinterpret_cast<int*>(base);
+    float* partial_o = reinterpret_cast<float*>(base + TW_ATTN_STATIC_COUNTER_BYTES);
+    float* partial_ml = partial_o + (size_t)n_seqs * Hq * nsplit * D;
+    if (int a = set_attrs()) return a;
+    // the array keeps what the last call left; only the counters need a defined start
+    e = cudaMemsetAsync(counters, 0, counter_bytes, stream);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid(nsplit * htiles, Hkv, n_seqs);
+    attn_decode_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, stream>>>(
+        (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
+        table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
+        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status);
+    return TW_LAUNCH_CHECK();
+}
