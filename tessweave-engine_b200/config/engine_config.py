@@ -25,6 +25,7 @@ class EngineConfig:
     prefix_cache: bool = True     # share full pages between requests with a common prefix
     max_step_tokens: int = 0      # token budget of a step; 0 = max_active + prefill_chunk
     cuda_graphs: bool = True      # replay captured graphs for decode-only steps
+    lookahead: bool = True        # launch the next step before the current one's tokens have reached the host
 
     def __post_init__(self):
         for key in ("block_size", "kv_blocks", "max_context", "max_active", "max_queue",

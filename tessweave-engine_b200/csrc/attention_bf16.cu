@@ -101,6 +101,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_is_last;
     __shared__ float s_row_max[16];
+    tw_grid_wait();
     const int s = blockIdx.z, kvh = blockIdx.y;
     const int split = blockIdx.x % nsplit, ht = blockIdx.x / nsplit;
     if (seq_q_len[s] != 1) return;
@@ -261,6 +262,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         __syncwarp();
     }
     cp_async_wait<0>();
+    tw_grid_launch_dependents();     // all keys are read: the next kernel may be scheduled
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -382,6 +384,8 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
                     const bf16* __restrict__ v_cache, int Hq, int Hkv, int page_size, int num_pages, int window,
                     float scale_log2e, int skip_single, int* status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    tw_grid_wait();
+    tw_grid_launch_dependents();
     const int s = blockIdx.z, kvh = blockIdx.y;
     const int q_len = seq_q_len[s];
     if (q_len <= 0 || (skip_single && q_len == 1)) return;
@@ -592,7 +596,7 @@ TW_EXPORT int tw_attn_decode(void* out, int out_stride, const void* q, int q_str
     float* partial_o = scratch;
     float* partial_ml = scratch ? scratch + (size_t)n_seqs * Hq * nsplit * D : nullptr;
     dim3 grid(nsplit * htiles, Hkv, n_seqs);
-    attn_decode_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, stream>>>(
+    tw_launch(attn_decode_kernel, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
         (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
         scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status);
@@ -609,7 +613,7 @@ TW_EXPORT int tw_attn_prefill(void* out, int out_stride, const void* q, int q_st
     if (int e = set_attrs()) return e;
     const int G = Hq / Hkv;
     dim3 grid((max_q_len * G + PF_BM - 1) / PF_BM, Hkv, n_seqs);
-    attn_prefill_kernel<<<grid, PF_WARPS * 32, PF_SMEM, stream>>>(
+    tw_launch(attn_prefill_kernel, dim3(grid), dim3(PF_WARPS * 32), PF_SMEM, stream, 1, 
         (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
         scale * 1.4426950408889634f, skip_single, status);
@@ -680,7 +684,7 @@ TW_EXPORT int tw_attn_decode_static(void* out, int out_stride, const void* q, in
     e = cudaMemsetAsync(counters, 0, counter_bytes, stream);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(nsplit * htiles, Hkv, n_seqs);
-    attn_decode_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, stream>>>(
+    tw_launch(attn_decode_kernel, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
         (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
         scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status);

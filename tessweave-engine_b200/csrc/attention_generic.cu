@@ -29,6 +29,8 @@ __global__ void attn_generic_kernel(T* __restrict__ out, int out_stride, const T
                                     int Hq, int Hkv, int D, int page_size, int num_pages, int window, float scale,
                                     int* status) {
     extern __shared__ float smem[];  // TW_ATTN_WARPS * (D + 2)
+    tw_grid_wait();
+    tw_grid_launch_dependents();
     const int n = blockIdx.x, head = blockIdx.y;
     const int s = seq_of_token[n];
     if (s < 0) return;
@@ -114,12 +116,12 @@ TW_EXPORT int tw_attn_generic(void* out, int out_stride, const void* q, int q_st
     dim3 grid(n_tokens, Hq);
     const size_t smem = (size_t)TW_ATTN_WARPS * (D + 2) * sizeof(float);
     if (dtype == TW_F32)
-        attn_generic_kernel<float><<<grid, 32 * TW_ATTN_WARPS, smem, stream>>>(
+        tw_launch(attn_generic_kernel<float>, dim3(grid), dim3(32 * TW_ATTN_WARPS), smem, stream, 1, 
             (float*)out, out_stride, (const float*)q, q_stride, positions, seq_of_token, seq_slot, block_table,
             table_stride, (const float*)k_cache, (const float*)v_cache, Hq, Hkv, D, page_size, num_pages, window, scale,
             status);
     else
-        attn_generic_kernel<__nv_bfloat16><<<grid, 32 * TW_ATTN_WARPS, smem, stream>>>(
+        tw_launch(attn_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(32 * TW_ATTN_WARPS), smem, stream, 1, 
             (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, positions, seq_of_token, seq_slot,
             block_table, table_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, Hq, Hkv, D,
             page_size, num_pages, window, scale, status);

@@ -11,13 +11,19 @@ namespace cg = cooperative_groups;
 
 // ---------------------------------------------------------------------------
 // Embedding: resid[n, :] = float(table[ids[n], :]).  No scaling
-// (reference: flow_engine/model.py:176).
+// (reference: flow_engine/model.py:176).  An id below zero names a token that is still on the
+// device: -(i + 1) stands for device_tokens[i], the i-th token the previous step sampled, so a
+// step can be launched before the host has seen its input tokens.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ table,
-                             const int* __restrict__ ids, int hidden, int vocab, int* status) {
+                             const int* __restrict__ ids, const int* __restrict__ device_tokens, int n_device_tokens,
+                             int hidden, int vocab, int* status) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
     const int n = blockIdx.x;
     int id = ids[n];
+    if (id < 0 && device_tokens && -(id + 1) < n_device_tokens) id = device_tokens[-(id + 1)];
     if (id < 0 || id >= vocab) {
         if (threadIdx.x == 0) atomicOr(status, TW_ERR_TOKEN_ID);
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) resid[(size_t)n * hidden + i] = 0.f;
@@ -28,14 +34,14 @@ __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ ta
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = tw_to_float(row[i]);
 }
 
-TW_EXPORT int tw_embed(void* resid, const void* table, const int* ids, int n_tokens, int hidden, int vocab,
-                       int dtype, int* status, cudaStream_t stream) {
+TW_EXPORT int tw_embed(void* resid, const void* table, const int* ids, const int* device_tokens, int n_device_tokens,
+                       int n_tokens, int hidden, int vocab, int dtype, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dtype == TW_F32)
-        embed_kernel<float><<<n_tokens, 256, 0, stream>>>((float*)resid, (const float*)table, ids, hidden, vocab, status);
+        tw_launch(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, 1, (float*)resid, (const float*)table, ids, device_tokens, n_device_tokens, hidden, vocab, status);
     else
-        embed_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>((float*)resid, (const __nv_bfloat16*)table, ids,
-                                                                   hidden, vocab, status);
+        tw_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, 1, (float*)resid, (const __nv_bfloat16*)table, ids,
+                                                                   device_tokens, n_device_tokens, hidden, vocab, status);
     return TW_LAUNCH_CHECK();
 }
 
@@ -63,6 +69,8 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __re
                    const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
+    tw_grid_wait();
+    tw_grid_launch_dependents();
     const int src = rows ? rows[r] : r;
     float* x = resid + (size_t)src * hidden;
     const T* d = delta ? delta + (size_t)src * hidden : nullptr;
@@ -136,6 +144,8 @@ add_rmsnorm_cluster_kernel(T* __restrict__ out, float* __restrict__ resid, const
                            const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
     __shared__ float scratch[33];
     __shared__ float my_ss;
+    tw_grid_wait();
+    tw_grid_launch_dependents();
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int r = blockIdx.x / TW_NORM_CLUSTER;
@@ -194,27 +204,14 @@ static int launch_add_rmsnorm(T* out, float* resid, const T* delta, const float*
                               size_t split_stride, const float* weight, float eps, int n_rows, int hidden,
                               const int* rows, cudaStream_t stream) {
     if (n_rows <= 64 && hidden >= 1024 && hidden <= TW_NORM_CLUSTER * TW_NORM_CTHREADS * TW_NORM_CMAXV) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(n_rows * TW_NORM_CLUSTER);
-        cfg.blockDim = dim3(TW_NORM_CTHREADS);
-        cfg.dynamicSmemBytes = 0;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = TW_NORM_CLUSTER;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, add_rmsnorm_cluster_kernel<T>, out, resid, delta, partial, nsplit,
-                                           split_stride, weight, eps, hidden, rows);
-        return e != cudaSuccess ? (int)e : TW_LAUNCH_CHECK();
+        return tw_launch(add_rmsnorm_cluster_kernel<T>, dim3(n_rows * TW_NORM_CLUSTER), dim3(TW_NORM_CTHREADS), 0, stream,
+                         TW_NORM_CLUSTER, out, resid, delta, partial, nsplit, split_stride, weight, eps, hidden, rows);
     }
     if (hidden <= TW_NORM_THREADS * TW_NORM_MAXV)
-        add_rmsnorm_kernel<T, true><<<n_rows, TW_NORM_THREADS, 0, stream>>>(out, resid, delta, partial, nsplit,
+        tw_launch(add_rmsnorm_kernel<T, true>, dim3(n_rows), dim3(TW_NORM_THREADS), 0, stream, 1, out, resid, delta, partial, nsplit,
                                                                             split_stride, weight, eps, hidden, rows);
     else
-        add_rmsnorm_kernel<T, false><<<n_rows, TW_NORM_THREADS, 0, stream>>>(out, resid, delta, partial, nsplit,
+        tw_launch(add_rmsnorm_kernel<T, false>, dim3(n_rows), dim3(TW_NORM_THREADS), 0, stream, 1, out, resid, delta, partial, nsplit,
                                                                              split_stride, weight, eps, hidden, rows);
     return TW_LAUNCH_CHECK();
 }
@@ -256,6 +253,8 @@ rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const float* __restric
                      const int* __restrict__ block_table, int table_stride, const float* __restrict__ inv_freq,
                      T* __restrict__ k_cache, T* __restrict__ v_cache, int Hq, int Hkv, int D, int page_size,
                      int num_pages, int write_cache, int* status) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
     const int n = blockIdx.x;
     const int s = seq_of_token[n];
     if (s < 0) return;  // padding row of a fixed-size batch
@@ -337,12 +336,12 @@ TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, 
     const dim3 grid(n_tokens, (work + TW_ROPE_THREADS - 1) / TW_ROPE_THREADS);
     const int threads = TW_ROPE_THREADS;
     if (dtype == TW_F32)
-        rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(
+        tw_launch(rope_kv_write_kernel<float>, dim3(grid), dim3(threads), 0, stream, 1, 
             (float*)qkv, qkv_stride, partial, nsplit, (size_t)split_stride, bias, positions, seq_of_token, seq_slot,
             block_table, table_stride, inv_freq,
             (float*)k_cache, (float*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache, status);
     else
-        rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+        tw_launch(rope_kv_write_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, 1, 
             (__nv_bfloat16*)qkv, qkv_stride, partial, nsplit, (size_t)split_stride, bias, positions, seq_of_token,
             seq_slot, block_table, table_stride, inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache,
             status);
@@ -359,6 +358,8 @@ TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, 
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, long total,
                                 int interleaved) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
     long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     const long step = (long)gridDim.x * blockDim.x;
     for (; idx < total; idx += step) {
@@ -373,17 +374,52 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_
     }
 }
 
+// bf16 with the intermediate size a multiple of 8: a thread handles 8 outputs with 16-byte accesses.
+__global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate_up,
+                                       int inter, long total8, int interleaved) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long step = (long)gridDim.x * blockDim.x;
+    const int groups = inter >> 3;
+    for (; idx < total8; idx += step) {
+        const long n = idx / groups;
+        const int j = (int)(idx - n * groups);
+        const __nv_bfloat16* row = gate_up + n * 2 * (long)inter;
+        const uint4 gv = *reinterpret_cast<const uint4*>(row + (interleaved ? j * 16 : j * 8));
+        const uint4 uv = *reinterpret_cast<const uint4*>(row + (interleaved ? j * 16 + 8 : inter + j * 8));
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        uint4 ov;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
+            o2[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+        }
+        *reinterpret_cast<uint4*>(out + n * (long)inter + j * 8) = ov;
+    }
+}
+
 TW_EXPORT int tw_silu_mul(void* out, const void* gate_up, int n_rows, int inter, int interleaved, int dtype,
                           cudaStream_t stream) {
     const long total = (long)n_rows * inter;
     if (total <= 0) return 0;
     long blocks = (total + 255) / 256;
     if (blocks > 148L * 16) blocks = 148L * 16;
+    if (dtype == TW_BF16 && (inter & 7) == 0) {
+        const long total8 = total >> 3;
+        long b8 = (total8 + 255) / 256;
+        if (b8 > 148L * 16) b8 = 148L * 16;
+        tw_launch(silu_mul_bf16x8_kernel, dim3((int)b8), dim3(256), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter,
+                                                            total8, interleaved);
+        return TW_LAUNCH_CHECK();
+    }
     if (dtype == TW_F32)
-        silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)out, (const float*)gate_up, inter, total,
+        tw_launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, 1, (float*)out, (const float*)gate_up, inter, total,
                                                                 interleaved);
     else
-        silu_mul_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)out,
+        tw_launch(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, 1, (__nv_bfloat16*)out,
                                                                         (const __nv_bfloat16*)gate_up, inter, total,
                                                                         interleaved);
     return TW_LAUNCH_CHECK();

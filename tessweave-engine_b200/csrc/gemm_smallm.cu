@@ -52,6 +52,7 @@ template <int NT>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M, int N, int K, int kper,
                    void* __restrict__ out, int out_mode, int out_stride) {
+    tw_grid_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int r0 = blockIdx.x * ROWS_PER_BLOCK + warp * 16;
@@ -106,6 +107,7 @@ gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M
         a_cur = a_nxt; b_cur = b_nxt;
         a_nxt = a_far; b_nxt = b_far;
     }
+    tw_grid_launch_dependents();     // the stream of weights is over: the next kernel may be scheduled
     // acc[t][0..1]: weight row ra, tokens t*8 + 2c, +1;  acc[t][2..3]: weight row rb
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
@@ -138,6 +140,8 @@ gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M
 // Sum of the slices into a dense result (for consumers that cannot add slices themselves).
 template <typename T>
 __global__ void reduce_partial_kernel(T* __restrict__ out, const float* __restrict__ partial, int nsplit, long total) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     float s = 0.f;
@@ -161,13 +165,13 @@ TW_EXPORT int tw_gemm_smallm(const void* w, const void* x, int M, int N, int K, 
     const bf16* wp = (const bf16*)w;
     const bf16* xp = (const bf16*)x;
     if (M <= 8)
-        gemm_smallm_kernel<1><<<grid, WARPS * 32, 0, stream>>>(wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
     else if (M <= 16)
-        gemm_smallm_kernel<2><<<grid, WARPS * 32, 0, stream>>>(wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<2>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
     else if (M <= 32)
-        gemm_smallm_kernel<4><<<grid, WARPS * 32, 0, stream>>>(wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<4>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
     else
-        gemm_smallm_kernel<8><<<grid, WARPS * 32, 0, stream>>>(wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<8>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
     return TW_LAUNCH_CHECK();
 }
 
@@ -175,8 +179,8 @@ TW_EXPORT int tw_reduce_partial(void* out, const float* partial, int nsplit, lon
     if (total <= 0) return 0;
     const int blocks = (int)((total + 255) / 256);
     if (dtype == TW_F32)
-        reduce_partial_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, partial, nsplit, total);
+        tw_launch(reduce_partial_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, (float*)out, partial, nsplit, total);
     else
-        reduce_partial_kernel<bf16><<<blocks, 256, 0, stream>>>((bf16*)out, partial, nsplit, total);
+        tw_launch(reduce_partial_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1, (bf16*)out, partial, nsplit, total);
     return TW_LAUNCH_CHECK();
 }

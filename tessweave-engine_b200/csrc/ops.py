@@ -90,14 +90,18 @@ def _fn(lib_name: str, fn_name: str, defines=None):
 
 
 # ---------------------------------------------------------------------------
-def embed(resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, n_tokens: int, status: torch.Tensor) -> None:
-    """resid[n] = float(table[ids[n]]); resid is fp32 [>=n_tokens, hidden]."""
-    _cuda(resid, table, ids, status)
+def embed(resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, n_tokens: int, status: torch.Tensor,
+          device_tokens: torch.Tensor | None = None) -> None:
+    """resid[n] = float(table[ids[n]]); resid is fp32 [>=n_tokens, hidden].  An id -(i + 1) is
+    replaced by ``device_tokens[i]`` (int32, on the device) inside the kernel."""
+    _cuda(resid, table, ids, status, device_tokens)
+    _need(device_tokens is None or device_tokens.dtype == torch.int32, "embed: device tokens must be int32")
     _need(resid.dtype == torch.float32 and resid.is_contiguous(), "embed: residual stream must be contiguous fp32")
     _need(table.is_contiguous() and ids.dtype == torch.int32, "embed: table contiguous, ids int32")
     _need(resid.shape[0] >= n_tokens and ids.numel() >= n_tokens and resid.shape[1] == table.shape[1],
           "embed: shapes disagree")
-    code = _fn("elementwise", "tw_embed")(_ptr(resid), _ptr(table), _ptr(ids), c_int(n_tokens),
+    code = _fn("elementwise", "tw_embed")(_ptr(resid), _ptr(table), _ptr(ids), _ptr(device_tokens),
+                                          c_int(0 if device_tokens is None else device_tokens.numel()), c_int(n_tokens),
                                           c_int(table.shape[1]), c_int(table.shape[0]),
                                           c_int(dtype_code(table.dtype)), _ptr(status), _stream())
     _check(code, "embed")

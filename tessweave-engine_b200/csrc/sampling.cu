@@ -32,6 +32,8 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
     __shared__ float swarp[32];
     __shared__ float sbcast[2];
     __shared__ int sbest;
+    tw_grid_wait();
+    tw_grid_launch_dependents();
     const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* x = logits + (size_t)r * vocab;
     const int chunk = (vocab + TW_SAMPLE_THREADS - 1) / TW_SAMPLE_THREADS;
@@ -115,7 +117,7 @@ TW_EXPORT int tw_sample(int* out, const float* logits, int n_rows, int vocab, co
                         const long long* seed, const long long* counter, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (vocab <= 0) return (int)cudaErrorInvalidValue;
-    sample_kernel<<<n_rows, TW_SAMPLE_THREADS, 0, stream>>>(out, logits, vocab, temperature, seed, counter);
+    tw_launch(sample_kernel, dim3(n_rows), dim3(TW_SAMPLE_THREADS), 0, stream, 1, out, logits, vocab, temperature, seed, counter);
     return TW_LAUNCH_CHECK();
 }
 

@@ -78,6 +78,8 @@ class ModelRunner:
         self._d = {k: self._dev[o:o + sz] for k, (o, sz) in self._offsets.items()}
         self.sampled = torch.zeros(m + 1, dtype=torch.int32, device=self.device)   # ids, then the status word
         self._sampled_host = torch.zeros(m + 1, dtype=torch.int32, pin_memory=True)
+        self._sampled_hosts = [torch.zeros(m + 1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._launched = 0
         self._staged = torch.cuda.Event()
         self._staged.record()
         self.use_graphs = bool(cuda_graphs and model.graph_safe)
@@ -148,7 +150,8 @@ class ModelRunner:
             seq_q_start=d["seq_q_start"][:seqs_total], seq_q_len=d["seq_q_len"][:seqs_total],
             seq_kv_len=d["seq_kv_len"][:seqs_total], status=self.status,
             host_slot=slot, host_q_start=qs, host_q_len=ql, host_kv_len=kl,
-            max_q_len=max(ql), max_kv_len=max(kl), decode_only=all(t == 1 for t in ql), fixed_shape=bool(pad_to))
+            max_q_len=max(ql), max_kv_len=max(kl), decode_only=all(t == 1 for t in ql), fixed_shape=bool(pad_to),
+            device_tokens=self.sampled)
         return ctx, m
 
     def _padding_context(self, rows: int, logit_rows: int) -> StepContext:
@@ -172,7 +175,7 @@ class ModelRunner:
             seq_kv_len=d["seq_kv_len"][:seqs], status=self.status, host_slot=[0] * seqs, host_q_start=[0] * seqs,
             host_q_len=[0] * seqs, host_kv_len=[0] * seqs, max_q_len=1,
             max_kv_len=self.cache.max_blocks * self.cache.page_size, decode_only=(rows <= self.max_seqs),
-            fixed_shape=True)
+            fixed_shape=True, device_tokens=self.sampled)
 
     # ------------------------------------------------------------------ the step
     @torch.inference_mode()
@@ -263,6 +266,38 @@ class ModelRunner:
         self._sampled_host[:m + 1].copy_(self.sampled[:m + 1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         out = self._sampled_host[:m + 1].tolist()
+        self._raise_on_status(out[m])
+        return out[:m]
+
+    # ------------------------------------------------------------------ steps in flight
+    @torch.inference_mode()
+    def launch(self, entries: list[StepEntry], temperature: list[float], seed: list[int], counter: list[int]):
+        """Launch a whole step -- forward, token selection, copy of the chosen ids to the host --
+        and return without waiting.  A token id -(i + 1) in an entry stands for the i-th token
+        chosen by the step launched just before, which is still on the device; so the next
+        step can be launched before this one's tokens have reached the host.  ``finish`` waits."""
+        self.stage_sampling(temperature, seed, counter)
+        logits = self.step(entries)
+        m = logits.shape[0]
+        host = self._sampled_hosts[self._launched % 2]
+        self._launched += 1
+        if m:
+            if all(t == 0 for t in temperature):
+                ops.sample(self.sampled, logits, m)
+            else:
+                ops.sample(self.sampled, logits, m, self._d["temperature"].view(torch.float32),
+                           self._d["seed"].view(torch.int64), self._d["counter"].view(torch.int64))
+        self.sampled[m:m + 1].copy_(self.status)
+        host[:m + 1].copy_(self.sampled[:m + 1], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return (done, host, m)
+
+    def finish(self, pending) -> list[int]:
+        """Wait for a launched step; its chosen token ids, in the order of the wanted rows."""
+        done, host, m = pending
+        done.synchronize()
+        out = host[:m + 1].tolist()
         self._raise_on_status(out[m])
         return out[:m]
 

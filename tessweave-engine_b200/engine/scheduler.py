@@ -55,6 +55,19 @@ class Request:
     events: queue.Queue = field(default_factory=lambda: queue.Queue(maxsize=256))
 
 
+@dataclass
+class Flight:
+    """A step that has been handed to the GPU."""
+    plan: list                                   # (request, tokens it brings)
+    rows: dict                                   # request id -> tokens it brings
+    sampling: list                               # requests whose last row is sampled, in row order
+    sampled_index: dict                          # request id -> its place among the sampled rows
+    started: float
+    pending: object = None                       # the runner's handle, or None when the step ran synchronously
+    tokens: list = field(default_factory=list)   # chosen tokens of a synchronous step
+    deferred: list = field(default_factory=list)  # leases of requests that ended while this step ran
+
+
 class Engine:
     """One model worker owns every change to the cache; callers never run kernels."""
 
@@ -80,6 +93,9 @@ class Engine:
         self.running = False
         self.thread = None
         self.fatal = None
+        self.inflight: Flight | None = None
+        # run one step ahead: the next step is launched before the current one's tokens are on the host
+        self.lookahead = bool(cfg.lookahead and hasattr(self.runner, "launch"))
         self.prefill_cursor = 0
         self.chunk = cfg.prefill_chunk
         self.prefill_ms_per_token = None
@@ -152,7 +168,10 @@ class Engine:
         elif r in self.waiting:
             self.waiting.remove(r)
         if r.lease is not None:
-            self.cache.release(r.lease)
+            if self.inflight is not None and r.id in self.inflight.rows:
+                self.inflight.deferred.append(r.lease)    # a running step still writes this request's pages
+            else:
+                self.cache.release(r.lease)
             r.lease = None
         r.status = reason
         del self.requests[r.id]
@@ -192,21 +211,30 @@ class Engine:
         return True
 
     # ------------------------------------------------------------------ one turn
-    def plan(self) -> list[tuple[Request, int]]:
+    def plan(self, flight: "Flight | None" = None) -> list[tuple[Request, int]]:
         """Which requests bring how many tokens to the next step: every decoding request one
-        token first, then prompt portions in round-robin order while the token budget lasts."""
+        token first, then prompt portions in round-robin order while the token budget lasts.
+
+        With ``flight`` (a step that is still running) the plan is made for the step after it:
+        positions count from where that step will have left each request, a request whose token
+        that step is choosing brings it by reference (it is still on the device), and a request
+        that the step will finish by its length budget brings nothing."""
+        ahead = flight.rows if flight else {}
         budget = self.config.step_token_budget
         plan: list[tuple[Request, int]] = []
         for r in self.active:
-            if r.computed >= len(r.prompt) and budget > 0:
+            done = r.computed + ahead.get(r.id, 0)
+            if done >= len(r.prompt) and budget > 0:
+                if flight and r.id in flight.sampled_index and len(r.output) + 1 >= r.max_tokens:
+                    continue
                 plan.append((r, 1))
                 budget -= 1
-        prefill = [r for r in self.active if r.computed < len(r.prompt)]
+        prefill = [r for r in self.active if r.computed + ahead.get(r.id, 0) < len(r.prompt)]
         if prefill:
             start = self.prefill_cursor % len(prefill)
             self.prefill_cursor += 1
             for r in prefill[start:] + prefill[:start]:
-                count = min(self.chunk, len(r.prompt) - r.computed, budget)
+                count = min(self.chunk, len(r.prompt) - r.computed - ahead.get(r.id, 0), budget)
                 if count <= 0:
                     break
                 plan.append((r, count))
@@ -222,47 +250,90 @@ class Engine:
                 self._fail(exc)
                 raise
 
-    @torch.inference_mode()
-    def _step(self) -> bool:
-        self._admit()
-        if not self.active:
-            return False
-        plan = self.plan()
-        started = time.perf_counter()
-        entries, sampling = [], []
+    def _launch(self, plan: list[tuple[Request, int]], after: "Flight | None") -> "Flight":
+        """Hand one step to the runner without waiting for it."""
+        ahead = after.rows if after else {}
+        entries, sampling, temps, seeds, counters = [], [], [], [], []
         for r, count in plan:
-            self.cache.ensure(r.lease, r.computed + count)
-            finishes_prompt = r.computed + count >= len(r.prompt)
-            entries.append(StepEntry(r.lease.slot, r.tokens[r.computed:r.computed + count], r.computed,
-                                     [count - 1] if finishes_prompt else []))
+            start = r.computed + ahead.get(r.id, 0)
+            self.cache.ensure(r.lease, start + count)
+            if start >= len(r.tokens):
+                # the token this row feeds is being chosen by the step in flight: name it by its place there
+                tokens = [-(after.sampled_index[r.id] + 1)]
+                drawn = len(r.output) + 1
+            else:
+                tokens = r.tokens[start:start + count]
+                drawn = len(r.output)
+            finishes_prompt = start + count >= len(r.prompt)
+            entries.append(StepEntry(r.lease.slot, tokens, start, [count - 1] if finishes_prompt else []))
             if finishes_prompt:
                 sampling.append(r)
-        self.runner.stage_sampling([r.temperature for r in sampling], [r.seed for r in sampling],
-                                   [len(r.output) for r in sampling])
-        logits = self.runner.step(entries)
-        if sampling:
-            chosen = self.runner.sample(logits, greedy_only=all(r.temperature == 0 for r in sampling))
-        else:
-            chosen = []
-            if self.config.adaptive_chunk:
-                torch.cuda.current_stream().synchronize()
-        elapsed = (time.perf_counter() - started) * 1000
+                temps.append(r.temperature); seeds.append(r.seed); counters.append(drawn)
+        flight = Flight(plan=plan, rows={r.id: c for r, c in plan}, sampling=sampling,
+                        sampled_index={r.id: i for i, r in enumerate(sampling)}, started=time.perf_counter())
+        if hasattr(self.runner, "launch"):
+            flight.pending = self.runner.launch(entries, temps, seeds, counters)
+        else:       # a stand-in runner without asynchronous steps
+            self.runner.stage_sampling(temps, seeds, counters)
+            logits = self.runner.step(entries)
+            flight.tokens = self.runner.sample(logits, greedy_only=all(t == 0 for t in temps)) if sampling else []
+        return flight
+
+    def _complete(self, flight: "Flight") -> None:
+        """Wait for a step, move its requests on, commit its tokens, give back what was held for it."""
+        try:
+            chosen = flight.tokens if flight.pending is None else self.runner.finish(flight.pending)
+        finally:
+            for lease in flight.deferred:
+                self.cache.release(lease)
+            flight.deferred = []
+        elapsed = (time.perf_counter() - flight.started) * 1000
         self.counters["steps"] += 1
         prefill_tokens = 0
-        for r, count in plan:
+        for r, count in flight.plan:
+            if r.id not in self.requests:
+                continue                     # finished or cancelled while the step ran; its row is dropped
             if r.computed < len(r.prompt):
                 prefill_tokens += count
             r.computed += count
             self.cache.advance(r.lease, r.tokens, r.computed)
         self.counters["prefill_tokens"] += prefill_tokens
-        for r, token in zip(sampling, chosen):
-            self._commit(r, int(token))
+        for r, token in zip(flight.sampling, chosen):
+            if r.id in self.requests:
+                self._commit(r, int(token))
         if prefill_tokens and self.config.adaptive_chunk:
-            self._adapt_chunk(elapsed, prefill_tokens, len(plan) - sum(1 for _, c in plan if c > 1))
-        self.trace.emit("step", phase="mixed", request_ids=[r.id for r, _ in plan], batch=len(plan),
-                        tokens=sum(c for _, c in plan), prefill_tokens=prefill_tokens, elapsed_ms=elapsed,
+            self._adapt_chunk(elapsed, prefill_tokens, sum(1 for _, c in flight.plan if c == 1))
+        self.trace.emit("step", phase="mixed", request_ids=[r.id for r, _ in flight.plan], batch=len(flight.plan),
+                        tokens=sum(c for _, c in flight.plan), prefill_tokens=prefill_tokens, elapsed_ms=elapsed,
                         prefill_chunk=self.chunk, **self.cache.stats())
+
+    @torch.inference_mode()
+    def _step(self) -> bool:
+        self._admit()
+        if self.inflight is None:
+            if not self.active:
+                return False
+            self.inflight = self._launch(self.plan(), None)
+        current, self.inflight = self.inflight, None
+        if self.lookahead and self.active:
+            ahead = self.plan(current)
+            if ahead:
+                # the step after `current` starts on the device before `current`'s tokens are on the host
+                self.inflight = self._launch(ahead, current)
+        self._complete(current)
         return True
+
+    def _drain(self) -> None:
+        """Wait for a step that is still running; its results are dropped."""
+        flight, self.inflight = self.inflight, None
+        if flight is not None:
+            try:
+                if flight.pending is not None:
+                    self.runner.finish(flight.pending)
+            finally:
+                for lease in flight.deferred:
+                    self.cache.release(lease)
+                flight.deferred = []
 
     def _adapt_chunk(self, elapsed_ms: float, prefill_tokens: int, decode_rows: int) -> None:
         """The reference's feedback controller (engine.py:261-268): an EMA of milliseconds per
@@ -278,6 +349,10 @@ class Engine:
         """A failed step ends every request with an error and gives all pages back (engine.py:283-289)."""
         self.fatal = f"{type(exc).__name__}: {exc}"
         self.trace.emit("fatal", error=self.fatal)
+        try:
+            self._drain()
+        except Exception:       # noqa: BLE001  (the first failure is the one reported)
+            pass
         for r in list(self.requests.values()):
             self._finish(r, "error", self.fatal)
         self.running = False
@@ -306,6 +381,7 @@ class Engine:
             self.thread.join()           # never free storage while kernels are in flight
             self.thread = None
         with self.lock:
+            self._drain()
             for r in list(self.requests.values()):
                 self._finish(r, "cancelled")
             self.cache.clear_prefixes()

@@ -85,7 +85,7 @@ class Model:
             raise RuntimeError("the model has no weights yet: load them or write random ones first")
         spec, n = self.spec, ctx.n_tokens
         resid = ctx.workspace.get("model.resid", (n, spec.hidden_size), torch.float32)
-        ops.embed(resid, self.embedding, ctx.token_ids, n, ctx.status)
+        ops.embed(resid, self.embedding, ctx.token_ids, n, ctx.status, ctx.device_tokens)
         stream = ResidualStream(resid)
         for i, entry in enumerate(spec.schedule):
             block = self.blocks[entry.layer]

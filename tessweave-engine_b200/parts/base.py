@@ -158,6 +158,7 @@ class StepContext:
     max_kv_len: int = 1
     decode_only: bool = False      # every sequence brings exactly one token
     fixed_shape: bool = False      # the launch is being captured: sizes must not depend on host values of this step
+    device_tokens: torch.Tensor | None = None   # int32: token ids the previous step left on the device (id -(i+1) -> [i])
     split_ok: bool = False         # the consumer of the running sub-layer's output adds split-product slices itself
 
 

@@ -203,3 +203,95 @@ def test_worker_thread_delivers_events(model):
     e.close()
     assert [ev["type"] for ev in events] == ["token"] * 3 + ["done"]
     assert events[-1]["usage"] == {"prompt_tokens": 3, "completion_tokens": 3, "total_tokens": 6}
+
+
+class ResolvingRunner(FakeRunner):
+    def __init__(self, vocab):
+        super().__init__(vocab)
+        self.queue = []          # launched, unfinished steps in order
+        self.results = {}        # launch number -> tokens
+        self.count = 0
+        self.max_in_flight = 0
+
+    def launch(self, entries, temperature, seed, counter):
+        if self.fail_next:
+            raise RuntimeError("injected failure")
+        self.count += 1
+        self.queue.append((self.count, entries))
+        self.max_in_flight = max(self.max_in_flight, len(self.queue))
+        return self.count
+
+    def _run(self, number, entries):
+        prev = self.results.get(number - 1, [])
+        rows, out = [], []
+        for e in entries:
+            toks = [prev[-(t + 1)] if t < 0 else t for t in e.tokens]
+            rows.append((e.slot, toks, e.start, list(e.want)))
+            out += [(toks[w] + e.start + w) % self.vocab for w in e.want]
+        self.steps.append(rows)
+        self.results[number] = out
+
+    def finish(self, pending):
+        while self.queue and self.queue[0][0] <= pending:
+            number, entries = self.queue.pop(0)
+            self._run(number, entries)
+        return self.results[pending]
+
+
+def lookahead_engine(model, lookahead, **kw):
+    defaults = dict(block_size=4, kv_blocks=64, max_context=64, prefill_chunk=4, min_prefill_chunk=1, max_active=4,
+                    lookahead=lookahead)
+    defaults.update(kw)
+    runner = ResolvingRunner(model.spec.vocab_size)
+    return Engine(model, EngineConfig(**defaults), runner=runner), runner
+
+
+def test_lookahead_gives_the_same_tokens_and_keeps_two_steps_in_flight(model):
+    prompts = [[1, 2, 3, 4, 5, 6, 7], [9], [20, 21, 22], [30, 31, 32, 33, 34, 35, 36, 37, 38, 39, 40]]
+    outs = {}
+    for look in (False, True):
+        e, runner = lookahead_engine(model, look)
+        reqs = [e.submit(p, max_tokens=5 + i, ignore_eos=True) for i, p in enumerate(prompts)]
+        drain(e)
+        outs[look] = [r.output for r in reqs]
+        assert runner.max_in_flight == (2 if look else 1)
+        e.cache.check_invariants()
+        e.close()
+        assert e.stats()["free_blocks"] == 64 and not e.cache.leases
+    assert outs[True] == outs[False]
+    assert all(len(o) == 5 + i for i, o in enumerate(outs[True]))
+
+
+def test_lookahead_request_that_stops_keeps_its_pages_until_the_running_step_is_done(model):
+    e, runner = lookahead_engine(model, True, prefix_cache=False)
+    eos = model.spec.eos_token_ids[0]
+    a = e.submit([eos - 1], max_tokens=10)              # second token is the stop token
+    b = e.submit([5, 6], max_tokens=6, ignore_eos=True)
+    e.step()            # prompts (and the step after them is launched)
+    e.step()            # a's second token arrives: a stops while the step after is running
+    assert a.status == "stop" and a.output == [eos - 1, eos]
+    assert e.inflight is not None and len(e.inflight.deferred) == 1       # a's pages are still held
+    assert len(e.cache.leases) == 2
+    e.step()
+    assert len(e.cache.leases) == 1                                        # given back once that step ended
+    drain(e)
+    assert len(b.output) == 6
+    e.close()
+    e.cache.check_invariants()
+    assert e.stats()["free_blocks"] == 64
+
+
+def test_lookahead_cancel_and_failure_leave_nothing_behind(model):
+    e, runner = lookahead_engine(model, True)
+    a = e.submit([1, 2, 3], max_tokens=20, ignore_eos=True)
+    b = e.submit([4, 5, 6], max_tokens=20, ignore_eos=True)
+    e.step(); e.step()
+    e.cancel(a.id)
+    assert a.status == "cancelled" and e.inflight.deferred
+    e.step()
+    runner.fail_next = True
+    with pytest.raises(RuntimeError, match="injected"):
+        e.step()
+    assert b.status == "error" and e.inflight is None
+    e.cache.check_invariants()
+    assert not e.cache.leases and e.stats()["free_blocks"] + e.stats()["cached_prefix_blocks"] == 64
