@@ -3,7 +3,7 @@
 //
 // Two kernels share the tile machinery:
 //   * decode:  requests that bring ONE token.  A block serves one (request, key/value head,
-//     slice of the keys); all query heads of the group are the rows of one MMA tile, so keys
+//     slice of the keys); the query heads of the group are the columns of one MMA tile, so keys
 //     and values are read once for the whole group.  The keys are split over blocks
 //     ("split-KV"); partial results (fp32 accumulator, running maximum, sum) go to scratch
 //     memory, and the block that finishes last merges them in slice order.
@@ -81,16 +81,46 @@ __device__ __forceinline__ long long key_offset(int p, int limit, const int* tab
 // ---------------------------------------------------------------------------------------
 // decode
 // ---------------------------------------------------------------------------------------
+// A warp works on 16 keys at a time with the roles of the MMA operands swapped against the
+// prefill kernel: S^T[key, head] = K[key, :] . Q^T, so the (at most 8) query heads of a tile are
+// the 8 columns of mma.m16n8k16 and nothing is padded to 16 rows; O^T[d, head] += V^T P^T.
+// K goes straight from global memory into A fragments, one tile ahead (the order of d inside a
+// dot product does not matter, so a thread reads 16 contiguous bytes of its two key rows per 32
+// values of d and q is read with the same permutation); V goes through shared memory, three
+// tiles deep, because the product needs it transposed (ldmatrix.trans).  P^T is obtained from the
+// S^T fragments with movmatrix.
 constexpr int DEC_WARPS = 4;
-constexpr int DEC_TILE = 64;                                  // keys per block and iteration (16 per warp)
-constexpr int DEC_STAGES = 3;                                 // tiles of a warp in shared memory (2 in flight)
-constexpr int DEC_STAGE = 2 * 16 * DP;                        // elements of one warp stage: K then V
-constexpr int DEC_PAGE_CACHE = 1024;                          // block-table entries kept in shared memory
+constexpr int DEC_TILE = DEC_WARPS * 16;                      // keys per block and iteration
+constexpr int DEC_HEADS = 8;                                  // query heads per block (columns of the MMA)
+constexpr int DEC_STAGES = 3;                                 // V tiles of a warp in shared memory (2 in flight)
+constexpr int DEC_STAGE = 16 * DP;                            // elements of one warp stage of V
+constexpr int DEC_PAGE_CACHE = 256;                           // block-table entries kept in shared memory
 constexpr int DEC_SMEM_STAGES = DEC_WARPS * DEC_STAGES * DEC_STAGE * 2;
 constexpr int DEC_SMEM_OFFS = DEC_WARPS * DEC_STAGES * 16 * 8;  // row offsets of the tiles in flight
 constexpr int DEC_SMEM = DEC_SMEM_STAGES + DEC_SMEM_OFFS + DEC_PAGE_CACHE * 4;
+constexpr int DB32 = D / 32;                                  // whole 32-wide blocks of d
+constexpr bool DTAIL16 = (D % 32) != 0;                       // plus one 16-wide block
+constexpr int MT_O = D / 16;                                  // m-tiles of O^T
 
-__global__ void __launch_bounds__(DEC_WARPS * 32)
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
+}
+__device__ __forceinline__ void mma_bf16_regs(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct KFrag {                    // the d values of one key row this thread feeds to the MMAs
+    uint4 blk[DB32 > 0 ? DB32 : 1];
+    uint2 tail;
+};
+
+__global__ void __launch_bounds__(DEC_WARPS * 32, (D <= 128 ? 4 : 2))
 attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
                    const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                    const int* __restrict__ seq_kv_len, const int* __restrict__ seq_slot,
@@ -100,13 +130,13 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
                    int* __restrict__ counters, int* status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_is_last;
-    __shared__ float s_row_max[16];
+    __shared__ float s_row_max[DEC_HEADS];
     tw_grid_wait();
     const int s = blockIdx.z, kvh = blockIdx.y;
     const int split = blockIdx.x % nsplit, ht = blockIdx.x / nsplit;
     if (seq_q_len[s] != 1) return;
-    const int G = Hq / Hkv, h0 = ht * 16;
-    const int nheads = min(16, G - h0);
+    const int G = Hq / Hkv, h0 = ht * DEC_HEADS;
+    const int nheads = min(DEC_HEADS, G - h0);
     const int n = seq_q_start[s];
     const int pos = seq_kv_len[s] - 1;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -132,31 +162,26 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
     }
     __syncthreads();
 
-    // query fragments: rows g and g + 8 are heads h0 + g and h0 + g + 8 of this group
-    uint32_t qf[KSTEPS][4];
+    // q as the B operand: head h0 + g, with the same order of d as the key fragments
+    KFrag qf;
     {
-        const bf16* q0 = q + (size_t)n * q_stride + (size_t)(kvh * G + h0 + g) * D;
-        const bf16* q1 = q0 + 8 * D;
-        const bool v0 = g < nheads, v1 = g + 8 < nheads;
+        const bool valid = g < nheads;
+        const bf16* qrow = q + (size_t)n * q_stride + (size_t)(kvh * G + h0 + (valid ? g : 0)) * D;
 #pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-            const int d = ks * 16 + 2 * c;
-            qf[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
-            qf[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
-            qf[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
-            qf[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
-        }
+        for (int jb = 0; jb < DB32; ++jb)
+            qf.blk[jb] = valid ? *reinterpret_cast<const uint4*>(qrow + 32 * jb + 8 * c) : make_uint4(0u, 0u, 0u, 0u);
+        qf.tail = (DTAIL16 && valid) ? *reinterpret_cast<const uint2*>(qrow + 32 * DB32 + 4 * c) : make_uint2(0u, 0u);
     }
 
-    float oacc[NT_O][4];
+    float oacc[MT_O][4];
 #pragma unroll
-    for (int i = 0; i < NT_O; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
-    float m0 = NEG_INF, m1 = NEG_INF, l0 = 0.f, l1 = 0.f;
+    for (int i = 0; i < MT_O; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
+    float m0 = NEG_INF, m1 = NEG_INF, l0 = 0.f, l1 = 0.f;      // heads 2c and 2c + 1 of the tile
 
     const int ntiles = k_begin < k_end ? (k_end - k_begin + DEC_TILE - 1) / DEC_TILE : 0;
 
-    // lanes 0..15 find the row offsets of the warp's 16 keys from the cached block-table entries
-    auto load_tile = [&](int t, int st) {
+    // lanes 0..15 find the row offsets of the warp's 16 keys of tile t; V of the tile is copied to stage st
+    auto stage_tile = [&](int t, int st) {
         if (t < ntiles) {
             const int kb = k_begin + t * DEC_TILE + warp * 16;
             long long* offs = offs_base + st * 16;
@@ -173,131 +198,129 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
                 offs[lane] = off;
             }
             __syncwarp();
-            bf16* ks_ = stage_base + st * DEC_STAGE;
-            bf16* vs_ = ks_ + 16 * DP;
+            bf16* vs_ = stage_base + st * DEC_STAGE;
 #pragma unroll
             for (int i = lane; i < 16 * CHUNKS; i += 32) {
                 const int row = i / CHUNKS, col = i - row * CHUNKS;
                 const long long off = offs[row];
-                const int bytes = off >= 0 ? 16 : 0;
-                const long long src = off >= 0 ? off + col * 8 : 0;
-                cp_async16(ks_ + row * DP + col * 8, k_cache + src, bytes);
-                cp_async16(vs_ + row * DP + col * 8, v_cache + src, bytes);
+                cp_async16(vs_ + row * DP + col * 8, v_cache + (off >= 0 ? off + col * 8 : 0), off >= 0 ? 16 : 0);
             }
         }
         cp_async_commit();      // one group per tile slot, empty past the end, so the wait count is constant
     };
-
+    // K of tile t (rows g and g + 8 of the warp's 16 keys), straight into registers; zero where there is no key
+    auto load_k = [&](int t, int st, KFrag& ka, KFrag& kb_) {
+        const long long* offs = offs_base + st * 16;
+        const long long oa = t < ntiles ? offs[g] : -1, ob = t < ntiles ? offs[g + 8] : -1;
 #pragma unroll
-    for (int t = 0; t < DEC_STAGES - 1; ++t) load_tile(t, t);
+        for (int jb = 0; jb < DB32; ++jb) {
+            ka.blk[jb] = oa >= 0 ? *reinterpret_cast<const uint4*>(k_cache + oa + 32 * jb + 8 * c) : make_uint4(0u, 0u, 0u, 0u);
+            kb_.blk[jb] = ob >= 0 ? *reinterpret_cast<const uint4*>(k_cache + ob + 32 * jb + 8 * c) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        ka.tail = (DTAIL16 && oa >= 0) ? *reinterpret_cast<const uint2*>(k_cache + oa + 32 * DB32 + 4 * c) : make_uint2(0u, 0u);
+        kb_.tail = (DTAIL16 && ob >= 0) ? *reinterpret_cast<const uint2*>(k_cache + ob + 32 * DB32 + 4 * c) : make_uint2(0u, 0u);
+    };
+
+    KFrag ka_next, kb_next;
+    stage_tile(0, 0);
+    load_k(0, 0, ka_next, kb_next);
+    stage_tile(1, 1);
     for (int t = 0; t < ntiles; ++t) {
         const int st = t % DEC_STAGES;
-        load_tile(t + DEC_STAGES - 1, (t + DEC_STAGES - 1) % DEC_STAGES);
-        cp_async_wait<DEC_STAGES - 1>();
-        __syncwarp();
-        const int kb = k_begin + t * DEC_TILE + warp * 16;
-        if (kb < k_end) {
-            const bf16* ks_ = stage_base + st * DEC_STAGE;
-            const bf16* vs_ = ks_ + 16 * DP;
-            float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            const int j = lane >> 3, r = lane & 7;
+        const KFrag ka = ka_next, kb_ = kb_next;
+        stage_tile(t + 2, (t + 2) % DEC_STAGES);
+        load_k(t + 1, (t + 1) % DEC_STAGES, ka_next, kb_next);      // in flight while this tile is worked on
+        const int key0 = k_begin + t * DEC_TILE + warp * 16;
+        if (key0 < k_end) {
+            // S^T = K Q^T: rows = keys g, g + 8; columns = heads 2c, 2c + 1
+            float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks) {
-                uint32_t b[4];
-                ldmatrix_x4(b, ks_ + ((j >> 1) * 8 + r) * DP + ks * 16 + (j & 1) * 8);
-                mma_bf16(sacc[0], qf[ks], b[0], b[1]);
-                mma_bf16(sacc[1], qf[ks], b[2], b[3]);
+            for (int jb = 0; jb < DB32; ++jb) {
+                mma_bf16_regs(sacc, ka.blk[jb].x, kb_.blk[jb].x, ka.blk[jb].y, kb_.blk[jb].y, qf.blk[jb].x, qf.blk[jb].y);
+                mma_bf16_regs(sacc, ka.blk[jb].z, kb_.blk[jb].z, ka.blk[jb].w, kb_.blk[jb].w, qf.blk[jb].z, qf.blk[jb].w);
             }
-            // mask, scale, online softmax (rows g and g + 8)
-            float rmax0 = NEG_INF, rmax1 = NEG_INF;
+            if (DTAIL16) mma_bf16_regs(sacc, ka.tail.x, kb_.tail.x, ka.tail.y, kb_.tail.y, qf.tail.x, qf.tail.y);
+            const bool oka = key0 + g < k_end, okb = key0 + g + 8 < k_end;
+            sacc[0] = oka ? sacc[0] * scale_log2e : NEG_INF;
+            sacc[1] = oka ? sacc[1] * scale_log2e : NEG_INF;
+            sacc[2] = okb ? sacc[2] * scale_log2e : NEG_INF;
+            sacc[3] = okb ? sacc[3] * scale_log2e : NEG_INF;
+            // maxima over the 16 keys: over the lanes that share c
+            float r0 = fmaxf(sacc[0], sacc[2]), r1 = fmaxf(sacc[1], sacc[3]);
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const bool ok = kb + nt * 8 + 2 * c + e < k_end;
-                    sacc[nt][e] = ok ? sacc[nt][e] * scale_log2e : NEG_INF;
-                    sacc[nt][2 + e] = ok ? sacc[nt][2 + e] * scale_log2e : NEG_INF;
-                    rmax0 = fmaxf(rmax0, sacc[nt][e]);
-                    rmax1 = fmaxf(rmax1, sacc[nt][2 + e]);
-                }
+            for (int o = 4; o < 32; o <<= 1) {
+                r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, o));
+                r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, o));
             }
-            rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 1));
-            rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 2));
-            rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 1));
-            rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 2));
-            const float mn0 = fmaxf(m0, rmax0), mn1 = fmaxf(m1, rmax1);
+            const float mn0 = fmaxf(m0, r0), mn1 = fmaxf(m1, r1);
             const float mu0 = mn0 == NEG_INF ? 0.f : mn0, mu1 = mn1 == NEG_INF ? 0.f : mn1;
             const float a0 = exp2f(m0 - mu0), a1 = exp2f(m1 - mu1);
+            const bool rescale = (mn0 != m0) || (mn1 != m1);
             m0 = mn0; m1 = mn1;
-            float ps0 = 0.f, ps1 = 0.f;
+            sacc[0] = exp2f(sacc[0] - mu0); sacc[1] = exp2f(sacc[1] - mu1);
+            sacc[2] = exp2f(sacc[2] - mu0); sacc[3] = exp2f(sacc[3] - mu1);
+            l0 = l0 * a0 + sacc[0] + sacc[2];          // this thread's keys only; summed over g at the end
+            l1 = l1 * a1 + sacc[1] + sacc[3];
+            // P^T as the B operand: keys 2c, 2c + 1 (and + 8) of head g
+            const uint32_t pb0 = movmatrix_trans(pack_bf16(sacc[0], sacc[1]));
+            const uint32_t pb1 = movmatrix_trans(pack_bf16(sacc[2], sacc[3]));
+            if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    sacc[nt][e] = exp2f(sacc[nt][e] - mu0);
-                    sacc[nt][2 + e] = exp2f(sacc[nt][2 + e] - mu1);
-                    ps0 += sacc[nt][e];
-                    ps1 += sacc[nt][2 + e];
+                for (int mt = 0; mt < MT_O; ++mt) {
+                    oacc[mt][0] *= a0; oacc[mt][1] *= a1; oacc[mt][2] *= a0; oacc[mt][3] *= a1;
                 }
             }
-            l0 = l0 * a0 + ps0;
-            l1 = l1 * a1 + ps1;
-            uint32_t pa[4];
-            pa[0] = pack_bf16(sacc[0][0], sacc[0][1]);
-            pa[1] = pack_bf16(sacc[0][2], sacc[0][3]);
-            pa[2] = pack_bf16(sacc[1][0], sacc[1][1]);
-            pa[3] = pack_bf16(sacc[1][2], sacc[1][3]);
+            cp_async_wait<DEC_STAGES - 1>();            // V of this tile has landed
+            __syncwarp();
+            const bf16* vs_ = stage_base + st * DEC_STAGE;
+            const int j = lane >> 3, r = lane & 7;
 #pragma unroll
-            for (int nt2 = 0; nt2 < NT_O / 2; ++nt2) {
-                uint32_t b[4];
-                ldmatrix_x4_trans(b, vs_ + ((j & 1) * 8 + r) * DP + nt2 * 16 + (j >> 1) * 8);
-                float* o0 = oacc[2 * nt2];
-                float* o1 = oacc[2 * nt2 + 1];
-                o0[0] *= a0; o0[1] *= a0; o0[2] *= a1; o0[3] *= a1;
-                o1[0] *= a0; o1[1] *= a0; o1[2] *= a1; o1[3] *= a1;
-                mma_bf16(oacc[2 * nt2], pa, b[0], b[1]);
-                mma_bf16(oacc[2 * nt2 + 1], pa, b[2], b[3]);
+            for (int mt = 0; mt < MT_O; ++mt) {
+                uint32_t a[4];
+                ldmatrix_x4_trans(a, vs_ + ((j >> 1) * 8 + r) * DP + mt * 16 + (j & 1) * 8);
+                mma_bf16_regs(oacc[mt], a[0], a[1], a[2], a[3], pb0, pb1);
             }
         }
         __syncwarp();
     }
     cp_async_wait<0>();
-    tw_grid_launch_dependents();     // all keys are read: the next kernel may be scheduled
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    // sums over the keys of the other threads with the same heads
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+    }
 
     // merge the warps through shared memory (the stage buffers are free now)
     __syncthreads();
-    float* mo = reinterpret_cast<float*>(smem_raw);              // [warps][16][D]
-    float* mml = mo + DEC_WARPS * 16 * D;                        // [warps][16][2]
+    float* mo = reinterpret_cast<float*>(smem_raw);              // [warps][heads][D]
+    float* mml = mo + DEC_WARPS * DEC_HEADS * D;                 // [warps][heads][2]
 #pragma unroll
-    for (int nt = 0; nt < NT_O; ++nt) {
-        const int d = nt * 8 + 2 * c;
-        float* p0 = mo + ((warp * 16 + g) * D + d);
-        float* p1 = mo + ((warp * 16 + g + 8) * D + d);
-        p0[0] = oacc[nt][0]; p0[1] = oacc[nt][1];
-        p1[0] = oacc[nt][2]; p1[1] = oacc[nt][3];
+    for (int mt = 0; mt < MT_O; ++mt) {
+        const int d = mt * 16 + g;
+        float* p0 = mo + (warp * DEC_HEADS + 2 * c) * D;
+        float* p1 = p0 + D;
+        p0[d] = oacc[mt][0]; p1[d] = oacc[mt][1];
+        p0[d + 8] = oacc[mt][2]; p1[d + 8] = oacc[mt][3];
     }
-    if (c == 0) {
-        mml[(warp * 16 + g) * 2] = m0; mml[(warp * 16 + g) * 2 + 1] = l0;
-        mml[(warp * 16 + g + 8) * 2] = m1; mml[(warp * 16 + g + 8) * 2 + 1] = l1;
+    if (g == 0) {
+        mml[(warp * DEC_HEADS + 2 * c) * 2] = m0; mml[(warp * DEC_HEADS + 2 * c) * 2 + 1] = l0;
+        mml[(warp * DEC_HEADS + 2 * c + 1) * 2] = m1; mml[(warp * DEC_HEADS + 2 * c + 1) * 2 + 1] = l1;
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < nheads * D; idx += DEC_WARPS * 32) {
         const int row = idx / D, d = idx - row * D;
         float M = NEG_INF;
 #pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, mml[(w * 16 + row) * 2]);
+        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, mml[(w * DEC_HEADS + row) * 2]);
         float L = 0.f, o = 0.f;
         if (M != NEG_INF) {
 #pragma unroll
             for (int w = 0; w < DEC_WARPS; ++w) {
-                const float mw = mml[(w * 16 + row) * 2];
+                const float mw = mml[(w * DEC_HEADS + row) * 2];
                 const float f = mw == NEG_INF ? 0.f : exp2f(mw - M);
-                L += mml[(w * 16 + row) * 2 + 1] * f;
-                o += mo[(w * 16 + row) * D + d] * f;
+                L += mml[(w * DEC_HEADS + row) * 2 + 1] * f;
+                o += mo[(w * DEC_HEADS + row) * D + d] * f;
             }
         }
         const int head = kvh * G + h0 + row;
@@ -309,6 +332,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
             if (d == 0) { partial_ml[base * 2] = M; partial_ml[base * 2 + 1] = L; }
         }
     }
+    tw_grid_launch_dependents();
     if (nsplit == 1) return;
 
     // The block that finishes last among the slices of this (request, head tile) merges them, in
@@ -327,7 +351,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
     __threadfence();
     // factors 2^(m_i - M) and weighted sums l_i 2^(m_i - M) of every (head, slice), loaded in parallel
     float* fac = reinterpret_cast<float*>(smem_raw);              // [nheads][nsplit]
-    float* lsum = fac + 16 * nsplit;                              // [nheads][nsplit]
+    float* lsum = fac + DEC_HEADS * nsplit;                       // [nheads][nsplit]
     const size_t group_base = ((size_t)s * Hq + kvh * G + h0) * nsplit;      // slices of head h0 start here
     for (int idx = threadIdx.x; idx < nheads * nsplit; idx += DEC_WARPS * 32) {
         fac[idx] = __ldcg(partial_ml + (group_base + idx) * 2);
@@ -578,7 +602,7 @@ int set_attrs() {
 TW_EXPORT int tw_attn_head_dim() { return D; }
 
 // Scratch floats the decode kernel needs for `n_seqs` requests: partial accumulators, then (max, sum) pairs.
-// Beside them it needs one int32 counter per (request, key/value head, tile of 16 heads), zero before the
+// Beside them it needs one int32 counter per (request, key/value head, tile of 8 heads), zero before the
 // first launch; the kernel leaves them zero.
 TW_EXPORT long long tw_attn_decode_scratch_floats(int n_seqs, int Hq, int nsplit) {
     return (long long)n_seqs * Hq * nsplit * (D + 2);
@@ -592,7 +616,7 @@ TW_EXPORT int tw_attn_decode(void* out, int out_stride, const void* q, int q_str
     if (n_seqs <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv || nsplit < 1 || (nsplit > 1 && (!scratch || !counters))) return (int)cudaErrorInvalidValue;
     if (int e = set_attrs()) return e;
-    const int G = Hq / Hkv, htiles = (G + 15) / 16;
+    const int G = Hq / Hkv, htiles = (G + DEC_HEADS - 1) / DEC_HEADS;
     float* partial_o = scratch;
     float* partial_ml = scratch ? scratch + (size_t)n_seqs * Hq * nsplit * D : nullptr;
     dim3 grid(nsplit * htiles, Hkv, n_seqs);
@@ -647,7 +671,7 @@ TW_EXPORT int tw_attn_decode_static(void* out, int out_stride, const void* q, in
     g_static_error[0] = 0;
     if (n_seqs <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv || nsplit < 1) return (int)cudaErrorInvalidValue;
-    const int G = Hq / Hkv, htiles = (G + 15) / 16;
+    const int G = Hq / Hkv, htiles = (G + DEC_HEADS - 1) / DEC_HEADS;
     const size_t partial_bytes = sizeof(float) * (size_t)n_seqs * Hq * nsplit * (D + 2);
     const size_t counter_bytes = sizeof(int) * (size_t)n_seqs * Hkv * htiles;
     if (counter_bytes > TW_ATTN_STATIC_COUNTER_BYTES ||

@@ -256,9 +256,14 @@ def tensor_core_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
 
 def decode_splits(n_seqs: int, n_kv_heads: int, group: int, max_kv_len: int) -> int:
     """How many slices the keys of a request are cut into, so that the launch fills the GPU."""
-    head_tiles = (group + 15) // 16
+    import os
+    forced = os.environ.get("TESSWEAVE_DECODE_SPLITS")
+    if forced:
+        return max(1, min(int(forced), 128, DECODE_SCRATCH_UNITS // max(1, n_seqs)))
+    head_tiles = (group + 7) // 8
     tiles = max(1, -(-max_kv_len // 64))
-    target = -(-4 * _SM_COUNT // max(1, n_seqs * n_kv_heads * head_tiles))
+    # the kernel fits four blocks on an SM; aim at a little under one full wave of blocks
+    target = max(1, (7 * _SM_COUNT // 2) // max(1, n_seqs * n_kv_heads * head_tiles))
     return max(1, min(tiles, target, 128, DECODE_SCRATCH_UNITS // max(1, n_seqs)))
 
 
@@ -269,7 +274,7 @@ def decode_scratch_floats(n_q_heads: int, head_dim: int) -> int:
 def decode_counter_ints(n_seqs: int, n_kv_heads: int, group: int) -> int:
     """int32 counters (zero before the first launch, left zero by every launch) the split
     decode kernel uses to find the block that finishes last."""
-    return max(n_seqs, DECODE_SCRATCH_UNITS) * n_kv_heads * ((group + 15) // 16)
+    return max(n_seqs, DECODE_SCRATCH_UNITS) * n_kv_heads * ((group + 7) // 8)
 
 
 def _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim):
@@ -295,7 +300,7 @@ def attention_decode(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block
         _need(scratch is not None and scratch.dtype == torch.float32
               and scratch.numel() >= n_seqs * n_q_heads * nsplit * (head_dim + 2), "attention_decode: scratch too small")
         _need(counters is not None and counters.dtype == torch.int32
-              and counters.numel() >= n_seqs * n_kv_heads * ((n_q_heads // n_kv_heads + 15) // 16),
+              and counters.numel() >= n_seqs * n_kv_heads * ((n_q_heads // n_kv_heads + 7) // 8),
               "attention_decode: too few counters")
     code = _fn("attention_bf16", "tw_attn_decode", {"TW_HEAD_DIM": head_dim})(
         _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(seq_q_start), _ptr(seq_q_len),
@@ -368,3 +373,42 @@ def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kp
     code = _fn("gemm_smallm", "tw_gemm_smallm")(_ptr(w), _ptr(x), c_int(m), c_int(n), c_int(k), c_int(kper), _ptr(out),
                                                 c_int(mode), c_int(stride), _stream())
     _check(code, "gemm_small_m")
+
+
+# ---------------------------------------------------------------------------
+# matrix products on tcgen05 tensor cores fed by TMA
+# ---------------------------------------------------------------------------
+def tcgen05_split(n: int, k: int) -> tuple[int, int]:
+    """(slices, k per slice) for the swap-AB use: about one block per SM, slices multiples of 64 wide."""
+    tiles = -(-n // 128)
+    want = max(1, min(16, round(_SM_COUNT / tiles))) if tiles < _SM_COUNT else 1
+    kper = max(256, -(-(-(-k // want)) // 64) * 64)
+    kper = min(kper, -(-k // 64) * 64)
+    return -(-k // kper), kper
+
+
+def gemm_tcgen05(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, status: torch.Tensor,
+                 kper: int | None = None, swap: bool | None = None) -> None:
+    """out[:m] = x[:m] @ w.T on the tcgen05 tensor cores (bf16 operands, fp32 accumulation in TMEM).
+    ``swap`` (default: m <= 64) makes the weights the 128-row operand; k may then be split into
+    slices of ``kper`` and ``out`` is fp32 [slices, m, n]."""
+    _cuda(out, x, w, status)
+    n, k = w.shape
+    swap = (m <= 64) if swap is None else swap
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x.is_contiguous()
+          and x.shape[1] == k and k % 8 == 0, "gemm_tcgen05: contiguous bf16 operands, k a multiple of 8")
+    _need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0, "gemm_tcgen05: operands must be 16-byte aligned")
+    kper = kper or -(-k // 64) * 64
+    split = -(-k // kper)
+    if split > 1:
+        _need(out.dtype == torch.float32 and out.dim() == 3 and tuple(out.shape) == (split, m, n) and out.is_contiguous(),
+              "gemm_tcgen05: split output must be fp32 [slices, m, n]")
+        mode, stride = 2, n
+    else:
+        _need(out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= m and out.shape[1] == n
+              and out.dtype in (torch.bfloat16, torch.float32), "gemm_tcgen05: bad output")
+        mode, stride = (0 if out.dtype == torch.bfloat16 else 1), out.stride(0)
+    code = _fn("gemm_tcgen05", "tw_gemm_tcgen05")(_ptr(x), _ptr(w), c_int(m), c_int(n), c_int(k), c_int(kper), _ptr(out),
+                                                  c_int(mode), c_int(stride), c_int(1 if swap else 0), _ptr(status),
+                                                  _stream())
+    _check(code, "gemm_tcgen05")
