@@ -378,6 +378,15 @@ def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kp
 # ---------------------------------------------------------------------------
 # matrix products on tcgen05 tensor cores fed by TMA
 # ---------------------------------------------------------------------------
+TCGEN05_MIN_M, TCGEN05_MAX_M = 9, 32     # rows for which the swap-AB tcgen05 kernel is the product path
+
+
+def tcgen05_supported(x: torch.Tensor, w: torch.Tensor, m: int) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and TCGEN05_MIN_M <= m <= TCGEN05_MAX_M
+            and w.shape[1] % 8 == 0 and w.is_contiguous() and x.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 def tcgen05_split(n: int, k: int) -> tuple[int, int]:
     """(slices, k per slice) for the swap-AB use: about one block per SM, slices multiples of 64 wide."""
     tiles = -(-n // 128)

@@ -44,13 +44,27 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
            allow_split: bool = False):
     """``x @ w.T`` into the workspace buffer ``name``.
 
-    Steps with few rows (decode) in bfloat16 go through the weight-streaming kernel of
-    csrc/gemm_smallm.cu; when the matrix has too few rows to fill the GPU that kernel splits
-    k and, if the caller can take it (``allow_split``), the fp32 slices are returned as a
-    ``SplitSum`` for the consuming kernel to add.  Everything else is a library product.
+    Steps with few rows (decode) in bfloat16 go through hand-written kernels: up to 8 rows
+    the weight-streaming kernel of csrc/gemm_smallm.cu, 9 to 32 rows the tcgen05/TMA kernel of
+    csrc/gemm_tcgen05.cu with the weights as the 128-row operand.  When the matrix has too few
+    rows to fill the GPU these kernels split k and, if the caller can take it
+    (``allow_split``), the fp32 slices are returned as a ``SplitSum`` for the consuming kernel
+    to add.  Everything else is a library product.
     """
     m, n = x.shape[0], w.shape[0]
     dtype = out_dtype or x.dtype
+    if x.is_cuda and ops.tcgen05_supported(x, w, m):
+        # 9..32 rows: tcgen05 tensor cores with the weights as the 128-row operand, fed by TMA
+        split, kper = ops.tcgen05_split(n, w.shape[1])
+        if split > 1:
+            slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
+            ops.gemm_tcgen05(slices, x, w, m, ctx.status, kper=kper, swap=True)
+            if allow_split:
+                return SplitSum(slices)
+            return SplitSum(slices).dense(dtype, ctx.workspace.get(name, (m, n), dtype))
+        out = ctx.workspace.get(name, (m, n), dtype)
+        ops.gemm_tcgen05(out, x, w, m, ctx.status, swap=True)
+        return out
     if x.is_cuda and ops.small_m_supported(x, w, m):
         split, kper = ops.small_m_split(n, w.shape[1])
         if split > 1 and allow_split:

@@ -292,7 +292,8 @@ def test_builtin_parts_alone(dtype):
         d.dest.copy_((torch.randn(d.shape) * 0.1).view(d.dest.shape))
     x = (torch.randn(n, 200, device="cuda") * 0.5).to(dtype)
     ws = Workspace(torch.device("cuda"))
-    ctx = type("Ctx", (), {"n_tokens": n, "workspace": ws, "split_ok": False})()
+    ctx = type("Ctx", (), {"n_tokens": n, "workspace": ws, "split_ok": False,
+                           "status": torch.zeros(1, dtype=torch.int32, device="cuda")})()
     got = ffn.forward(ctx, x).float().cpu()
     w = {f"m.{d.name}": d.dest.float().cpu().reshape(d.shape) for d in ffn.weights()}
     assert torch.allclose(got, plain_qwen2.swiglu(w, "m", x.float().cpu()), **tol)
