@@ -199,6 +199,65 @@ add_rmsnorm_cluster_kernel(T* __restrict__ out, float* __restrict__ resid, const
     }
 }
 
+__device__ __forceinline__ float4 tw_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 tw_load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void tw_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void tw_store4(__nv_bfloat16* p, float4 v) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// Many rows (prompt portions): four values per thread and access, one pass, values kept in registers.
+// Dense delta only; hidden a multiple of 4 and at most 4 * 256 * TW_NORM_V4 wide.
+#define TW_NORM_V4 4
+template <typename T>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_vec4_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,
+                        const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
+    __shared__ float scratch[33];
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float4* x4 = reinterpret_cast<float4*>(resid + (size_t)src * hidden);
+    const int n4 = hidden >> 2;
+    float4 v[TW_NORM_V4];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < TW_NORM_V4; ++j) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4) {
+            v[j] = x4[i];
+            if (delta) {
+                const float4 d = tw_load4(delta + (size_t)src * hidden + 4 * i);
+                v[j].x += d.x; v[j].y += d.y; v[j].z += d.z; v[j].w += d.w;
+                if (!rows) x4[i] = v[j];
+            }
+            ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+        }
+    }
+    ss = tw_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    const float4* w4 = reinterpret_cast<const float4*>(weight);
+#pragma unroll
+    for (int j = 0; j < TW_NORM_V4; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4) {
+            const float4 w = w4[i];
+            tw_store4(out + (size_t)r * hidden + 4 * i,
+                      make_float4((v[j].x * inv) * w.x, (v[j].y * inv) * w.y, (v[j].z * inv) * w.z, (v[j].w * inv) * w.w));
+        }
+    }
+}
+
 template <typename T>
 static int launch_add_rmsnorm(T* out, float* resid, const T* delta, const float* partial, int nsplit,
                               size_t split_stride, const float* weight, float eps, int n_rows, int hidden,
@@ -206,6 +265,11 @@ static int launch_add_rmsnorm(T* out, float* resid, const T* delta, const float*
     if (n_rows <= 64 && hidden >= 1024 && hidden <= TW_NORM_CLUSTER * TW_NORM_CTHREADS * TW_NORM_CMAXV) {
         return tw_launch(add_rmsnorm_cluster_kernel<T>, dim3(n_rows * TW_NORM_CLUSTER), dim3(TW_NORM_CTHREADS), 0, stream,
                          TW_NORM_CLUSTER, out, resid, delta, partial, nsplit, split_stride, weight, eps, hidden, rows);
+    }
+    if (!partial && (hidden & 3) == 0 && hidden <= 4 * 256 * TW_NORM_V4) {
+        tw_launch(add_rmsnorm_vec4_kernel<T>, dim3(n_rows), dim3(256), 0, stream, 1, out, resid, delta, weight, eps, hidden,
+                  rows);
+        return TW_LAUNCH_CHECK();
     }
     if (hidden <= TW_NORM_THREADS * TW_NORM_MAXV)
         tw_launch(add_rmsnorm_kernel<T, true>, dim3(n_rows), dim3(TW_NORM_THREADS), 0, stream, 1, out, resid, delta, partial, nsplit,
@@ -324,6 +388,74 @@ rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const float* __restric
     }
 }
 
+// bf16, dense source, head size a multiple of 16: a thread rotates eight neighbouring pairs with 16-byte accesses
+// (or copies sixteen values of v).  Same arithmetic as the kernel above.
+__global__ void __launch_bounds__(TW_ROPE_THREADS)
+rope_kv_write_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, int qkv_stride, const float* __restrict__ bias,
+                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                            const int* __restrict__ seq_slot, const int* __restrict__ block_table, int table_stride,
+                            const float* __restrict__ inv_freq, __nv_bfloat16* __restrict__ k_cache,
+                            __nv_bfloat16* __restrict__ v_cache, int Hq, int Hkv, int D, int page_size, int num_pages,
+                            int write_cache, int* status) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int n = blockIdx.x;
+    const int s = seq_of_token[n];
+    if (s < 0) return;
+    const int pos = positions[n];
+    const int half = D >> 1, groups = half >> 3;           // groups of 8 pairs per head
+    __nv_bfloat16* row = qkv + (size_t)n * qkv_stride;
+    int page = -1;
+    if (write_cache) {
+        const int blk = pos / page_size;
+        page = blk < table_stride ? block_table[(size_t)seq_slot[s] * table_stride + blk] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, TW_ERR_PAGE);
+            page = -1;
+        }
+    }
+    const int in_page = pos % page_size;
+    const int rot_items = (write_cache ? Hq + Hkv : Hq) * groups;
+    const int v_items = write_cache ? Hkv * groups : 0;      // v: 8 values of each half per item
+    const int idx = blockIdx.y * TW_ROPE_THREADS + threadIdx.x;
+    if (idx >= rot_items + v_items) return;
+    const bool is_v = idx >= rot_items;
+    const int item = is_v ? idx - rot_items : idx;
+    const int head = item / groups, i0 = (item - head * groups) * 8;
+    const int col = (is_v ? (Hq + Hkv) * D : 0) + head * D + i0;
+    uint4 lo = *reinterpret_cast<const uint4*>(row + col), hi = *reinterpret_cast<const uint4*>(row + col + half);
+    __nv_bfloat162* lo2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+    __nv_bfloat162* hi2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        float2 x1 = __bfloat1622float2(lo2[e]), x2 = __bfloat1622float2(hi2[e]);
+        if (bias) {
+            x1.x += bias[col + 2 * e]; x1.y += bias[col + 2 * e + 1];
+            x2.x += bias[col + half + 2 * e]; x2.y += bias[col + half + 2 * e + 1];
+        }
+        float2 y1 = x1, y2 = x2;
+        if (inv_freq && !is_v) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i0 + 2 * e], &sn, &cs);
+            y1.x = x1.x * cs - x2.x * sn; y2.x = x2.x * cs + x1.x * sn;
+            sincosf((float)pos * inv_freq[i0 + 2 * e + 1], &sn, &cs);
+            y1.y = x1.y * cs - x2.y * sn; y2.y = x2.y * cs + x1.y * sn;
+        }
+        lo2[e] = __floats2bfloat162_rn(y1.x, y1.y);
+        hi2[e] = __floats2bfloat162_rn(y2.x, y2.y);
+    }
+    __nv_bfloat16* dst;
+    if (!is_v && head < Hq) {
+        dst = row + col;
+    } else {
+        if (page < 0) return;
+        const int kvh = is_v ? head : head - Hq;
+        dst = (is_v ? v_cache : k_cache) + (((size_t)page * Hkv + kvh) * page_size + in_page) * D + i0;
+    }
+    *reinterpret_cast<uint4*>(dst) = lo;
+    *reinterpret_cast<uint4*>(dst + half) = hi;
+}
+
 TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, int nsplit, long split_stride,
                                const float* bias, const int* positions,
                                const int* seq_of_token, const int* seq_slot, const int* block_table, int table_stride,
@@ -332,6 +464,15 @@ TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, 
                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (D <= 0 || (D & 1)) return (int)cudaErrorInvalidValue;
+    if (dtype == TW_BF16 && !partial && (D & 15) == 0 && (qkv_stride & 7) == 0 &&
+        (reinterpret_cast<uintptr_t>(qkv) & 15) == 0) {
+        const int items = (Hq + 2 * Hkv) * (D / 16);
+        const dim3 vgrid(n_tokens, (items + TW_ROPE_THREADS - 1) / TW_ROPE_THREADS);
+        return tw_launch(rope_kv_write_bf16x8_kernel, vgrid, dim3(TW_ROPE_THREADS), 0, stream, 1, (__nv_bfloat16*)qkv,
+                         qkv_stride, bias, positions, seq_of_token, seq_slot, block_table, table_stride, inv_freq,
+                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, page_size, num_pages,
+                         write_cache, status);
+    }
     const int work = (Hq + 2 * Hkv) * (D / 2);
     const dim3 grid(n_tokens, (work + TW_ROPE_THREADS - 1) / TW_ROPE_THREADS);
     const int threads = TW_ROPE_THREADS;
