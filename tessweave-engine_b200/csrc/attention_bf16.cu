@@ -7,8 +7,10 @@
 //     and values are read once for the whole group.  The keys are split over blocks
 //     ("split-KV"); partial results (fp32 accumulator, running maximum, sum) go to scratch
 //     memory, and the block that finishes last merges them in slice order.
-//   * prefill: requests that bring several tokens.  A block serves 64 rows, a row being a
-//     (token, query head of the group) pair, and walks the keys up to the last visible one.
+//   * prefill: requests that bring several tokens.  A block serves 128 rows (64 for head sizes
+//     above 128), a row being a (token, query head of the group) pair, and walks the keys up
+//     to the last visible one; a warp holds two 16-row tiles, so that every key and value
+//     fragment it reads from shared memory feeds two MMAs.
 // Scores, softmax statistics and the accumulator are fp32; probabilities are rounded to
 // bf16 only as the operand of the P.V product.  Keys beyond the visible range are never
 // read: their shared-memory rows are zero-filled, so stale page contents cannot leak in.
@@ -395,12 +397,14 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
 // prefill
 // ---------------------------------------------------------------------------------------
 constexpr int PF_WARPS = 4;
-constexpr int PF_BM = 16 * PF_WARPS;                          // rows (token, head) per block
+constexpr int PF_MT = D <= 128 ? 2 : 1;                       // 16-row tiles per warp (the accumulators must fit the registers)
+constexpr int PF_BM = 16 * PF_MT * PF_WARPS;                  // rows (token, head) per block
 constexpr int PF_BN = 64;                                     // keys per iteration
 constexpr int PF_STAGE = 2 * PF_BN * DP;                      // K then V
-constexpr int PF_SMEM = 2 * PF_STAGE * 2 + 2 * PF_BN * 8;
+constexpr int PF_Q_ELEMS = PF_BM * DP;
+constexpr int PF_SMEM = PF_Q_ELEMS * 2 + 2 * PF_STAGE * 2 + 2 * PF_BN * 8;
 
-__global__ void __launch_bounds__(PF_WARPS * 32)
+__global__ void __launch_bounds__(PF_WARPS * 32, (D <= 128 ? 2 : 1))
 attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
                     const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                     const int* __restrict__ seq_kv_len, const int* __restrict__ seq_slot,
@@ -424,34 +428,44 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
     const int g = lane >> 2, c = lane & 3;
     const int* table = block_table + (size_t)seq_slot[s] * table_stride;
 
-    bf16* stages = reinterpret_cast<bf16*>(smem_raw);
-    long long* offs_all = reinterpret_cast<long long*>(smem_raw + 2 * PF_STAGE * 2);
+    bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);
+    bf16* stages = q_tile + PF_Q_ELEMS;
+    long long* offs_all = reinterpret_cast<long long*>(smem_raw + PF_Q_ELEMS * 2 + 2 * PF_STAGE * 2);
 
-    // rows of this thread
-    const int ra = row0 + warp * 16 + g, rb = ra + 8;
-    const bool va = ra < rows_total, vb = rb < rows_total;
-    const int ta = ra / G, tb = rb / G;
-    const int pa_ = pos0 + ta, pb_ = pos0 + tb;                  // positions of the two rows
-    const int loa = (window > 0 && pa_ - window + 1 > 0) ? pa_ - window + 1 : 0;
-    const int lob = (window > 0 && pb_ - window + 1 > 0) ? pb_ - window + 1 : 0;
+    // the block's query rows into shared memory (rows beyond the portion are zero)
+    for (int i = threadIdx.x; i < PF_BM * CHUNKS; i += PF_WARPS * 32) {
+        const int rr = i / CHUNKS, col = i - rr * CHUNKS;
+        const int r = row0 + rr;
+        const bool v = r < rows_total;
+        const int t = v ? r / G : 0;
+        const bf16* src = q + (size_t)(n0 + t) * q_stride + (size_t)(kvh * G + (v ? r - t * G : 0)) * D + col * 8;
+        cp_async16(q_tile + rr * DP + col * 8, src, v ? 16 : 0);
+    }
+    cp_async_commit();
 
-    uint32_t qf[KSTEPS][4];
-    {
-        const bf16* q0 = q + (size_t)(n0 + (va ? ta : 0)) * q_stride + (size_t)(kvh * G + (va ? ra - ta * G : 0)) * D;
-        const bf16* q1 = q + (size_t)(n0 + (vb ? tb : 0)) * q_stride + (size_t)(kvh * G + (vb ? rb - tb * G : 0)) * D;
+    // rows of this thread: m-tile mt holds rows wbase + 16 mt + g and + 8
+    const int wbase = row0 + warp * 16 * PF_MT;
+    int rpos[PF_MT][2], rlo[PF_MT][2];
+    bool rvalid[PF_MT][2];
 #pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-            const int d = ks * 16 + 2 * c;
-            qf[ks][0] = va ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
-            qf[ks][1] = vb ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
-            qf[ks][2] = va ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
-            qf[ks][3] = vb ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
+    for (int mt = 0; mt < PF_MT; ++mt) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = wbase + 16 * mt + g + 8 * h;
+            rvalid[mt][h] = r < rows_total;
+            rpos[mt][h] = pos0 + r / G;
+            rlo[mt][h] = (window > 0 && rpos[mt][h] - window + 1 > 0) ? rpos[mt][h] - window + 1 : 0;
         }
     }
-    float oacc[NT_O][4];
+    float oacc[PF_MT][NT_O][4];
+    float mrow[PF_MT][2], lrow[PF_MT][2];
 #pragma unroll
-    for (int i = 0; i < NT_O; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
-    float m0 = NEG_INF, m1 = NEG_INF, l0 = 0.f, l1 = 0.f;
+    for (int mt = 0; mt < PF_MT; ++mt) {
+        mrow[mt][0] = mrow[mt][1] = NEG_INF;
+        lrow[mt][0] = lrow[mt][1] = 0.f;
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i) { oacc[mt][i][0] = oacc[mt][i][1] = oacc[mt][i][2] = oacc[mt][i][3] = 0.f; }
+    }
 
     // keys this block has to look at: from the first row's window start to the last row's position
     const int t_last = min(q_len - 1, (row0 + PF_BM - 1) / G);
@@ -461,9 +475,9 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
     const int key_begin = lo_block / PF_BN * PF_BN;
     const int ntiles = (key_end - key_begin + PF_BN - 1) / PF_BN;
     // warp-level bounds, to skip tiles no row of the warp can see
-    const int wr0 = row0 + warp * 16, wr1 = min(rows_total - 1, wr0 + 15);
+    const int wr1 = min(rows_total - 1, wbase + 16 * PF_MT - 1);
     const int warp_hi = pos0 + wr1 / G;
-    const int warp_lo = (window > 0 && pos0 + wr0 / G - window + 1 > 0) ? pos0 + wr0 / G - window + 1 : 0;
+    const int warp_lo = (window > 0 && pos0 + wbase / G - window + 1 > 0) ? pos0 + wbase / G - window + 1 : 0;
 
     auto load_tile = [&](int t, int st) {
         const int kb = key_begin + t * PF_BN;
@@ -485,6 +499,7 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
         cp_async_commit();
     };
 
+    const int j = lane >> 3, r8 = lane & 7;
     load_tile(0, 0);
     for (int t = 0; t < ntiles; ++t) {
         const int st = t & 1;
@@ -496,92 +511,115 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
         }
         __syncthreads();
         const int kb = key_begin + t * PF_BN;
-        if (wr0 < rows_total && kb <= warp_hi && kb + PF_BN > warp_lo) {
+        if (wbase < rows_total && kb <= warp_hi && kb + PF_BN > warp_lo) {
             const bf16* ks_ = stages + st * PF_STAGE;
             const bf16* vs_ = ks_ + PF_BN * DP;
-            float sacc[PF_BN / 8][4];
+            float sacc[PF_MT][PF_BN / 8][4];
 #pragma unroll
-            for (int i = 0; i < PF_BN / 8; ++i) { sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f; }
-            const int j = lane >> 3, r = lane & 7;
+            for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+                for (int i = 0; i < PF_BN / 8; ++i) { sacc[mt][i][0] = sacc[mt][i][1] = sacc[mt][i][2] = sacc[mt][i][3] = 0.f; }
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) {
+                uint32_t qa[PF_MT][4];
+#pragma unroll
+                for (int mt = 0; mt < PF_MT; ++mt)
+                    ldmatrix_x4(qa[mt], q_tile + ((warp * PF_MT + mt) * 16 + (j & 1) * 8 + r8) * DP + ks * 16 + (j >> 1) * 8);
 #pragma unroll
                 for (int np = 0; np < PF_BN / 16; ++np) {
                     uint32_t b[4];
-                    ldmatrix_x4(b, ks_ + (np * 16 + (j >> 1) * 8 + r) * DP + ks * 16 + (j & 1) * 8);
-                    mma_bf16(sacc[2 * np], qf[ks], b[0], b[1]);
-                    mma_bf16(sacc[2 * np + 1], qf[ks], b[2], b[3]);
+                    ldmatrix_x4(b, ks_ + (np * 16 + (j >> 1) * 8 + r8) * DP + ks * 16 + (j & 1) * 8);
+#pragma unroll
+                    for (int mt = 0; mt < PF_MT; ++mt) {
+                        mma_bf16(sacc[mt][2 * np], qa[mt], b[0], b[1]);
+                        mma_bf16(sacc[mt][2 * np + 1], qa[mt], b[2], b[3]);
+                    }
                 }
             }
-            float rmax0 = NEG_INF, rmax1 = NEG_INF;
+            uint32_t pfrag[PF_MT][PF_BN / 16][4];
 #pragma unroll
-            for (int nt = 0; nt < PF_BN / 8; ++nt) {
+            for (int mt = 0; mt < PF_MT; ++mt) {
+                float rmax0 = NEG_INF, rmax1 = NEG_INF;
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int key = kb + nt * 8 + 2 * c + e;
-                    const bool oka = va && key <= pa_ && key >= loa;
-                    const bool okb = vb && key <= pb_ && key >= lob;
-                    sacc[nt][e] = oka ? sacc[nt][e] * scale_log2e : NEG_INF;
-                    sacc[nt][2 + e] = okb ? sacc[nt][2 + e] * scale_log2e : NEG_INF;
-                    rmax0 = fmaxf(rmax0, sacc[nt][e]);
-                    rmax1 = fmaxf(rmax1, sacc[nt][2 + e]);
+                for (int nt = 0; nt < PF_BN / 8; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = kb + nt * 8 + 2 * c + e;
+                        const bool oka = rvalid[mt][0] && key <= rpos[mt][0] && key >= rlo[mt][0];
+                        const bool okb = rvalid[mt][1] && key <= rpos[mt][1] && key >= rlo[mt][1];
+                        sacc[mt][nt][e] = oka ? sacc[mt][nt][e] * scale_log2e : NEG_INF;
+                        sacc[mt][nt][2 + e] = okb ? sacc[mt][nt][2 + e] * scale_log2e : NEG_INF;
+                        rmax0 = fmaxf(rmax0, sacc[mt][nt][e]);
+                        rmax1 = fmaxf(rmax1, sacc[mt][nt][2 + e]);
+                    }
                 }
-            }
-            rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 1));
-            rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 2));
-            rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 1));
-            rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 2));
-            const float mn0 = fmaxf(m0, rmax0), mn1 = fmaxf(m1, rmax1);
-            const float mu0 = mn0 == NEG_INF ? 0.f : mn0, mu1 = mn1 == NEG_INF ? 0.f : mn1;
-            const float a0 = exp2f(m0 - mu0), a1 = exp2f(m1 - mu1);
-            m0 = mn0; m1 = mn1;
-            float ps0 = 0.f, ps1 = 0.f;
+                rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 1));
+                rmax0 = fmaxf(rmax0, __shfl_xor_sync(0xffffffffu, rmax0, 2));
+                rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 1));
+                rmax1 = fmaxf(rmax1, __shfl_xor_sync(0xffffffffu, rmax1, 2));
+                const float mn0 = fmaxf(mrow[mt][0], rmax0), mn1 = fmaxf(mrow[mt][1], rmax1);
+                const float mu0 = mn0 == NEG_INF ? 0.f : mn0, mu1 = mn1 == NEG_INF ? 0.f : mn1;
+                const float a0 = exp2f(mrow[mt][0] - mu0), a1 = exp2f(mrow[mt][1] - mu1);
+                mrow[mt][0] = mn0; mrow[mt][1] = mn1;
+                float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-            for (int nt = 0; nt < PF_BN / 8; ++nt) {
+                for (int nt = 0; nt < PF_BN / 8; ++nt) {
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    sacc[nt][e] = exp2f(sacc[nt][e] - mu0);
-                    sacc[nt][2 + e] = exp2f(sacc[nt][2 + e] - mu1);
-                    ps0 += sacc[nt][e];
-                    ps1 += sacc[nt][2 + e];
+                    for (int e = 0; e < 2; ++e) {
+                        sacc[mt][nt][e] = exp2f(sacc[mt][nt][e] - mu0);
+                        sacc[mt][nt][2 + e] = exp2f(sacc[mt][nt][2 + e] - mu1);
+                        ps0 += sacc[mt][nt][e];
+                        ps1 += sacc[mt][nt][2 + e];
+                    }
                 }
-            }
-            l0 = l0 * a0 + ps0;
-            l1 = l1 * a1 + ps1;
+                lrow[mt][0] = lrow[mt][0] * a0 + ps0;
+                lrow[mt][1] = lrow[mt][1] * a1 + ps1;
 #pragma unroll
-            for (int nt = 0; nt < NT_O; ++nt) {
-                oacc[nt][0] *= a0; oacc[nt][1] *= a0; oacc[nt][2] *= a1; oacc[nt][3] *= a1;
+                for (int nt = 0; nt < NT_O; ++nt) {
+                    oacc[mt][nt][0] *= a0; oacc[mt][nt][1] *= a0; oacc[mt][nt][2] *= a1; oacc[mt][nt][3] *= a1;
+                }
+#pragma unroll
+                for (int kk = 0; kk < PF_BN / 16; ++kk) {
+                    pfrag[mt][kk][0] = pack_bf16(sacc[mt][2 * kk][0], sacc[mt][2 * kk][1]);
+                    pfrag[mt][kk][1] = pack_bf16(sacc[mt][2 * kk][2], sacc[mt][2 * kk][3]);
+                    pfrag[mt][kk][2] = pack_bf16(sacc[mt][2 * kk + 1][0], sacc[mt][2 * kk + 1][1]);
+                    pfrag[mt][kk][3] = pack_bf16(sacc[mt][2 * kk + 1][2], sacc[mt][2 * kk + 1][3]);
+                }
             }
 #pragma unroll
             for (int kk = 0; kk < PF_BN / 16; ++kk) {
-                uint32_t pa[4];
-                pa[0] = pack_bf16(sacc[2 * kk][0], sacc[2 * kk][1]);
-                pa[1] = pack_bf16(sacc[2 * kk][2], sacc[2 * kk][3]);
-                pa[2] = pack_bf16(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
-                pa[3] = pack_bf16(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
 #pragma unroll
                 for (int nt2 = 0; nt2 < NT_O / 2; ++nt2) {
                     uint32_t b[4];
-                    ldmatrix_x4_trans(b, vs_ + (kk * 16 + (j & 1) * 8 + r) * DP + nt2 * 16 + (j >> 1) * 8);
-                    mma_bf16(oacc[2 * nt2], pa, b[0], b[1]);
-                    mma_bf16(oacc[2 * nt2 + 1], pa, b[2], b[3]);
+                    ldmatrix_x4_trans(b, vs_ + (kk * 16 + (j & 1) * 8 + r8) * DP + nt2 * 16 + (j >> 1) * 8);
+#pragma unroll
+                    for (int mt = 0; mt < PF_MT; ++mt) {
+                        mma_bf16(oacc[mt][2 * nt2], pfrag[mt][kk], b[0], b[1]);
+                        mma_bf16(oacc[mt][2 * nt2 + 1], pfrag[mt][kk], b[2], b[3]);
+                    }
                 }
             }
         }
         __syncthreads();
     }
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
-    bf16* oa = out + (size_t)(n0 + ta) * out_stride + (size_t)(kvh * G + ra - ta * G) * D;
-    bf16* ob = out + (size_t)(n0 + tb) * out_stride + (size_t)(kvh * G + rb - tb * G) * D;
 #pragma unroll
-    for (int nt = 0; nt < NT_O; ++nt) {
-        const int d = nt * 8 + 2 * c;
-        if (va) *reinterpret_cast<uint32_t*>(oa + d) = pack_bf16(oacc[nt][0] * i0, oacc[nt][1] * i0);
-        if (vb) *reinterpret_cast<uint32_t*>(ob + d) = pack_bf16(oacc[nt][2] * i1, oacc[nt][3] * i1);
+    for (int mt = 0; mt < PF_MT; ++mt) {
+        float l0 = lrow[mt][0], l1 = lrow[mt][1];
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+        const int ra = wbase + 16 * mt + g, rb = ra + 8;
+        const int ta = ra / G, tb = rb / G;
+        bf16* oa = out + (size_t)(n0 + ta) * out_stride + (size_t)(kvh * G + ra - ta * G) * D;
+        bf16* ob = out + (size_t)(n0 + tb) * out_stride + (size_t)(kvh * G + rb - tb * G) * D;
+#pragma unroll
+        for (int nt = 0; nt < NT_O; ++nt) {
+            const int d = nt * 8 + 2 * c;
+            if (rvalid[mt][0]) *reinterpret_cast<uint32_t*>(oa + d) = pack_bf16(oacc[mt][nt][0] * i0, oacc[mt][nt][1] * i0);
+            if (rvalid[mt][1]) *reinterpret_cast<uint32_t*>(ob + d) = pack_bf16(oacc[mt][nt][2] * i1, oacc[mt][nt][3] * i1);
+        }
     }
 }
 
