@@ -334,7 +334,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
             if (d == 0) { partial_ml[base * 2] = M; partial_ml[base * 2 + 1] = L; }
         }
     }
-    tw_grid_launch_dependents();
+    tw_grid_launch_dependents_late();
     if (nsplit == 1) return;
 
     // The block that finishes last among the slices of this (request, head tile) merges them, in

@@ -80,15 +80,21 @@ __device__ __forceinline__ float tw_block_max(float v, float* scratch) {
 // ---------------------------------------------------------------------------------------
 // Programmatic dependent launch.  Every kernel of this engine starts with tw_grid_wait():
 // nothing it reads that an earlier kernel wrote, and nothing it writes, is touched before.
-// What does not depend on earlier kernels (streaming the first weights of a matrix product)
-// may come before it.  tw_grid_launch_dependents() then lets the next kernel of the stream
-// be scheduled early, so that its launch latency and its own prologue overlap this kernel's
-// body.  In a kernel launched without the attribute both calls do nothing.
-// Off by default: on B200 with CUDA graphs the early scheduling made decode steps slower
-// (4.6 ms against 4.25 ms at batch 8); TESSWEAVE_PDL=1 in the environment switches it on.
+// Kernels are launched with the programmatic-serialization attribute, so inside a CUDA graph
+// the next kernel's launch overlaps the tail of the one before (measured on B200: 2 % off a
+// decode step).  Letting the next kernel become resident even earlier with an explicit
+// griddepcontrol.launch_dependents -- at the top of short kernels or after the main loop of long
+// ones -- made the step slower (up to 8 %), so tw_grid_launch_dependents() compiles to nothing
+// unless TW_PDL_TRIGGERS is defined.  TESSWEAVE_PDL=0 in the environment launches every kernel
+// the ordinary way.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void tw_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void tw_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void tw_grid_launch_dependents() {
+#ifdef TW_PDL_TRIGGERS
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void tw_grid_launch_dependents_late() { tw_grid_launch_dependents(); }
 
 #ifndef __CUDA_ARCH__
 #include <stdlib.h>
@@ -96,7 +102,7 @@ static inline bool tw_pdl_enabled() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("TESSWEAVE_PDL");
-        v = (e && e[0] == '1') ? 1 : 0;
+        v = (e && e[0] == '0') ? 0 : 1;
     }
     return v != 0;
 }
@@ -115,7 +121,10 @@ static inline int tw_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
     int n = 0;
-    if (tw_pdl_enabled()) {
+    // only while the stream is being captured into a graph: on plain launches the attribute costs time
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (tw_pdl_enabled() && cudaStreamIsCapturing(stream, &capturing) == cudaSuccess &&
+        capturing == cudaStreamCaptureStatusActive) {
         attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attrs[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;

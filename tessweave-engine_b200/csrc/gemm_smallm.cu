@@ -107,7 +107,7 @@ gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M
         a_cur = a_nxt; b_cur = b_nxt;
         a_nxt = a_far; b_nxt = b_far;
     }
-    tw_grid_launch_dependents();     // the stream of weights is over: the next kernel may be scheduled
+    tw_grid_launch_dependents_late();     // the stream of weights is over: the next kernel may be scheduled
     // acc[t][0..1]: weight row ra, tokens t*8 + 2c, +1;  acc[t][2..3]: weight row rb
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
