@@ -240,6 +240,71 @@ def e2e_run(model, cfg, batch: int, context: int, steps: int, warmup: int):
             "generated": generated}
 
 
+WORKLOAD_SIZES = {
+    # layer sizes of the Qwen2.5-14B-sized and -32B-sized configurations
+    "continuous14b": dict(num_hidden_layers=48, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                          head_dim=128, intermediate_size=13824),
+    "prefix32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                      head_dim=128, intermediate_size=27648),
+}
+
+
+def workload_run(name: str, layers: int | None) -> dict:
+    """Two whole-engine workloads through ``Engine.submit`` / ``Engine.step`` with random weights:
+    continuous14b -- 32 requests, prompts of 128..2048 tokens, 64..512 generated tokens each, prompt
+                     portions of 512, continuous batching;
+    prefix32b     -- 16 requests with prompts of 8192 tokens that share their first 4096, 256 generated
+                     tokens each; the shared pages are computed once."""
+    import torch
+    import tessweave_engine_b200 as tw
+    from tessweave_engine_b200.parts.base import Runtime
+    sizes = dict(WORKLOAD_SIZES[name])
+    full_layers = sizes["num_hidden_layers"]
+    if layers:
+        sizes["num_hidden_layers"] = layers
+    config = dict(BENCH_CONFIG, **sizes)
+    cfg, spec = tw.resolve(config)
+    model = tw.Model(spec, Runtime(torch.device("cuda:0"), torch.bfloat16), config=cfg)
+    tw.fill_random(model, seed=0)
+    gen = torch.Generator().manual_seed(11)
+    rand = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=gen))
+    toks = lambda n: torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
+    if name == "continuous14b":
+        jobs = [(toks(rand(128, 2048)), rand(64, 512)) for _ in range(32)]
+        pages = sum(-(-(len(p) + m) // PAGE_SIZE) for p, m in jobs) + 8
+        engine = tw.Engine(model, tw.EngineConfig(block_size=PAGE_SIZE, kv_blocks=pages, max_context=2560, max_active=32,
+                                                  max_queue=32, prefill_chunk=512, max_step_tokens=512 + 32))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        reqs = [engine.submit(p, max_tokens=m, ignore_eos=True) for p, m in jobs]
+        engine.run_until_done()
+    else:
+        shared = toks(4096)
+        jobs = [(shared + toks(4096), 256) for _ in range(16)]
+        pages = 4096 // PAGE_SIZE + 16 * (-(-(4096 + 256) // PAGE_SIZE)) + 8
+        engine = tw.Engine(model, tw.EngineConfig(block_size=PAGE_SIZE, kv_blocks=pages, max_context=8192 + 256,
+                                                  max_active=16, max_queue=16, prefill_chunk=2048,
+                                                  max_step_tokens=2048 + 16))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        reqs = [engine.submit(jobs[0][0], max_tokens=256, ignore_eos=True)]
+        while reqs[0].computed < 4096:           # the owner of the prefix computes it first
+            engine.step()
+        reqs += [engine.submit(p, max_tokens=m, ignore_eos=True) for p, m in jobs[1:]]
+        engine.run_until_done()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    stats = engine.stats()
+    engine.close()
+    generated = sum(len(r.output) for r in reqs)
+    return {"workload": name, "impl": "ours", "layers": sizes["num_hidden_layers"], "layers_full": full_layers,
+            "requests": len(reqs), "prompt_tokens": sum(len(p) for p, _ in jobs), "generated_tokens": generated,
+            "prefill_tokens_computed": stats["prefill_tokens"], "prefix_hit_tokens": stats["prefix_hit_tokens"],
+            "steps": stats["steps"], "seconds": round(seconds, 3), "generated_tok_s": round(generated / seconds, 1),
+            "total_tok_s": round((generated + stats["prefill_tokens"]) / seconds, 1),
+            "finished": stats["finished"], "weights_gb": round(model.weight_bytes() / 1e9, 2)}
+
+
 def reference_arm(args) -> int:
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "flow_engine").exists():
@@ -267,6 +332,8 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one small measurement and print its figures (for profiling a kernel on a small case)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    ap.add_argument("--workload", choices=sorted(WORKLOAD_SIZES), default=None,
+                    help="run a whole-engine workload at 14B / 32B layer sizes instead of the headline measurement")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU engine")
@@ -279,6 +346,9 @@ def main() -> int:
     if not torch.cuda.is_available():
         print("bench.py needs a CUDA device", file=sys.stderr)
         return 1
+    if args.workload:
+        print(json.dumps(workload_run(args.workload, args.layers if args.layers != BENCH_CONFIG["num_hidden_layers"] else None)))
+        return 0
     pk, pk_source = peaks()
     model, cfg = build_model(args.layers)
     if args.only == "prefill":

@@ -395,7 +395,18 @@ class Engine:
 
     # ------------------------------------------------------------------ convenience
     def run_until_done(self, limit: int = 1_000_000) -> None:
+        """Step until nothing is left to do, acting as the consumer of every request's events
+        (the bounded queues would otherwise end long generations with "Consumer too slow");
+        tokens stay available in ``request.output``."""
         for _ in range(limit):
-            if not self.step():
+            busy = self.step()
+            with self.lock:
+                for r in list(self.requests.values()):
+                    while not r.events.empty():
+                        try:
+                            r.events.get_nowait()
+                        except queue.Empty:
+                            break
+            if not busy:
                 return
         raise RuntimeError("the engine did not come to rest")
