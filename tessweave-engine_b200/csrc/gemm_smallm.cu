@@ -38,7 +38,10 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
     return v;
 }
 
-constexpr int WARPS = 8;
+#ifndef TW_GEMM_WARPS
+#define TW_GEMM_WARPS 4
+#endif
+constexpr int WARPS = TW_GEMM_WARPS;
 constexpr int ROWS_PER_BLOCK = WARPS * 16;
 constexpr int CHUNK = 64;      // values of k per step: a thread reads 32 contiguous bytes of each of its rows
 
