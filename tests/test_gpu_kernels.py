@@ -474,3 +474,16 @@ def test_gemm_tcgen05(m, n, k, swap):
         ops().gemm_tcgen05(slices, x, w, m, st, kper=kper, swap=swap)
         assert torch.allclose(slices.sum(0), want, **tol)
     assert int(st) == 0
+
+
+def test_decode_attention_many_pages_per_block():
+    """Pages of 4 tokens and one slice: a block walks 375 block-table entries, more than it keeps
+    in shared memory, so the entries beyond come straight from the table."""
+    hq, hkv, d = 6, 3, 32
+    setup = paged_setup([1500, 9], 4, hkv, d, torch.bfloat16, seed=11)
+    rows_of = [[1499], [8]]
+    q = torch.randn(2, hq, d, generator=torch.Generator().manual_seed(3))
+    got, qr = run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, 0, nsplit=1)
+    for i, r in enumerate(rows_of):
+        k = setup["k"][i].to(torch.bfloat16).float(); v = setup["v"][i].to(torch.bfloat16).float()
+        assert torch.allclose(got[i:i + 1], dense_attention(qr[i:i + 1], k, v, r), **TOL["bfloat16"])
