@@ -230,6 +230,12 @@ class ModelRunner:
         return self._graphs[bucket]
 
     def _graph_step(self, entries: list[StepEntry], bucket: int) -> torch.Tensor:
+        if not self._graphs:
+            # capture every bucket at the first decode step, so that a batch that shrinks or grows
+            # later does not pay for a capture in the middle of generation
+            for b in GRAPH_BUCKETS:
+                if b <= self.max_seqs:
+                    self._capture(b)
         graph, logits = self._graphs.get(bucket) or self._capture(bucket)
         wanted = [i for i, e in enumerate(entries) if e.want]
         for e in entries:
