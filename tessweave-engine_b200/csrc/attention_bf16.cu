@@ -5,8 +5,11 @@
 //   * decode:  requests that bring ONE token.  A block serves one (request, key/value head,
 //     slice of the keys); the query heads of the group are the columns of one MMA tile, so keys
 //     and values are read once for the whole group.  The keys are split over blocks
-//     ("split-KV"); partial results (fp32 accumulator, running maximum, sum) go to scratch
-//     memory, and the block that finishes last merges them in slice order.
+//     ("split-KV").  Up to 16 slices form one thread-block cluster: the partial results (fp32
+//     accumulator, running maximum, sum) stay in shared memory and every block of the cluster
+//     merges its share of the outputs by reading its neighbours' shared memory.  With more
+//     slices the partial results go to scratch memory and the block that finishes last merges
+//     them.  Both merge in slice order.
 //   * prefill: requests that bring several tokens.  A block serves 128 rows (64 for head sizes
 //     above 128), a row being a (token, query head of the group) pair, and walks the keys up
 //     to the last visible one; a warp holds two 16-row tiles, so that every key and value
@@ -18,6 +21,9 @@
 //   score = (q . k) * scale,  visible iff  position - window < p <= position
 // Reference: flow_engine/model.py:193-200 and flow_engine/kernels/paged_decode.py:13-43.
 #include "common.cuh"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 #ifndef TW_HEAD_DIM
 #define TW_HEAD_DIM 128
@@ -103,6 +109,9 @@ constexpr int DEC_SMEM = DEC_SMEM_STAGES + DEC_SMEM_OFFS + DEC_PAGE_CACHE * 4;
 constexpr int DB32 = D / 32;                                  // whole 32-wide blocks of d
 constexpr bool DTAIL16 = (D % 32) != 0;                       // plus one 16-wide block
 constexpr int MT_O = D / 16;                                  // m-tiles of O^T
+constexpr int DEC_MAX_CLUSTER = 16;                           // slices that can merge through distributed shared memory
+// after the last tile the stage buffers hold the warps' partial results and this block's merged slice
+static_assert((DEC_WARPS + 1) * DEC_HEADS * (D + 2) * 4 <= DEC_SMEM_STAGES, "merge area must fit the stage buffers");
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
     uint32_t r;
@@ -122,6 +131,7 @@ struct KFrag {                    // the d values of one key row this thread fee
     uint2 tail;
 };
 
+template <bool CLUSTER>
 __global__ void __launch_bounds__(DEC_WARPS * 32, (D <= 128 ? 4 : 2))
 attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
                    const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
@@ -309,6 +319,8 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         mml[(warp * DEC_HEADS + 2 * c) * 2] = m0; mml[(warp * DEC_HEADS + 2 * c) * 2 + 1] = l0;
         mml[(warp * DEC_HEADS + 2 * c + 1) * 2] = m1; mml[(warp * DEC_HEADS + 2 * c + 1) * 2 + 1] = l1;
     }
+    float* part_o = mml + DEC_WARPS * DEC_HEADS * 2;             // [heads][D]: this block's slice, for the cluster
+    float* part_ml = part_o + DEC_HEADS * D;                     // [heads][2]
     __syncthreads();
     for (int idx = threadIdx.x; idx < nheads * D; idx += DEC_WARPS * 32) {
         const int row = idx / D, d = idx - row * D;
@@ -328,6 +340,9 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         const int head = kvh * G + h0 + row;
         if (nsplit == 1) {
             out[(size_t)n * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+        } else if (CLUSTER) {
+            part_o[row * D + d] = o;
+            if (d == 0) { part_ml[row * 2] = M; part_ml[row * 2 + 1] = L; }
         } else {
             const size_t base = ((size_t)s * Hq + head) * nsplit + split;
             partial_o[base * D + d] = o;
@@ -336,6 +351,30 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
     }
     tw_grid_launch_dependents_late();
     if (nsplit == 1) return;
+
+    if constexpr (CLUSTER) {
+        // The slices of this (request, head tile) are the blocks of one cluster, slice i being block
+        // i.  Every block merges its share of the outputs, reading all slices in slice order:
+        //   out = sum_i o_i 2^(m_i - M) / sum_i l_i 2^(m_i - M)
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        for (int idx = split * (DEC_WARPS * 32) + threadIdx.x; idx < nheads * D; idx += nsplit * (DEC_WARPS * 32)) {
+            const int row = idx / D, d = idx - row * D;
+            float M = NEG_INF;
+            for (int i = 0; i < nsplit; ++i) M = fmaxf(M, *cluster.map_shared_rank(part_ml + row * 2, i));
+            float L = 0.f, o = 0.f;
+            for (int i = 0; i < nsplit; ++i) {
+                const float* ml = cluster.map_shared_rank(part_ml + row * 2, i);
+                const float mi = ml[0];
+                const float f = (mi == NEG_INF || M == NEG_INF) ? 0.f : exp2f(mi - M);
+                L += ml[1] * f;
+                o += *cluster.map_shared_rank(part_o + row * D + d, i) * f;
+            }
+            out[(size_t)n * out_stride + (size_t)(kvh * G + h0 + row) * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+        }
+        cluster.sync();          // nobody leaves while a neighbour may still read its shared memory
+        return;
+    }
 
     // The block that finishes last among the slices of this (request, head tile) merges them, in
     // slice order, so the result does not depend on which block that is:
@@ -374,22 +413,37 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         lsum[idx] *= f;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < nheads * D; idx += DEC_WARPS * 32) {
-        const int row = idx / D, d = idx - row * D;
+    // four values of d per thread and eight slices in flight at once: the merge is a chain of
+    // L2 round trips on one block while the rest of the GPU waits, so it is kept short
+    constexpr int D4 = D / 4;
+    for (int idx = threadIdx.x; idx < nheads * D4; idx += DEC_WARPS * 32) {
+        const int row = idx / D4, d4 = idx - row * D4;
         const float* f = fac + row * nsplit;
-        const float* po = partial_o + (group_base + (size_t)row * nsplit) * D + d;
-        float L = 0.f, o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+        const float4* po = reinterpret_cast<const float4*>(partial_o + (group_base + (size_t)row * nsplit) * D) + d4;
+        float L = 0.f;
         for (int i = 0; i < nsplit; ++i) L += lsum[row * nsplit + i];
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
         int i = 0;
-        for (; i + 4 <= nsplit; i += 4) {          // four independent loads in flight; fixed order of the sums
-            o0 += __ldcg(po + (size_t)i * D) * f[i];
-            o1 += __ldcg(po + (size_t)(i + 1) * D) * f[i + 1];
-            o2 += __ldcg(po + (size_t)(i + 2) * D) * f[i + 2];
-            o3 += __ldcg(po + (size_t)(i + 3) * D) * f[i + 3];
+        for (; i + 8 <= nsplit; i += 8) {          // fixed order of the sums: slice 0, 1, 2, ...
+            float4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __ldcg(po + (size_t)(i + j) * D4);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float fj = f[i + j];
+                o.x += v[j].x * fj; o.y += v[j].y * fj; o.z += v[j].z * fj; o.w += v[j].w * fj;
+            }
         }
-        for (; i < nsplit; ++i) o0 += __ldcg(po + (size_t)i * D) * f[i];
-        const float o = (o0 + o1) + (o2 + o3);
-        out[(size_t)n * out_stride + (size_t)(kvh * G + h0 + row) * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+        for (; i < nsplit; ++i) {
+            const float4 v = __ldcg(po + (size_t)i * D4);
+            const float fj = f[i];
+            o.x += v.x * fj; o.y += v.y * fj; o.z += v.z * fj; o.w += v.w * fj;
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        uint2 packed;
+        packed.x = pack_bf16(o.x * inv, o.y * inv);
+        packed.y = pack_bf16(o.z * inv, o.w * inv);
+        *reinterpret_cast<uint2*>(out + (size_t)n * out_stride + (size_t)(kvh * G + h0 + row) * D + 4 * d4) = packed;
     }
 }
 
@@ -627,7 +681,11 @@ bool g_attrs_set = false;
 
 int set_attrs() {
     if (g_attrs_set) return 0;
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
     if (e != cudaSuccess) return (int)e;
@@ -635,9 +693,37 @@ int set_attrs() {
     return 0;
 }
 
+// Whether clusters of `size` decode blocks can be resident on this GPU (asked once per size).
+int g_cluster_ok[DEC_MAX_CLUSTER + 1];          // 0 = not asked yet, 1 = yes, -1 = no
+
+bool decode_cluster_ok(int size) {
+    if (size < 2 || size > DEC_MAX_CLUSTER) return false;
+    if (g_cluster_ok[size] == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(size);
+        cfg.blockDim = dim3(DEC_WARPS * 32);
+        cfg.dynamicSmemBytes = DEC_SMEM;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = size;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, attn_decode_kernel<true>, &cfg);
+        if (e != cudaSuccess) (void)cudaGetLastError();
+        g_cluster_ok[size] = (e == cudaSuccess && clusters >= 1) ? 1 : -1;
+    }
+    return g_cluster_ok[size] > 0;
+}
+
 }  // namespace
 
 TW_EXPORT int tw_attn_head_dim() { return D; }
+
+// Most slices that merge through a cluster; more go through scratch memory.
+TW_EXPORT int tw_attn_decode_cluster_slices() { return DEC_MAX_CLUSTER; }
 
 // Scratch floats the decode kernel needs for `n_seqs` requests: partial accumulators, then (max, sum) pairs.
 // Beside them it needs one int32 counter per (request, key/value head, tile of 8 heads), zero before the
@@ -649,16 +735,23 @@ TW_EXPORT long long tw_attn_decode_scratch_floats(int n_seqs, int Hq, int nsplit
 TW_EXPORT int tw_attn_decode(void* out, int out_stride, const void* q, int q_stride, const int* seq_q_start,
                              const int* seq_q_len, const int* seq_kv_len, const int* seq_slot, const int* block_table,
                              int table_stride, const void* k_cache, const void* v_cache, int n_seqs, int Hq, int Hkv,
-                             int page_size, int num_pages, int window, float scale, int nsplit, float* scratch,
-                             int* counters, int* status, cudaStream_t stream) {
+                             int page_size, int num_pages, int window, float scale, int nsplit, int flags,
+                             float* scratch, int* counters, int* status, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv || nsplit < 1 || (nsplit > 1 && (!scratch || !counters))) return (int)cudaErrorInvalidValue;
+    // the merge reads the partial results 16 bytes at a time and writes 8 bytes of the result at a time
+    if (((uintptr_t)out & 7) || (out_stride & 3) || ((uintptr_t)scratch & 15)) return (int)cudaErrorMisalignedAddress;
     if (int e = set_attrs()) return e;
     const int G = Hq / Hkv, htiles = (G + DEC_HEADS - 1) / DEC_HEADS;
     float* partial_o = scratch;
     float* partial_ml = scratch ? scratch + (size_t)n_seqs * Hq * nsplit * D : nullptr;
     dim3 grid(nsplit * htiles, Hkv, n_seqs);
-    tw_launch(attn_decode_kernel, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
+    if (nsplit > 1 && !(flags & 1) && decode_cluster_ok(nsplit))
+        return tw_launch(attn_decode_kernel<true>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, nsplit,
+            (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
+            table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
+            scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status);
+    tw_launch(attn_decode_kernel<false>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
         (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
         scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status);
@@ -709,6 +802,7 @@ TW_EXPORT int tw_attn_decode_static(void* out, int out_stride, const void* q, in
     g_static_error[0] = 0;
     if (n_seqs <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv || nsplit < 1) return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)out & 7) || (out_stride & 3)) return (int)cudaErrorMisalignedAddress;
     const int G = Hq / Hkv, htiles = (G + DEC_HEADS - 1) / DEC_HEADS;
     const size_t partial_bytes = sizeof(float) * (size_t)n_seqs * Hq * nsplit * (D + 2);
     const size_t counter_bytes = sizeof(int) * (size_t)n_seqs * Hkv * htiles;
@@ -746,7 +840,7 @@ TW_EXPORT int tw_attn_decode_static(void* out, int out_stride, const void* q, in
     e = cudaMemsetAsync(counters, 0, counter_bytes, stream);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(nsplit * htiles, Hkv, n_seqs);
-    tw_launch(attn_decode_kernel, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
+    tw_launch(attn_decode_kernel<false>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
         (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
         scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status);

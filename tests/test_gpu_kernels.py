@@ -290,7 +290,7 @@ def test_sample_greedy_and_temperature():
 TC_CASES = [(8, 8, 16), (8, 2, 32), (8, 1, 64), (6, 3, 48), (28, 4, 128), (4, 2, 256), (3, 1, 80), (40, 2, 64)]
 
 
-def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None):
+def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None, merge_in_scratch=False):
     """rows_of: request -> the consecutive positions it brings; the request holds exactly
     positions 0..last.  Requests with one row go through the decode kernel."""
     o = ops()
@@ -315,7 +315,8 @@ def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None
         for _ in range(2):      # twice: the counters must come back to zero
             out.fill_(float("nan")) if not any(len(r) > 1 for r in rows_of) else None
             o.attention_decode(out, qd, q_start, q_len, kv_len, slot, setup["table"], setup["k_pages"], setup["v_pages"],
-                               len(rows_of), hq, hkv, d, window, d ** -0.5, ns, scratch, counters, st)
+                               len(rows_of), hq, hkv, d, window, d ** -0.5, ns, scratch, counters, st,
+                               merge_in_scratch=merge_in_scratch)
         assert int(counters.abs().sum()) == 0
     assert int(st) == 0
     return out.float().cpu().reshape(n, hq, d), qd.float().cpu().reshape(n, hq, d)
@@ -342,15 +343,17 @@ def test_tensor_core_attention_mixed_rows(hq, hkv, d, window):
         cursor += len(r)
 
 
-@pytest.mark.parametrize("nsplit", [1, 2, 7, 64])
-def test_decode_attention_any_split(nsplit):
-    """The split count must not matter, also when most slices are empty."""
+@pytest.mark.parametrize("merge_in_scratch", [False, True])
+@pytest.mark.parametrize("nsplit", [1, 2, 7, 16, 17, 64])
+def test_decode_attention_any_split(nsplit, merge_in_scratch):
+    """The split count must not matter, also when most slices are empty; neither may the way the
+    slices are merged (inside a cluster up to 16 slices, through scratch memory beyond)."""
     hq, hkv, d = 14, 2, 64
     lengths = [5, 64, 65, 1000]
     setup = paged_setup(lengths, 16, hkv, d, torch.bfloat16, seed=9)
     rows_of = [[n - 1] for n in lengths]
     q = torch.randn(4, hq, d, generator=torch.Generator().manual_seed(1))
-    got, qr = run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, 0, nsplit=nsplit)
+    got, qr = run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, 0, nsplit=nsplit, merge_in_scratch=merge_in_scratch)
     for i, r in enumerate(rows_of):
         k = setup["k"][i].to(torch.bfloat16).float(); v = setup["v"][i].to(torch.bfloat16).float()
         assert torch.allclose(got[i:i + 1], dense_attention(qr[i:i + 1], k, v, r), **TOL["bfloat16"]), f"request {i}"
