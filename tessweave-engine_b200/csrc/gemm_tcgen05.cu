@@ -24,98 +24,18 @@
 //
 // The reference runs these products through a library (nn.Linear: flow_engine/model.py:54,
 // 76-80,201,204).
-#include "common.cuh"
-
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
+#include "tcgen05.cuh"
 
 namespace {
 
-typedef __nv_bfloat16 bf16;
+using namespace tc5;
 
 constexpr int BM = 128;            // rows of the A tile = TMEM lanes
 constexpr int BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 128;
-constexpr long long WAIT_CYCLES = 2000000000ll;      // bound of every mbarrier wait
 
 enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_PARTIAL = 2 };
-
-// ---- PTX wrappers ------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false (and the error bit set) if the phase did not complete in time.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long start = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - start > WAIT_CYCLES) {
-            atomicOr(status, TW_ERR_WAIT);
-            return false;
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols));
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a [rows][64] bf16 tile written by TMA with the 128-byte
-// swizzle: K-major, rows 128 bytes apart, groups of 8 rows 1024 bytes apart (stride byte offset),
-// leading byte offset 1 (unused for swizzled K-major), descriptor version 1, layout SWIZZLE_128B.
-__device__ __forceinline__ uint64_t smem_desc(const void* tile, int k_byte_offset) {
-    const uint32_t addr = smem_u32(tile) + k_byte_offset;
-    return (uint64_t)((addr & 0x3FFFF) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor: D fp32, A and B bf16, both K-major, N = bn, M = 128, dense, no negate.
-__device__ __forceinline__ uint32_t instr_desc(int bn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
 
 template <int BN> struct Config {
     static constexpr int A_BYTES = BM * BK * 2;
@@ -263,61 +183,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
-}
-
-// ---- host side: tensor maps -----------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; int rows, k, box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& m) const {
-        return std::hash<const void*>()(m.ptr) ^ (size_t)m.rows * 1000003u ^ (size_t)m.k * 7919u ^ (size_t)m.box_rows * 31u;
-    }
-};
-std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
-std::mutex g_maps_mutex;
-
-// A [rows, k] bf16 matrix with k contiguous, read in boxes of [box_rows, 64] with the 128-byte swizzle;
-// what lies outside the matrix reads as zero.
-int get_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out) {
-    std::lock_guard<std::mutex> lock(g_maps_mutex);
-    const MapKey key{ptr, rows, k, box_rows};
-    auto it = g_maps.find(key);
-    if (it != g_maps.end()) { *out = it->second; return 0; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return (int)cudaErrorNotSupported;
-    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUtensorMap m;
-    const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return 1000 + (int)r;
-    if (g_maps.size() > 4096) g_maps.clear();
-    g_maps[key] = m;
-    *out = m;
-    return 0;
 }
 
 template <int BN>

@@ -254,6 +254,31 @@ def tensor_core_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
 
 
+def tcgen05_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    """The tcgen05 prefill attention takes bfloat16, head sizes 64 and 128, and pages of at least
+    8 keys that divide a tile of 128 keys or are a multiple of it."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and page_size >= 8
+            and (128 % page_size == 0 or page_size % 128 == 0))
+
+
+TCGEN05_ATTENTION_MIN_TOKENS = 128
+
+
+def prefer_tcgen05_attention(dtype: torch.dtype, head_dim: int, page_size: int, max_q_len: int) -> bool:
+    """Whether a step whose longest portion has ``max_q_len`` tokens runs its prompt attention on
+    the tcgen05 kernel.  TESSWEAVE_PREFILL_ATTENTION=mma|tcgen05 forces one of the two (the latter
+    only for shapes the kernel takes)."""
+    import os
+    if not tcgen05_attention_supported(dtype, head_dim, page_size):
+        return False
+    forced = os.environ.get("TESSWEAVE_PREFILL_ATTENTION")
+    if forced == "mma":
+        return False
+    if forced == "tcgen05":
+        return True
+    return max_q_len >= TCGEN05_ATTENTION_MIN_TOKENS
+
+
 def decode_splits(n_seqs: int, n_kv_heads: int, group: int, max_kv_len: int) -> int:
     """How many slices the keys of a request are cut into, so that the launch fills the GPU.
     Up to 16 slices merge inside a thread-block cluster, which saves 2-3 us over the merge through
@@ -323,6 +348,24 @@ def attention_decode(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block
         c_int(window), c_float(scale), c_int(nsplit), c_int(1 if merge_in_scratch else 0), _ptr(scratch), _ptr(counters),
         _ptr(status), _stream())
     _check(code, "attention_decode")
+
+
+def attention_prefill_tcgen05(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, n_seqs,
+                              max_q_len, n_q_heads, n_kv_heads, head_dim, window, scale, skip_single, status) -> None:
+    """The same as ``attention_prefill`` on the 5th-generation tensor cores (TMA, tcgen05.mma,
+    accumulators in tensor memory), for the shapes ``tcgen05_attention_supported`` names."""
+    _cuda(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, status)
+    _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim)
+    _need(tcgen05_attention_supported(q.dtype, head_dim, k_pages.shape[2]),
+          f"tcgen05 attention does not take head size {head_dim} with pages of {k_pages.shape[2]} keys")
+    _need(q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0,
+          "tcgen05 attention: rows of q and out must be 16-byte aligned")
+    code = _fn("attention_tcgen05", "tw_attn_prefill_tc5", {"TW_HEAD_DIM": head_dim})(
+        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(seq_q_start), _ptr(seq_q_len),
+        _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages),
+        c_int(n_seqs), c_int(max_q_len), c_int(n_q_heads), c_int(n_kv_heads), c_int(k_pages.shape[2]),
+        c_int(k_pages.shape[0]), c_int(window), c_float(scale), c_int(1 if skip_single else 0), _ptr(status), _stream())
+    _check(code, "attention_prefill_tcgen05")
 
 
 def attention_prefill(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, n_seqs,

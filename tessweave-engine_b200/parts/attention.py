@@ -89,7 +89,12 @@ class GQAAttention(Mixer):
         window = self.window or 0
         singles = ctx.decode_only or ctx.fixed_shape or any(n == 1 for n in ctx.host_q_len)
         if not ctx.decode_only:
-            ops.attention_prefill(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
+            # long portions: tcgen05 kernel (TMA, accumulators in tensor memory); short ones, and the shapes it
+            # does not take, stay on the mma.sync kernel, which starts faster
+            prefill = ops.attention_prefill
+            if ops.prefer_tcgen05_attention(self.runtime.dtype, self.head_dim, cache.k_pages.shape[2], ctx.max_q_len):
+                prefill = ops.attention_prefill_tcgen05
+            prefill(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
                                   cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, ctx.max_q_len,
                                   self.n_heads, self.n_kv_heads, self.head_dim, window, self.scale, singles, ctx.status)
         if singles:

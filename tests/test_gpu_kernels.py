@@ -290,7 +290,7 @@ def test_sample_greedy_and_temperature():
 TC_CASES = [(8, 8, 16), (8, 2, 32), (8, 1, 64), (6, 3, 48), (28, 4, 128), (4, 2, 256), (3, 1, 80), (40, 2, 64)]
 
 
-def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None, merge_in_scratch=False):
+def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None, merge_in_scratch=False, tcgen05=False):
     """rows_of: request -> the consecutive positions it brings; the request holds exactly
     positions 0..last.  Requests with one row go through the decode kernel."""
     o = ops()
@@ -305,7 +305,8 @@ def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None
     st = status()
     singles = any(len(r) == 1 for r in rows_of)
     if any(len(r) > 1 for r in rows_of):
-        o.attention_prefill(out, qd, q_start, q_len, kv_len, slot, setup["table"], setup["k_pages"], setup["v_pages"],
+        prefill = o.attention_prefill_tcgen05 if tcgen05 else o.attention_prefill
+        prefill(out, qd, q_start, q_len, kv_len, slot, setup["table"], setup["k_pages"], setup["v_pages"],
                             len(rows_of), max(len(r) for r in rows_of), hq, hkv, d, window, d ** -0.5, singles, st)
     if singles:
         max_kv = max(r[-1] + 1 for r in rows_of)
@@ -389,6 +390,86 @@ def test_tensor_core_attention_finds_one_far_key(kind, where):
     assert torch.allclose(got, want, **TOL["bfloat16"])
     hit = (got[0, 0] - marker).abs().max() < 0.5
     assert bool(hit) == (where != "window_edge_outside")
+
+
+# ---------------------------------------------------------------------------
+# tcgen05 attention for prompt portions (TMA, accumulators and probabilities in tensor memory)
+# ---------------------------------------------------------------------------
+TC5_CASES = [
+    # hq, hkv, d, page, lengths, rows of each request, window
+    (1, 1, 64, 16, [100], [(0, 100)], 0),                                   # one tile of keys, one tile of rows
+    (2, 1, 128, 16, [300], [(0, 300)], 0),                                  # several tiles, both row tiles
+    (28, 4, 128, 16, [300, 65, 257], [(0, 300), (0, 65), (200, 257)], 0),   # groups of 7: rows of a token straddle tiles
+    (28, 4, 128, 16, [700], [(100, 700)], 200),                             # a window that drops whole tiles
+    (8, 1, 64, 32, [1000, 130], [(0, 1000), (128, 130)], 0),                # a two-token portion beside a long one
+    (6, 2, 128, 128, [513], [(0, 513)], 0),                                 # a page = a tile
+    (6, 2, 64, 256, [513], [(0, 513)], 24),                                 # a page = two tiles
+    (6, 2, 64, 8, [513], [(500, 513)], 0),                                  # sixteen pages to a tile
+    (5, 5, 128, 16, [1200], [(0, 1200)], 0),                                # no grouping
+]
+
+
+@pytest.mark.parametrize("hq,hkv,d,page,lengths,spans,window", TC5_CASES)
+def test_tcgen05_attention(hq, hkv, d, page, lengths, spans, window):
+    """Freed and unused cache slots hold NaN here, so a value row past a request's end that
+    reached a product would show."""
+    setup = paged_setup(lengths, page, hkv, d, torch.bfloat16, seed=hq * 10 + d)
+    rows_of = [list(range(a, b)) for a, b in spans]
+    n = sum(len(r) for r in rows_of)
+    q = torch.randn(n, hq, d, generator=torch.Generator().manual_seed(5))
+    got, qr = run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, tcgen05=True)
+    cursor = 0
+    for i, r in enumerate(rows_of):
+        k = setup["k"][i].to(torch.bfloat16).float(); v = setup["v"][i].to(torch.bfloat16).float()
+        want = dense_attention(qr[cursor:cursor + len(r)], k, v, r, window or None)
+        assert torch.allclose(got[cursor:cursor + len(r)], want, **TOL["bfloat16"]), f"request {i}"
+        cursor += len(r)
+
+
+@pytest.mark.parametrize("where", ["first_of_page", "last_of_page", "position_zero", "tile_edge", "next_tile",
+                                   "window_edge_inside", "window_edge_outside"])
+def test_tcgen05_attention_finds_one_far_key(where):
+    """One dominating key among 700, at a page's first and last slot, at both sides of a 128-key
+    tile's edge, at position 0 and at both sides of a window's edge.  Scores that large also
+    make the rows' maxima jump, so the accumulator in tensor memory is rescaled."""
+    hq, hkv, d, page, n = 4, 2, 128, 16, 700
+    window = 0
+    rows = list(range(n - 40, n))
+    pos = rows[0]
+    target = {"first_of_page": 16 * 7, "last_of_page": 16 * 9 + 15, "position_zero": 0, "tile_edge": 127,
+              "next_tile": 128}.get(where)
+    if where.startswith("window_edge"):
+        window = 300
+        target = pos - window + 1 if where.endswith("inside") else pos - window
+    setup = paged_setup([n], page, hkv, d, torch.bfloat16, seed=3)
+    direction = torch.randn(d, generator=torch.Generator().manual_seed(2)); direction /= direction.norm()
+    q = torch.randn(len(rows), hq, d) * 0.1
+    q[0, :] = direction * 12.0
+    kp, vp = setup["k_pages"], setup["v_pages"]
+    pid = int(setup["table"][setup["slots"][0], target // page])
+    kp[pid, :, target % page] = (direction * 12.0).to(torch.bfloat16).cuda()
+    marker = torch.arange(d, dtype=torch.float32) / d + 2.0
+    vp[pid, :, target % page] = marker.to(torch.bfloat16).cuda()
+    got, qr = run_tensor_core_attention(setup, [rows], q, hq, hkv, d, window, tcgen05=True)
+    k = setup["k"][0].clone(); v = setup["v"][0].clone()
+    k[target] = direction * 12.0; v[target] = marker
+    want = dense_attention(qr, k.to(torch.bfloat16).float(), v.to(torch.bfloat16).float(), rows, window or None)
+    assert torch.allclose(got, want, **TOL["bfloat16"])
+    hit = (got[0, 0] - marker).abs().max() < 0.5
+    assert bool(hit) == (where != "window_edge_outside")
+
+
+def test_tcgen05_attention_refuses_other_shapes():
+    o = ops()
+    assert not o.tcgen05_attention_supported(torch.bfloat16, 80, 16)
+    assert not o.tcgen05_attention_supported(torch.bfloat16, 128, 48)
+    assert not o.tcgen05_attention_supported(torch.float32, 128, 16)
+    setup = paged_setup([40], 16, 1, 32, torch.bfloat16)
+    q = dev(torch.randn(40, 32), torch.bfloat16)
+    i32 = lambda v: dev(torch.tensor(v, dtype=torch.int32))
+    with pytest.raises(Exception, match="tcgen05 attention"):
+        o.attention_prefill_tcgen05(torch.empty_like(q), q, i32([0]), i32([40]), i32([40]), i32(setup["slots"]), setup["table"],
+                                    setup["k_pages"], setup["v_pages"], 1, 40, 1, 1, 32, 0, 32 ** -0.5, False, status())
 
 
 # ---------------------------------------------------------------------------
