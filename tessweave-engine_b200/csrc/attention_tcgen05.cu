@@ -54,10 +54,48 @@ constexpr int O_COL = 256;
 constexpr float RESCALE_THRESHOLD = 8.f;      // log2 units
 #define NEG_INF (-INFINITY)
 
+// -DTW_TRACE: block (0, 0, 0) records clock64() at the hand-over points of its roles, for a
+// timeline of one block (tw_attn_tc5_trace_ptr gives the buffer).  Off in the product.
+#ifdef TW_TRACE
+constexpr int TRACE_SLOTS = 12, TRACE_TILES = 80, TRACE_ROLES = 10;     // a role = a warp
+__device__ long long g_trace[TRACE_ROLES * TRACE_TILES * TRACE_SLOTS];
+#define TW_TRACE_AT(role, tile, slot)                                                              \
+    do {                                                                                           \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) < TRACE_TILES)         \
+            g_trace[((role) * TRACE_TILES + (tile)) * TRACE_SLOTS + (slot)] = clock64();           \
+    } while (0)
+#else
+#define TW_TRACE_AT(role, tile, slot) do {} while (0)
+#endif
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// (a0, a1) * b + c and (a0, a1) + (b0, b1) as one packed instruction each
+__device__ __forceinline__ float2 fma2(float a0, float a1, float b, float c) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -90,6 +128,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int pos_first = pos0 + row0 / G, pos_last = pos0 + (row_end - 1) / G;
     const int j_begin = (window > 0 && pos_first - window + 1 > 0) ? (pos_first - window + 1) / BN : 0;
     const int ntiles = pos_last / BN + 1 - j_begin;
+    const int tail_rows = max(0, (j_begin + ntiles) * BN - kv_len);  // rows of the last tile that hold no key
 
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* q_s = tiles;                                      // [NQ][KB][128 rows][128 B]
@@ -102,7 +141,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     uint64_t* s_full = v_empty + KV_STAGES;                          // S of tile X is complete
     uint64_t* p_full = s_full + NQ;                                  // P of tile X is written, S read, O rescaled
     uint64_t* o_done = p_full + NQ;                                  // the P V products of tile X so far have retired
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + NQ);
+    uint64_t* v_fixed = o_done + NQ;                                 // value rows past the last key are zeroed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(v_fixed + 1);
     volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -111,7 +151,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
         }
-        for (int x = 0; x < NQ; ++x) { mbar_init(&s_full[x], 1); mbar_init(&p_full[x], BM); mbar_init(&o_done[x], 1); }
+        for (int x = 0; x < NQ; ++x) { mbar_init(&s_full[x], 1); mbar_init(&p_full[x], BM / 32); mbar_init(&o_done[x], 1); }
+        mbar_init(v_fixed, 1);
         *aborted = 0;
         mbar_fence_init();
     }
@@ -161,6 +202,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
+            if (lane == 0) TW_TRACE_AT(0, i, 0);
             if (row_coord >= 0) {
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb)
@@ -175,12 +217,31 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 if (lane == 0) mbar_wait(&k_full[st], parity, status);
                 break;
             }
+            if (lane == 0) TW_TRACE_AT(1, i, 2);
             if (row_coord >= 0) {
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb)
                     tma_load_2d(v_s + st * KV_STAGE_BYTES + kb * BLK + lane * box_rows * 128, &map_v, &v_full[st], kb * 64, row_coord);
             }
             issued = i + 1;
+        }
+        if (tail_rows && issued == ntiles) {
+            // The last tile reaches past the request's last key.  What its value rows hold there (the rest
+            // of a page, or whatever the stage held before) must not reach a product, since 0 x NaN is NaN:
+            // zero them once the copies have landed, then tell the MMA thread.
+            const int last = ntiles - 1;
+            if (mbar_wait(&v_full[last % KV_STAGES], (last / KV_STAGES) & 1, status)) {
+                unsigned char* vt = v_s + (last % KV_STAGES) * KV_STAGE_BYTES;
+                for (int idx = lane; idx < tail_rows * KB * 8; idx += 32) {
+                    const int r = BN - tail_rows + idx / (KB * 8), rest = idx % (KB * 8);
+                    *reinterpret_cast<uint4*>(vt + (rest >> 3) * BLK + r * 128 + ((rest & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(v_fixed);
+            } else {
+                *aborted = 1;
+            }
         }
         if (*aborted && lane == 0) {
             // wait (bounded) for the copies already in flight, so that none lands after the block has gone
@@ -190,73 +251,63 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             }
         }
     } else if (warp == 1) {
-        // ---- tensor cores: lane 0 issues every MMA of the block; the warp zeroes value rows past the last key
-        const uint32_t idesc_s = instr_desc(BN), idesc_o = instr_desc(D, true);
-        auto issue_s = [&](int x, int i) {
-            const unsigned char* kt = k_s + (i % KV_STAGES) * KV_STAGE_BYTES;
+        // ---- tensor cores: lane 0 issues every MMA of the block.  The tensor pipe runs dry as soon as
+        // this thread does anything else, so whatever a group of MMAs needs beside P (V of the tile, K of
+        // the next one) is waited for before P, and the groups follow one another without a break.
+        if (lane == 0 && ntiles > 0) {
+            const uint32_t idesc_s = instr_desc(BN), idesc_o = instr_desc(D, true);
+            auto issue_s = [&](int x, int i) {
+                const unsigned char* kt = k_s + (i % KV_STAGES) * KV_STAGE_BYTES;
 #pragma unroll
-            for (int kb = 0; kb < KB; ++kb)
+                for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem_base + x * BN, smem_desc(q_s + (x * KB + kb) * BLK, k * 32), smem_desc(kt + kb * BLK, k * 32),
-                              idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
-            umma_commit(&s_full[x]);
-        };
-        auto issue_o = [&](int x, int i) {
-            const unsigned char* vt = v_s + (i % KV_STAGES) * KV_STAGE_BYTES;
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + x * BN, smem_desc(q_s + (x * KB + kb) * BLK, k * 32), smem_desc(kt + kb * BLK, k * 32),
+                                  idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&s_full[x]);
+            };
+            auto issue_o = [&](int x, int i) {
+                const unsigned char* vt = v_s + (i % KV_STAGES) * KV_STAGE_BYTES;
 #pragma unroll
-            for (int k = 0; k < BN / 16; ++k)
-                umma_bf16_ts(tmem_base + O_COL + x * D, tmem_base + x * BN + k * 8, smem_desc_mn_major(vt + k * 2048, BLK),
-                             idesc_o, (i > 0 || k > 0) ? 1u : 0u);
-            umma_commit(&o_done[x]);
-        };
-        bool ok = ntiles > 0 && !*aborted && mbar_wait(&k_full[0], 0, status);
-        if (ok) {
-            tc_fence_after();
-            if (lane == 0) {
+                for (int k = 0; k < BN / 16; ++k)
+                    umma_bf16_ts(tmem_base + O_COL + x * D, tmem_base + x * BN + k * 8, smem_desc_mn_major(vt + k * 2048, BLK),
+                                 idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&o_done[x]);
+            };
+            bool ok = mbar_wait(&k_full[0], 0, status);
+            if (ok) {
+                tc_fence_after();
                 for (int x = 0; x < nq; ++x) issue_s(x, 0);
                 umma_commit(&k_empty[0]);
             }
-            __syncwarp();
-        }
-        for (int i = 0; ok && i < ntiles; ++i) {
-            const int st = i % KV_STAGES;
-            for (int x = 0; ok && x < nq; ++x) {
-                ok = !*aborted && mbar_wait(&p_full[x], i & 1, status);
-                if (ok && x == 0) {
-                    ok = mbar_wait(&v_full[st], (i / KV_STAGES) & 1, status);
-                    const int have = kv_len - (j_begin + i) * BN;            // keys of this tile that exist
-                    if (ok && have < BN) {
-                        unsigned char* vt = v_s + st * KV_STAGE_BYTES;
-                        for (int idx = lane; idx < (BN - have) * KB * 8; idx += 32) {
-                            const int r = have + idx / (KB * 8), rest = idx % (KB * 8);
-                            *reinterpret_cast<uint4*>(vt + (rest >> 3) * BLK + r * 128 + ((rest & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
-                        }
-                        fence_proxy_async();
-                    }
-                    __syncwarp();
-                }
-                if (!ok) break;
-                tc_fence_after();
-                if (lane == 0) {
+            for (int i = 0; ok && i < ntiles; ++i) {
+                const int st = i % KV_STAGES;
+                TW_TRACE_AT(1, i, 10);
+                ok = mbar_wait(&v_full[st], (i / KV_STAGES) & 1, status);
+                TW_TRACE_AT(1, i, 2);
+                if (ok && i == ntiles - 1 && tail_rows) ok = mbar_wait(v_fixed, 0, status);
+                if (ok && i + 1 < ntiles) ok = mbar_wait(&k_full[(i + 1) % KV_STAGES], ((i + 1) / KV_STAGES) & 1, status);
+                TW_TRACE_AT(1, i, 4);
+                for (int x = 0; ok && x < nq; ++x) {
+                    TW_TRACE_AT(1, i, x * 6 + 0);
+                    ok = mbar_wait(&p_full[x], i & 1, status);
+                    if (!ok) break;
+                    TW_TRACE_AT(1, i, x * 6 + 1);
+                    tc_fence_after();
                     issue_o(x, i);
-                    if (x == nq - 1) umma_commit(&v_empty[st]);
+                    TW_TRACE_AT(1, i, x * 6 + 3);
+                    if (i + 1 < ntiles) issue_s(x, i + 1);
+                    TW_TRACE_AT(1, i, x * 6 + 5);
                 }
-                if (i + 1 < ntiles) {
-                    if (x == 0) {
-                        ok = mbar_wait(&k_full[(i + 1) % KV_STAGES], ((i + 1) / KV_STAGES) & 1, status);
-                        if (!ok) break;
-                        tc_fence_after();
-                    }
-                    if (lane == 0) {
-                        issue_s(x, i + 1);
-                        if (x == nq - 1) umma_commit(&k_empty[(i + 1) % KV_STAGES]);
-                    }
+                if (ok) {
+                    umma_commit(&v_empty[st]);
+                    if (i + 1 < ntiles) umma_commit(&k_empty[(i + 1) % KV_STAGES]);
                 }
-                __syncwarp();
+                TW_TRACE_AT(1, i, 8);
             }
+            if (!ok) *aborted = 1;
         }
-        if (!ok) *aborted = 1;
+        __syncwarp();
     } else if ((warp - 2) / 4 < nq) {
         // ---- softmax: thread = row rt of tile x = TMEM lane rt
         const int x = (warp - 2) / 4;
@@ -273,13 +324,16 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         bool ok = true;
         for (int i = 0; i < ntiles; ++i) {
             const int kbase = (j_begin + i) * BN;
+            if (lane == 0) TW_TRACE_AT(warp, i, 0);
             ok = !*aborted && mbar_wait(&s_full[x], i & 1, status);
             if (!ok) break;
+            if (lane == 0) TW_TRACE_AT(warp, i, 1);
             tc_fence_after();
             uint32_t v[BN];
 #pragma unroll
             for (int c = 0; c < BN; c += 32) tmem_ld32_nowait(s_addr + c, v + c);
             tmem_wait_ld();
+            if (lane == 0) TW_TRACE_AT(warp, i, 2);
             const bool all_visible = kbase + BN - 1 <= pos && kbase >= lo;
             if (!__all_sync(0xffffffffu, all_visible)) {
 #pragma unroll
@@ -288,10 +342,14 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     if (key > pos || key < lo) v[c] = __float_as_uint(NEG_INF);
                 }
             }
-            float mt = NEG_INF;
+            // four independent chains of three-input maxima
+            float mx[4] = {NEG_INF, NEG_INF, NEG_INF, NEG_INF};
 #pragma unroll
-            for (int c = 0; c < BN; ++c) mt = fmaxf(mt, __uint_as_float(v[c]));
-            mt *= scale_log2e;                                // scale > 0: the maximum commutes with it
+            for (int c = 0; c < BN; c += 8) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) mx[k] = max3(mx[k], __uint_as_float(v[c + 2 * k]), __uint_as_float(v[c + 2 * k + 1]));
+            }
+            const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2e;   // scale > 0: the maximum commutes with it
             const bool rescale = mt > m_used + RESCALE_THRESHOLD;     // also the first finite maximum (m_used = -inf)
             float factor = 1.f;
             if (rescale) {
@@ -299,14 +357,20 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 m_used = mt;
             }
             const float neg_mu = m_used == NEG_INF ? 0.f : -m_used;
-            float sum = 0.f;
+            // p = 2^(s c - m) two at a time (packed fp32 multiply-add and add), four independent sums of pairs
+            float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int c = 0; c < BN; c += 2) {
-                const float p0 = ex2(fmaf(__uint_as_float(v[c]), scale_log2e, neg_mu));
-                const float p1 = ex2(fmaf(__uint_as_float(v[c + 1]), scale_log2e, neg_mu));
-                sum += p0 + p1;
-                v[c >> 1] = pack_bf16(p0, p1);
+            for (int c = 0; c < BN; c += 8) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float2 e = fma2(__uint_as_float(v[c + 2 * k]), __uint_as_float(v[c + 2 * k + 1]), scale_log2e, neg_mu);
+                    e.x = ex2(e.x);
+                    e.y = ex2(e.y);
+                    acc[k] = add2(acc[k], e);
+                    v[(c >> 1) + k] = pack_bf16(e.x, e.y);
+                }
             }
+            const float sum = ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
             l = l * factor + sum;
             if (i > 0 && __any_sync(0xffffffffu, rescale)) {
                 // P V of the tile before has retired (it was issued before the S just read): O is complete up to it
@@ -326,12 +390,15 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     tmem_wait_st();
                 }
             }
+            if (lane == 0) TW_TRACE_AT(warp, i, 3);
             // P over the first 64 columns of S: the whole row of S is in registers by now
             tmem_st32_nowait(s_addr, v);
             tmem_st32_nowait(s_addr + 32, v + 32);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&p_full[x]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[x]);      // one arrival per warp: 128 arrivals on one barrier take 450 cycles
+            if (lane == 0) TW_TRACE_AT(warp, i, 4);
         }
         if (ok && ntiles > 0) ok = mbar_wait(&o_done[x], (ntiles - 1) & 1, status);
         if (!ok) {
@@ -368,6 +435,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 }  // namespace
 
 TW_EXPORT int tw_attn_tc5_head_dim() { return D; }
+
+#ifdef TW_TRACE
+TW_EXPORT int tw_attn_tc5_trace_ptr(long long** ptr, int* roles, int* tiles, int* slots) {
+    *roles = TRACE_ROLES; *tiles = TRACE_TILES; *slots = TRACE_SLOTS;
+    return (int)cudaGetSymbolAddress((void**)ptr, g_trace);
+}
+#endif
 
 // Whether the kernel takes this page size: a key tile is a whole number of pages, or a page a
 // whole number of key tiles, and a tile has at most 32 boxes.
