@@ -34,3 +34,46 @@ def test_benchmark_layer_sizes_against_plain(dtype, big, tmp_path):
         rows = replay_in_process(folder, dtype, steps, tmp_path / name)
         worst = max(float(np.abs(rows[("r", p)] - want[p]).max()) for p in range(len(tokens)))
         assert worst <= tol, f"{dtype} {name}: off by {worst:.3e} (logits up to {np.abs(want).max():.2f})"
+
+
+# A model whose prompt portions are long enough for the tcgen05 attention kernel (128 tokens and
+# more, head size 64), small enough to replay several requests in many ways.
+MEDIUM = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 1536, "hidden_size": 320, "intermediate_size": 704, "num_hidden_layers": 2,
+    "num_attention_heads": 5, "num_key_value_heads": 1, "head_dim": 64,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 2048,
+    "tie_word_embeddings": True, "use_sliding_window": False, "hidden_act": "silu", "initializer_range": 0.05,
+}
+
+
+@pytest.fixture(scope="module")
+def medium(tmp_path_factory):
+    folder = tw.write_random_model(tmp_path_factory.mktemp("medium") / "m", MEDIUM, seed=9)
+    requests = {rid: random_tokens(MEDIUM["vocab_size"], n, 40 + i) for i, (rid, n) in enumerate(
+        (("a", 420), ("b", 131), ("c", 300), ("d", 257), ("e", 64)))}
+    return folder, requests, {rid: plain_logits(folder, toks) for rid, toks in requests.items()}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("how", ["whole", "tail", "portions", "mixed"])
+def test_long_portions_against_plain(dtype, how, medium, tmp_path):
+    """Portions of 128 tokens and more beside short ones and single tokens: in bfloat16 the long ones run on
+    the tcgen05 attention kernel and the others on the mma.sync kernels, and every position must still
+    agree with the plain implementation, whichever kernel wrote its keys and read them."""
+    from helpers import schedule_mixed, schedule_portions
+    folder, requests, want = medium
+    steps = {
+        "whole": lambda: schedule_whole(requests),
+        "tail": lambda: schedule_tail(requests, tail=8),
+        "portions": lambda: schedule_portions(requests, sizes=(130, 2, 200, 1, 64, 129, 3, 256)),
+        "mixed": lambda: schedule_mixed(requests, live=3, seed=4, prefill=(140, 2, 128, 9, 190), decode_from=0.9),
+    }[how]()
+    rows = replay_in_process(folder, dtype, steps, tmp_path / how)
+    for rid, toks in requests.items():
+        scale = max(1.0, float(np.abs(want[rid]).max()))
+        tol = 1e-4 if dtype == "float32" else 0.03 * scale
+        got = [p for p in range(len(toks)) if (rid, p) in rows]
+        assert got, f"no logits for request {rid}"
+        worst = max(float(np.abs(rows[(rid, p)] - want[rid][p]).max()) for p in got)
+        assert worst <= tol, f"{dtype} {how} request {rid}: off by {worst:.3e}"
