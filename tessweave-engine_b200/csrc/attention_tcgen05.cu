@@ -256,21 +256,25 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         // the next one) is waited for before P, and the groups follow one another without a break.
         if (lane == 0 && ntiles > 0) {
             const uint32_t idesc_s = instr_desc(BN), idesc_o = instr_desc(D, true);
+            // Descriptors are built once; per MMA only a constant is added to the address field (a thread
+            // that computes a descriptor from scratch before each MMA issues them slower than they execute).
+            const uint64_t q_desc = smem_desc(q_s, 0), k_desc = smem_desc(k_s, 0), v_desc = smem_desc_mn_major(v_s, BLK);
             auto issue_s = [&](int x, int i) {
-                const unsigned char* kt = k_s + (i % KV_STAGES) * KV_STAGE_BYTES;
+                const uint64_t kd = k_desc + (uint64_t)((i % KV_STAGES) * (KV_STAGE_BYTES >> 4));
+                const uint64_t qd = q_desc + (uint64_t)(x * KB * (BLK >> 4));
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_base + x * BN, smem_desc(q_s + (x * KB + kb) * BLK, k * 32), smem_desc(kt + kb * BLK, k * 32),
+                        umma_bf16(tmem_base + x * BN, qd + (uint64_t)(kb * (BLK >> 4) + k * 2), kd + (uint64_t)(kb * (BLK >> 4) + k * 2),
                                   idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
                 umma_commit(&s_full[x]);
             };
             auto issue_o = [&](int x, int i) {
-                const unsigned char* vt = v_s + (i % KV_STAGES) * KV_STAGE_BYTES;
+                const uint64_t vd = v_desc + (uint64_t)((i % KV_STAGES) * (KV_STAGE_BYTES >> 4));
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)
-                    umma_bf16_ts(tmem_base + O_COL + x * D, tmem_base + x * BN + k * 8, smem_desc_mn_major(vt + k * 2048, BLK),
+                    umma_bf16_ts(tmem_base + O_COL + x * D, tmem_base + x * BN + k * 8, vd + (uint64_t)(k * (2048 >> 4)),
                                  idesc_o, (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(&o_done[x]);
             };
