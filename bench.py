@@ -3,6 +3,7 @@ decode through the Python entry point, prefill of 2,048 tokens, and decode at ba
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--context C]
     python bench.py --impl reference ...      # the unmodified reference, if it is installed
+    python bench.py --kernels                 # every operation of a layer alone, with its roofline
 
 The default run has the layer sizes of the Qwen2.5-7B-sized benchmark configuration with
 random weights (N(0, 0.02), drawn on the device), a batch of 8 and a context of 4,096 tokens.
@@ -332,6 +333,8 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one small measurement and print its figures (for profiling a kernel on a small case)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    ap.add_argument("--kernels", action="store_true",
+                    help="time every operation of a layer and the output head alone and print each with its roofline")
     ap.add_argument("--workload", choices=sorted(WORKLOAD_SIZES), default=None,
                     help="run a whole-engine workload at 14B / 32B layer sizes instead of the headline measurement")
     args = ap.parse_args()
@@ -350,6 +353,15 @@ def main() -> int:
         print(json.dumps(workload_run(args.workload, args.layers if args.layers != BENCH_CONFIG["num_hidden_layers"] else None)))
         return 0
     pk, pk_source = peaks()
+    if args.kernels:
+        import tessweave_engine_b200 as tw
+        from tessweave_engine_b200.engine.kernel_bench import format_table, kernel_table
+        cfg = tw.Qwen2Config.from_dict(BENCH_CONFIG)
+        rows = kernel_table(cfg, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE)
+        print(format_table(rows), file=sys.stderr)
+        print(json.dumps({"kernels": rows, "peaks": pk, "peaks_source": pk_source, "batch": args.batch,
+                          "context": args.context, "prefill_tokens": PREFILL_TOKENS}))
+        return 0
     model, cfg = build_model(args.layers)
     if args.only == "prefill":
         print(json.dumps({"only": "prefill", "layers": args.layers, **prefill_run(model, cfg, PREFILL_TOKENS, args.steps, args.warmup)}))

@@ -39,12 +39,24 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
     const int chunk = (vocab + TW_SAMPLE_THREADS - 1) / TW_SAMPLE_THREADS;
     const int begin = tid * chunk, end = min(vocab, begin + chunk);
 
-    // -- maximum and its lowest index
+    // -- maximum and its lowest index: the threads stride over the row together (16 bytes each where the
+    //    row allows), indices rise within a thread, and ties between threads go to the lower index
     float best = -INFINITY;
     int besti = 0x7fffffff;
-    for (int v = begin; v < end; ++v) {
-        const float f = x[v];
-        if (f > best) { best = f; besti = v; }
+    if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        for (int v4 = tid; v4 < (vocab >> 2); v4 += TW_SAMPLE_THREADS) {
+            const float4 f = x4[v4];
+            if (f.x > best) { best = f.x; besti = 4 * v4; }
+            if (f.y > best) { best = f.y; besti = 4 * v4 + 1; }
+            if (f.z > best) { best = f.z; besti = 4 * v4 + 2; }
+            if (f.w > best) { best = f.w; besti = 4 * v4 + 3; }
+        }
+    } else {
+        for (int v = tid; v < vocab; v += TW_SAMPLE_THREADS) {
+            const float f = x[v];
+            if (f > best) { best = f; besti = v; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
