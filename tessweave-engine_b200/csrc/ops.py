@@ -479,3 +479,27 @@ def gemm_tcgen05(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, st
                                                   c_int(mode), c_int(stride), c_int(1 if swap else 0), _ptr(status),
                                                   _stream())
     _check(code, "gemm_tcgen05")
+
+
+def gemm_tcgen05_pair(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, status: torch.Tensor,
+                      silu_mul_pairs: bool = False) -> None:
+    """out[:m] = x[:m] @ w.T for many rows, on pairs of thread blocks (tcgen05.mma.cta_group::2,
+    256 x 256 tiles).  ``out`` is bf16 or fp32 [>=m, n]; with ``silu_mul_pairs`` (rows of w in
+    groups of eight gates and their eight ups) it is bf16 [>=m, n / 2] = silu(gate) * up."""
+    _cuda(out, x, w, status)
+    n, k = w.shape
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x.is_contiguous()
+          and x.shape[1] == k and k % 8 == 0, "gemm_tcgen05_pair: contiguous bf16 operands, k a multiple of 8")
+    _need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0, "gemm_tcgen05_pair: operands must be 16-byte aligned")
+    if silu_mul_pairs:
+        _need(n % 16 == 0 and out.dtype == torch.bfloat16 and out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= m
+              and out.shape[1] == n // 2 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0,
+              "gemm_tcgen05_pair: the SiLU.mul output must be bf16 [m, n / 2] with 16-byte aligned rows")
+        mode = 3
+    else:
+        _need(out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= m and out.shape[1] == n
+              and out.dtype in (torch.bfloat16, torch.float32), "gemm_tcgen05_pair: bad output")
+        mode = 0 if out.dtype == torch.bfloat16 else 1
+    code = _fn("gemm_tcgen05_pair", "tw_gemm_tcgen05_pair")(_ptr(x), _ptr(w), c_int(m), c_int(n), c_int(k), _ptr(out),
+                                                            c_int(mode), c_int(out.stride(0)), _ptr(status), _stream())
+    _check(code, "gemm_tcgen05_pair")
