@@ -16,6 +16,13 @@
 //     (tcgen05.ld, one TMEM lane per thread) while the tensor cores work on the next; they write bf16,
 //     fp32, or silu(gate) * up for weights whose rows come in groups of eight gates and eight ups.
 //
+// Measured on B200 (2,048 x 37,888 x 3,584): 391 us, 0.88 of the library's product; with the
+// SiLU.mul epilogue it equals the library's product plus the separate SiLU.mul kernel.  Per k-block
+// the copies alone take 560 cycles, the MMAs alone 660 (512 of them in the tensor pipe), both
+// together 830.  Tried and measured no better: tiles of 256 x 512 (the accumulator then fills the
+// tensor memory and the epilogue no longer overlaps), L2 prefetch of the weight tiles ahead of
+// the copies, the next k-block's wait between the MMAs of the current one, spinning waits.
+//
 // Every wait on an mbarrier is bounded; a wait that runs out sets TW_ERR_WAIT in the status word,
 // the role stops, and the block goes on to the common end (cluster barrier, tensor memory freed).
 //
@@ -35,7 +42,7 @@ constexpr int EPI_WARPS = 4;
 constexpr int THREADS = 64 + EPI_WARPS * 32;   // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STAGES = 6;
+constexpr int STAGES = 7;
 constexpr int TMEM_COLS = 512;         // two accumulators of 256 columns: the epilogue of a tile overlaps the next tile's MMAs
 constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 
@@ -193,7 +200,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const int s = it % STAGES;
                     ok = mbar_wait(&full[s], (it / STAGES) & 1, status);
                     if (!ok) break;
-                    tc_fence_after();
                     const uint64_t off = (uint64_t)(s * (STAGE_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)

@@ -45,6 +45,10 @@ class SwiGLU(FeedForward):
         act = ws.get("ffn.act", (n, self.intermediate), dt)
         if self.interleaved and ops.small_m_supported(h, self.w_gate_up, n):
             ops.gemm_small_m(act, h, self.w_gate_up, n, silu_mul_pairs=True)
+        elif self.interleaved and ops.pair_product_preferred(h, self.w_gate_up, n):
+            # prompt steps: 256 x 256 tiles on pairs of thread blocks (tcgen05.mma.cta_group::2), SiLU.mul in the
+            # epilogue, so the [tokens, 2 * intermediate] product never reaches memory
+            ops.gemm_tcgen05_pair(act, h, self.w_gate_up, n, ctx.status, silu_mul_pairs=True)
         else:
             gate_up = linear(ctx, "ffn.gate_up", h, self.w_gate_up)
             ops.silu_mul(act, gate_up, n, self.interleaved)

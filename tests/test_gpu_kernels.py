@@ -571,3 +571,37 @@ def test_decode_attention_many_pages_per_block():
     for i, r in enumerate(rows_of):
         k = setup["k"][i].to(torch.bfloat16).float(); v = setup["v"][i].to(torch.bfloat16).float()
         assert torch.allclose(got[i:i + 1], dense_attention(qr[i:i + 1], k, v, r), **TOL["bfloat16"])
+
+
+# ---------------------------------------------------------------------------
+# products with many rows on pairs of thread blocks (tcgen05.mma.cta_group::2)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 1000, 3584), (512, 768, 1024), (1, 16, 8), (700, 4608, 200)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_pair(m, n, k, out_dtype):
+    """Whole tiles, ragged tiles in every direction (rows, columns, k), one row, bf16 and fp32 results."""
+    g = torch.Generator().manual_seed(m + n + k)
+    x = dev(torch.randn(m, k, generator=g), torch.bfloat16)
+    w = dev(torch.randn(n, k, generator=g) * 0.05, torch.bfloat16)
+    out = torch.full((m, n), float("nan"), device="cuda", dtype=out_dtype)
+    st = status()
+    ops().gemm_tcgen05_pair(out, x, w, m, st)
+    assert int(st) == 0
+    want = x.float() @ w.float().t()
+    tol = dict(rtol=2e-2, atol=2e-2) if out_dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-3)
+    assert torch.allclose(out.float(), want, **tol)
+
+
+@pytest.mark.parametrize("m,n,k", [(300, 1024, 512), (600, 20000, 512), (257, 48, 64)])
+def test_gemm_tcgen05_pair_silu_mul(m, n, k):
+    """The fused epilogue: weight rows in groups of eight gates and their eight ups."""
+    g = torch.Generator().manual_seed(7)
+    x = dev(torch.randn(m, k, generator=g), torch.bfloat16)
+    w = dev(torch.randn(n, k, generator=g) * 0.05, torch.bfloat16)
+    out = torch.full((m, n // 2), float("nan"), device="cuda", dtype=torch.bfloat16)
+    st = status()
+    ops().gemm_tcgen05_pair(out, x, w, m, st, silu_mul_pairs=True)
+    assert int(st) == 0
+    y = (x.float() @ w.float().t()).reshape(m, n // 16, 2, 8)
+    want = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(m, n // 2)
+    assert torch.allclose(out.float(), want, rtol=2e-2, atol=2e-2)
