@@ -37,7 +37,7 @@ using namespace tc5;
 constexpr int BM = 128;            // rows per block (256 per pair)
 constexpr int BN = 256;            // weight rows per pair tile
 constexpr int BNH = BN / 2;        // weight rows a block loads
-constexpr int BK = 64;
+constexpr int BK = 64;            // four MMAs of 16 values of k per k-block (the issue loop is written out for four)
 constexpr int EPI_WARPS = 4;
 constexpr int THREADS = 64 + EPI_WARPS * 32;   // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2;
@@ -189,22 +189,33 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // ---- tensor cores of both SMs: one thread of the pair's first block issues every MMA
             const uint32_t idesc = instr_desc_pair();
             const uint64_t a_desc = smem_desc(tiles, 0), b_desc = smem_desc(tiles + A_BYTES, 0);
-            int it = 0, lt = 0;
-            bool ok = true;
+            // An MMA is not accepted before the one before it has retired, so whatever this thread does
+            // between the last MMA of a k-block and the first of the next leaves the tensor pipe idle.  The
+            // test of the next k-block's barrier is therefore made before the last MMA is issued, while the
+            // third one runs; only if the copies have not landed by then does the thread wait for them later.
+            int s = 0, lt = 0;
+            uint32_t phase = 0;
+            bool ok = true, ready = false;
             for (int t = pair; ok && t < n_tiles; t += pairs, ++lt) {
                 const int b = lt & 1;
                 ok = mbar_wait(&acc_empty[b], ((lt >> 1) & 1) ^ 1, status);       // the epilogues have read what was there
                 if (!ok) break;
                 tc_fence_after();
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    ok = mbar_wait(&full[s], (it / STAGES) & 1, status);
+                const uint32_t acc = tmem_base + b * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!ready) ok = mbar_wait(&full[s], phase, status);
                     if (!ok) break;
-                    const uint64_t off = (uint64_t)(s * (STAGE_BYTES >> 4));
-#pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        umma_bf16_pair(tmem_base + b * BN, a_desc + off + 2 * k, b_desc + off + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    const uint64_t ad = a_desc + (uint64_t)(s * (STAGE_BYTES >> 4)), bd = b_desc + (uint64_t)(s * (STAGE_BYTES >> 4));
+                    const int s_next = s + 1 == STAGES ? 0 : s + 1;
+                    const uint32_t phase_next = s + 1 == STAGES ? phase ^ 1u : phase;
+                    umma_bf16_pair(acc, ad, bd, idesc, kb > 0 ? 1u : 0u);
+                    umma_bf16_pair(acc, ad + 2, bd + 2, idesc, 1u);
+                    umma_bf16_pair(acc, ad + 4, bd + 4, idesc, 1u);
+                    ready = mbar_test_wait(&full[s_next], phase_next);     // usually true: the copies run stages ahead
+                    umma_bf16_pair(acc, ad + 6, bd + 6, idesc, 1u);
                     umma_commit_pair(&empty[s]);
+                    s = s_next;
+                    phase = phase_next;
                 }
                 if (ok) umma_commit_pair(&acc_full[b]);
             }
