@@ -267,6 +267,14 @@ def workload_run(name: str, layers: int | None) -> dict:
     cfg, spec = tw.resolve(config)
     model = tw.Model(spec, Runtime(torch.device("cuda:0"), torch.bfloat16), config=cfg)
     tw.fill_random(model, seed=0)
+    # An untimed request first: whatever has to be compiled or captured (kernels of this head size, prompt
+    # portions long enough for the tcgen05 kernels, decode graphs) is compiled and captured here.
+    warm = tw.Engine(model, tw.EngineConfig(block_size=PAGE_SIZE, kv_blocks=64, max_context=800, max_active=2, max_queue=2,
+                                            prefill_chunk=640, max_step_tokens=642, prefix_cache=False))
+    warm.submit(torch.randint(0, cfg.vocab_size, (700,)).tolist(), max_tokens=3, ignore_eos=True)
+    warm.run_until_done()
+    warm.close()
+    del warm
     gen = torch.Generator().manual_seed(11)
     rand = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=gen))
     toks = lambda n: torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
