@@ -415,6 +415,12 @@ rope_kv_write_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, int qkv_stride, con
         }
     }
     const int in_page = pos % page_size;
+    // the angles depend on the position and the pair only: each is evaluated once per block, not once per head
+    __shared__ float s_cos[128], s_sin[128];
+    if (inv_freq) {
+        for (int i = threadIdx.x; i < half; i += TW_ROPE_THREADS) sincosf((float)pos * inv_freq[i], &s_sin[i], &s_cos[i]);
+    }
+    __syncthreads();
     const int rot_items = (write_cache ? Hq + Hkv : Hq) * groups;
     const int v_items = write_cache ? Hkv * groups : 0;      // v: 8 values of each half per item
     const int idx = blockIdx.y * TW_ROPE_THREADS + threadIdx.x;
@@ -426,19 +432,25 @@ rope_kv_write_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, int qkv_stride, con
     uint4 lo = *reinterpret_cast<const uint4*>(row + col), hi = *reinterpret_cast<const uint4*>(row + col + half);
     __nv_bfloat162* lo2 = reinterpret_cast<__nv_bfloat162*>(&lo);
     __nv_bfloat162* hi2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+    float blo[8], bhi[8];                       // col and half are multiples of 8: 32-byte aligned reads of the bias
+    if (bias) {
+        *reinterpret_cast<float4*>(blo) = *reinterpret_cast<const float4*>(bias + col);
+        *reinterpret_cast<float4*>(blo + 4) = *reinterpret_cast<const float4*>(bias + col + 4);
+        *reinterpret_cast<float4*>(bhi) = *reinterpret_cast<const float4*>(bias + col + half);
+        *reinterpret_cast<float4*>(bhi + 4) = *reinterpret_cast<const float4*>(bias + col + half + 4);
+    }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
         float2 x1 = __bfloat1622float2(lo2[e]), x2 = __bfloat1622float2(hi2[e]);
         if (bias) {
-            x1.x += bias[col + 2 * e]; x1.y += bias[col + 2 * e + 1];
-            x2.x += bias[col + half + 2 * e]; x2.y += bias[col + half + 2 * e + 1];
+            x1.x += blo[2 * e]; x1.y += blo[2 * e + 1];
+            x2.x += bhi[2 * e]; x2.y += bhi[2 * e + 1];
         }
         float2 y1 = x1, y2 = x2;
         if (inv_freq && !is_v) {
-            float sn, cs;
-            sincosf((float)pos * inv_freq[i0 + 2 * e], &sn, &cs);
+            float sn = s_sin[i0 + 2 * e], cs = s_cos[i0 + 2 * e];
             y1.x = x1.x * cs - x2.x * sn; y2.x = x2.x * cs + x1.x * sn;
-            sincosf((float)pos * inv_freq[i0 + 2 * e + 1], &sn, &cs);
+            sn = s_sin[i0 + 2 * e + 1]; cs = s_cos[i0 + 2 * e + 1];
             y1.y = x1.y * cs - x2.y * sn; y2.y = x2.y * cs + x1.y * sn;
         }
         lo2[e] = __floats2bfloat162_rn(y1.x, y1.y);
@@ -464,7 +476,7 @@ TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, 
                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (D <= 0 || (D & 1)) return (int)cudaErrorInvalidValue;
-    if (dtype == TW_BF16 && !partial && (D & 15) == 0 && (qkv_stride & 7) == 0 &&
+    if (dtype == TW_BF16 && !partial && (D & 15) == 0 && D <= 256 && (qkv_stride & 7) == 0 && (reinterpret_cast<uintptr_t>(bias) & 15) == 0 &&
         (reinterpret_cast<uintptr_t>(qkv) & 15) == 0) {
         const int items = (Hq + 2 * Hkv) * (D / 16);
         const dim3 vgrid(n_tokens, (items + TW_ROPE_THREADS - 1) / TW_ROPE_THREADS);
