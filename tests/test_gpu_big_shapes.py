@@ -51,7 +51,7 @@ MEDIUM = {
 def medium(tmp_path_factory):
     folder = tw.write_random_model(tmp_path_factory.mktemp("medium") / "m", MEDIUM, seed=9)
     requests = {rid: random_tokens(MEDIUM["vocab_size"], n, 40 + i) for i, (rid, n) in enumerate(
-        (("a", 420), ("b", 131), ("c", 300), ("d", 257), ("e", 64)))}
+        (("a", 420), ("b", 131), ("c", 300), ("d", 257), ("e", 64), ("f", 700)))}
     return folder, requests, {rid: plain_logits(folder, toks) for rid, toks in requests.items()}
 
 
@@ -60,14 +60,15 @@ def medium(tmp_path_factory):
 def test_long_portions_against_plain(dtype, how, medium, tmp_path):
     """Portions of 128 tokens and more beside short ones and single tokens: in bfloat16 the long ones run on
     the tcgen05 attention kernel and the others on the mma.sync kernels, and every position must still
-    agree with the plain implementation, whichever kernel wrote its keys and read them."""
+    agree with the plain implementation, whichever kernel wrote its keys and read them.  Steps of 512 rows
+    and more (request f whole, and the wide mixed steps) take the gate/up product on block pairs."""
     from helpers import schedule_mixed, schedule_portions
     folder, requests, want = medium
     steps = {
         "whole": lambda: schedule_whole(requests),
         "tail": lambda: schedule_tail(requests, tail=8),
-        "portions": lambda: schedule_portions(requests, sizes=(130, 2, 200, 1, 64, 129, 3, 256)),
-        "mixed": lambda: schedule_mixed(requests, live=3, seed=4, prefill=(140, 2, 128, 9, 190), decode_from=0.9),
+        "portions": lambda: schedule_portions(requests, sizes=(130, 2, 200, 1, 64, 129, 3, 256, 520)),
+        "mixed": lambda: schedule_mixed(requests, live=4, seed=4, prefill=(140, 2, 128, 9, 190, 300), decode_from=0.9),
     }[how]()
     rows = replay_in_process(folder, dtype, steps, tmp_path / how)
     for rid, toks in requests.items():
