@@ -131,7 +131,55 @@ struct KFrag {                    // the d values of one key row this thread fee
     uint2 tail;
 };
 
-template <bool CLUSTER>
+// Where a decode step's query, key and value come from when the kernel makes them itself: the rows of the
+// q/k/v product (fp32 slices of a product split over k, or one bf16 row), its bias, the rotation table.
+struct FusedQkv {
+    const float* partial;        // [slices][rows][width] fp32, or null
+    int nslices;
+    long long slice_stride;      // elements between slices
+    const bf16* dense;           // [rows][dense_stride] bf16, used when partial is null
+    int dense_stride;
+    const float* bias;           // [width] or null
+    const float* inv_freq;       // [D / 2]; null: no rotation
+    bf16* k_cache;               // where the new key and value go; null: the cache is not written
+    bf16* v_cache;
+};
+
+// fp32 values of NC columns of one row of the q/k/v product, bias included.  The slices of a split product are
+// summed (0 + 4 + 8 ..), (1 + 5 + ..), .. first and then ((.) + (.)) + ((.) + (.)), as the kernel that otherwise
+// does this work sums them; the loads of all columns and of four slices are independent of one another.
+template <int NC>
+__device__ __forceinline__ void product_cols(const FusedQkv& fq, size_t row, int width, const int (&cols)[NC], float (&out)[NC]) {
+    if (fq.partial) {
+        const float* prow = fq.partial + row * width;
+        float acc[NC][4];
+#pragma unroll
+        for (int j = 0; j < NC; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+        int k = 0;
+        for (; k + 4 <= fq.nslices; k += 4) {
+#pragma unroll
+            for (int j = 0; j < NC; ++j) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[j][u] += prow[(size_t)(k + u) * fq.slice_stride + cols[j]];
+            }
+        }
+        for (; k < fq.nslices; ++k) {
+#pragma unroll
+            for (int j = 0; j < NC; ++j) acc[j][0] += prow[(size_t)k * fq.slice_stride + cols[j]];
+        }
+#pragma unroll
+        for (int j = 0; j < NC; ++j) out[j] = (acc[j][0] + acc[j][1]) + (acc[j][2] + acc[j][3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < NC; ++j) out[j] = __bfloat162float(fq.dense[row * fq.dense_stride + cols[j]]);
+    }
+    if (fq.bias) {
+#pragma unroll
+        for (int j = 0; j < NC; ++j) out[j] += fq.bias[cols[j]];
+    }
+}
+
+template <bool CLUSTER, bool FUSED>
 __global__ void __launch_bounds__(DEC_WARPS * 32, (D <= 128 ? 4 : 2))
 attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
                    const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
@@ -139,10 +187,11 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
                    const int* __restrict__ block_table, int table_stride, const bf16* __restrict__ k_cache,
                    const bf16* __restrict__ v_cache, int Hq, int Hkv, int page_size, int num_pages, int window,
                    float scale_log2e, int nsplit, float* __restrict__ partial_o, float* __restrict__ partial_ml,
-                   int* __restrict__ counters, int* status) {
+                   int* __restrict__ counters, int* status, const FusedQkv fq) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_is_last;
     __shared__ float s_row_max[DEC_HEADS];
+    __shared__ __align__(16) bf16 s_q[FUSED ? DEC_HEADS * D : 8];      // the rotated query heads, when the kernel makes them
     tw_grid_wait();
     const int s = blockIdx.z, kvh = blockIdx.y;
     const int split = blockIdx.x % nsplit, ht = blockIdx.x / nsplit;
@@ -174,9 +223,43 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
     }
     __syncthreads();
 
+    // ---- with FUSED: bias, rotation by position and the cache write of the step's new token, done here instead
+    // of in a kernel of their own (same arithmetic and the same order of the slice sums as that kernel).
+    constexpr int half = D / 2;
+    const int width = (Hq + 2 * Hkv) * D;
+    if constexpr (FUSED) {
+        // The block whose slice holds the newest position writes that position's key and value before any of its
+        // copies starts (its slice is the last one with keys, and as a rule the shortest).
+        if (fq.k_cache && pos >= k_begin && pos < k_end) {
+            const int blk = pos / page_size;
+            const int page = blk < table_stride ? table[blk] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (threadIdx.x == 0) atomicOr(status, TW_ERR_PAGE);
+            } else {
+                const size_t off = (((size_t)page * Hkv + kvh) * page_size + (pos - blk * page_size)) * D;
+                for (int i = threadIdx.x; i < D; i += DEC_WARPS * 32) {
+                    // thread i: pair i of the key if i < D / 2, and element i of the value
+                    const int ik = i < half ? i : 0;
+                    const int cols[3] = {(Hq + kvh) * D + ik, (Hq + kvh) * D + ik + half, (Hq + Hkv + kvh) * D + i};
+                    float x[3];
+                    product_cols<3>(fq, (size_t)n, width, cols, x);
+                    if (i < half) {
+                        float sn = 0.f, cs = 1.f;
+                        if (fq.inv_freq) sincosf((float)pos * fq.inv_freq[i], &sn, &cs);
+                        fq.k_cache[off + i] = __float2bfloat16_rn(x[0] * cs - x[1] * sn);
+                        fq.k_cache[off + i + half] = __float2bfloat16_rn(x[1] * cs + x[0] * sn);
+                    }
+                    fq.v_cache[off + i] = __float2bfloat16_rn(x[2]);
+                }
+            }
+            __threadfence();
+            __syncthreads();
+        }
+    }
+
     // q as the B operand: head h0 + g, with the same order of d as the key fragments
     KFrag qf;
-    {
+    if constexpr (!FUSED) {
         const bool valid = g < nheads;
         const bf16* qrow = q + (size_t)n * q_stride + (size_t)(kvh * G + h0 + (valid ? g : 0)) * D;
 #pragma unroll
@@ -237,6 +320,43 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
     stage_tile(0, 0);
     load_k(0, 0, ka_next, kb_next);
     stage_tile(1, 1);
+    if constexpr (FUSED) {
+        // While the first keys and values are on their way: this block's query heads, rotated, into shared memory
+        // (computed once for the block), from where every warp takes its fragments.
+        constexpr int PQ = (DEC_HEADS * half + DEC_WARPS * 32 - 1) / (DEC_WARPS * 32);     // pairs per thread
+        int cols[2 * PQ];
+        float x[2 * PQ];
+#pragma unroll
+        for (int j = 0; j < PQ; ++j) {
+            const int p = threadIdx.x + j * DEC_WARPS * 32;
+            const int head = p / half, i = p - head * half;
+            const bool live = p < DEC_HEADS * half && head < nheads;
+            cols[2 * j] = live ? (kvh * G + h0 + head) * D + i : 0;
+            cols[2 * j + 1] = cols[2 * j] + half;
+        }
+        product_cols<2 * PQ>(fq, (size_t)n, width, cols, x);
+#pragma unroll
+        for (int j = 0; j < PQ; ++j) {
+            const int p = threadIdx.x + j * DEC_WARPS * 32;
+            if (p < DEC_HEADS * half) {
+                const int head = p / half, i = p - head * half;
+                float y1 = 0.f, y2 = 0.f;
+                if (head < nheads) {
+                    float sn = 0.f, cs = 1.f;
+                    if (fq.inv_freq) sincosf((float)pos * fq.inv_freq[i], &sn, &cs);
+                    y1 = x[2 * j] * cs - x[2 * j + 1] * sn;
+                    y2 = x[2 * j + 1] * cs + x[2 * j] * sn;
+                }
+                s_q[head * D + i] = __float2bfloat16_rn(y1);
+                s_q[head * D + i + half] = __float2bfloat16_rn(y2);
+            }
+        }
+        __syncthreads();
+        const bf16* qrow = s_q + g * D;                     // zero beyond nheads
+#pragma unroll
+        for (int jb = 0; jb < DB32; ++jb) qf.blk[jb] = *reinterpret_cast<const uint4*>(qrow + 32 * jb + 8 * c);
+        qf.tail = DTAIL16 ? *reinterpret_cast<const uint2*>(qrow + 32 * DB32 + 4 * c) : make_uint2(0u, 0u);
+    }
     for (int t = 0; t < ntiles; ++t) {
         const int st = t % DEC_STAGES;
         const KFrag ka = ka_next, kb_ = kb_next;
@@ -681,11 +801,17 @@ bool g_attrs_set = false;
 
 int set_attrs() {
     if (g_attrs_set) return 0;
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+    e = cudaFuncSetAttribute(attn_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    e = cudaFuncSetAttribute(attn_decode_kernel<true, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_decode_kernel<true, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
     if (e != cudaSuccess) return (int)e;
@@ -711,7 +837,7 @@ bool decode_cluster_ok(int size) {
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         int clusters = 0;
-        const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, attn_decode_kernel<true>, &cfg);
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, attn_decode_kernel<true, false>, &cfg);
         if (e != cudaSuccess) (void)cudaGetLastError();
         g_cluster_ok[size] = (e == cudaSuccess && clusters >= 1) ? 1 : -1;
     }
@@ -747,14 +873,53 @@ TW_EXPORT int tw_attn_decode(void* out, int out_stride, const void* q, int q_str
     float* partial_ml = scratch ? scratch + (size_t)n_seqs * Hq * nsplit * D : nullptr;
     dim3 grid(nsplit * htiles, Hkv, n_seqs);
     if (nsplit > 1 && !(flags & 1) && decode_cluster_ok(nsplit))
-        return tw_launch(attn_decode_kernel<true>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, nsplit,
+        return tw_launch(attn_decode_kernel<true, false>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, nsplit,
             (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
             table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
-            scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status);
-    tw_launch(attn_decode_kernel<false>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
+            scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, FusedQkv{});
+    tw_launch(attn_decode_kernel<false, false>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
         (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
-        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status);
+        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, FusedQkv{});
+    return TW_LAUNCH_CHECK();
+}
+
+// The same for a decode-only step whose q/k/v product has not been touched yet: the kernel adds the bias,
+// rotates q and k by position, writes the new key and value to their cache pages and attends, so the step
+// needs no kernel between the product and the attention.  The product is given as fp32 slices
+// [nslices][rows][(Hq + 2 Hkv) D] (`partial`) or as bf16 rows (`dense`); `bias` and `inv_freq` may be null;
+// with write_cache 0 the cache is read only (the new position must then be in it already).
+TW_EXPORT int tw_attn_decode_fused(void* out, int out_stride, const float* partial, int nslices, long long slice_stride,
+                                   const void* dense, int dense_stride, const float* bias, const float* inv_freq,
+                                   int write_cache, const int* seq_q_start, const int* seq_q_len, const int* seq_kv_len,
+                                   const int* seq_slot, const int* block_table, int table_stride, void* k_cache,
+                                   void* v_cache, int n_seqs, int Hq, int Hkv, int page_size, int num_pages, int window,
+                                   float scale, int nsplit, int flags, float* scratch, int* counters, int* status,
+                                   cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (Hkv <= 0 || Hq % Hkv || nsplit < 1 || (nsplit > 1 && (!scratch || !counters)) || (!partial && !dense) ||
+        (partial && nslices < 1))
+        return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)out & 7) || (out_stride & 3) || ((uintptr_t)scratch & 15)) return (int)cudaErrorMisalignedAddress;
+    if (int e = set_attrs()) return e;
+    const int G = Hq / Hkv, htiles = (G + DEC_HEADS - 1) / DEC_HEADS;
+    float* partial_o = scratch;
+    float* partial_ml = scratch ? scratch + (size_t)n_seqs * Hq * nsplit * D : nullptr;
+    FusedQkv fq;
+    fq.partial = partial; fq.nslices = nslices; fq.slice_stride = slice_stride;
+    fq.dense = (const bf16*)dense; fq.dense_stride = dense_stride; fq.bias = bias; fq.inv_freq = inv_freq;
+    fq.k_cache = write_cache ? (bf16*)k_cache : nullptr;
+    fq.v_cache = write_cache ? (bf16*)v_cache : nullptr;
+    dim3 grid(nsplit * htiles, Hkv, n_seqs);
+    if (nsplit > 1 && !(flags & 1) && decode_cluster_ok(nsplit))
+        return tw_launch(attn_decode_kernel<true, true>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, nsplit,
+            (bf16*)out, out_stride, (const bf16*)nullptr, 0, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
+            table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
+            scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, fq);
+    tw_launch(attn_decode_kernel<false, true>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1,
+        (bf16*)out, out_stride, (const bf16*)nullptr, 0, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
+        table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
+        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, fq);
     return TW_LAUNCH_CHECK();
 }
 
@@ -840,9 +1005,9 @@ TW_EXPORT int tw_attn_decode_static(void* out, int out_stride, const void* q, in
     e = cudaMemsetAsync(counters, 0, counter_bytes, stream);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(nsplit * htiles, Hkv, n_seqs);
-    tw_launch(attn_decode_kernel<false>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
+    tw_launch(attn_decode_kernel<false, false>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
         (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
-        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status);
+        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, FusedQkv{});
     return TW_LAUNCH_CHECK();
 }

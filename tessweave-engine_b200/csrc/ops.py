@@ -350,6 +350,62 @@ def attention_decode(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block
     _check(code, "attention_decode")
 
 
+def fused_decode_enabled() -> bool:
+    """TESSWEAVE_FUSED_DECODE=0 keeps bias, rotation and cache write of decode-only steps in a kernel of their own."""
+    import os
+    return os.environ.get("TESSWEAVE_FUSED_DECODE", "1") != "0"
+
+
+def attention_decode_fused(out, source, bias, inv_freq, write_cache, seq_q_start, seq_q_len, seq_kv_len, seq_slot,
+                           block_table, k_pages, v_pages, n_seqs, n_q_heads, n_kv_heads, head_dim, window, scale,
+                           nsplit, scratch, counters, status, merge_in_scratch: bool = False) -> None:
+    """Decode attention straight from the q/k/v product of a decode-only step: the kernel adds ``bias``,
+    rotates q and k by position (``inv_freq``), writes the new key and value into their cache pages
+    (``write_cache``) and attends.  ``source`` is the product: a ``SplitSum`` of fp32 slices or a bf16
+    [rows, (Hq + 2 Hkv) D] tensor.  The other arguments are those of ``attention_decode``."""
+    width = (n_q_heads + 2 * n_kv_heads) * head_dim
+    partial = dense = None
+    nslices = slice_stride = dense_stride = 0
+    if isinstance(source, SplitSum):
+        partial = source.slices
+        _need(partial.is_cuda and partial.dtype == torch.float32 and partial.dim() == 3 and partial.shape[2] == width
+              and partial[0].is_contiguous(), "attention_decode_fused: bad split source")
+        nslices, slice_stride = partial.shape[0], partial.stride(0)
+    else:
+        dense = source
+        _need(dense.is_cuda and dense.dtype == torch.bfloat16 and dense.dim() == 2 and dense.shape[1] == width
+              and dense.stride(1) == 1, "attention_decode_fused: the product must be bf16 [rows, (Hq + 2 Hkv) D]")
+        dense_stride = dense.stride(0)
+    _cuda(out, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, scratch, counters, status,
+          bias, inv_freq)
+    _need(tensor_core_attention_supported(out.dtype, head_dim) and out.dtype == k_pages.dtype == v_pages.dtype,
+          "attention_decode_fused: bfloat16 and a head size that is a multiple of 16 up to 256")
+    _need(n_q_heads % n_kv_heads == 0, "attention: query heads must be a multiple of key/value heads")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape[3] == head_dim
+          and k_pages.shape[1] == n_kv_heads and v_pages.shape == k_pages.shape,
+          "attention: cache pages must be contiguous [pages, kv_heads, page, head_dim]")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: bad block table")
+    _need(out.stride(1) == 1 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0,
+          "attention_decode_fused: output rows must be 8-byte aligned")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == width), "attention_decode_fused: bias must be fp32")
+    _need(inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2),
+          "attention_decode_fused: inv_freq must be fp32 [D/2]")
+    if nsplit > 1:
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.data_ptr() % 16 == 0
+              and scratch.numel() >= n_seqs * n_q_heads * nsplit * (head_dim + 2), "attention_decode: scratch too small")
+        _need(counters is not None and counters.dtype == torch.int32
+              and counters.numel() >= n_seqs * n_kv_heads * ((n_q_heads // n_kv_heads + 7) // 8),
+              "attention_decode: too few counters")
+    code = _fn("attention_bf16", "tw_attn_decode_fused", {"TW_HEAD_DIM": head_dim})(
+        _ptr(out), c_int(out.stride(0)), _ptr(partial), c_int(nslices), ctypes.c_longlong(slice_stride), _ptr(dense),
+        c_int(dense_stride), _ptr(bias), _ptr(inv_freq), c_int(1 if write_cache else 0), _ptr(seq_q_start), _ptr(seq_q_len),
+        _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages),
+        c_int(n_seqs), c_int(n_q_heads), c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]),
+        c_int(window), c_float(scale), c_int(nsplit), c_int(1 if merge_in_scratch else 0), _ptr(scratch), _ptr(counters),
+        _ptr(status), _stream())
+    _check(code, "attention_decode_fused")
+
+
 def attention_prefill_tcgen05(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, n_seqs,
                               max_q_len, n_q_heads, n_kv_heads, head_dim, window, scale, skip_single, status) -> None:
     """The same as ``attention_prefill`` on the 5th-generation tensor cores (TMA, tcgen05.mma,

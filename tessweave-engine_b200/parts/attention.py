@@ -67,6 +67,12 @@ class GQAAttention(Mixer):
         source = None
         if isinstance(qkv, SplitSum):       # the fused kernel below adds the slices itself
             source, qkv = qkv, ws.get("attn.qkv", (n, self.qkv_width), dt)
+        out = ws.get("attn.out", (n, self.q_size), dt)
+        if (table is not None and ctx.decode_only and ops.fused_decode_enabled()
+                and ops.tensor_core_attention_supported(dt, self.head_dim)):
+            # decode-only step: the attention kernel adds the bias, rotates, writes the new key and value and attends
+            self._decode(ctx, out, None, cache, fused=(source if source is not None else qkv, table, write_cache))
+            return linear(ctx, "mixer.delta", out, self.w_o, allow_split=ctx.split_ok)
         if table is None:
             # generic path: bias, then the position part's own transformation, then the cache write
             if self.b_qkv is not None:
@@ -79,7 +85,6 @@ class GQAAttention(Mixer):
         ops.rope_kv_write(qkv, bias, ctx.positions, ctx.seq_of_token, ctx.seq_slot, cache.block_table, table,
                           cache.k_pages, cache.v_pages, n, self.n_heads, self.n_kv_heads, self.head_dim,
                           write_cache, ctx.status, source=source)
-        out = ws.get("attn.out", (n, self.q_size), dt)
         self._attend(ctx, out, qkv, cache)
         return linear(ctx, "mixer.delta", out, self.w_o, allow_split=ctx.split_ok)
 
@@ -98,16 +103,29 @@ class GQAAttention(Mixer):
                                   cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, ctx.max_q_len,
                                   self.n_heads, self.n_kv_heads, self.head_dim, window, self.scale, singles, ctx.status)
         if singles:
-            nsplit = ops.decode_splits(ctx.n_seqs, self.n_kv_heads, self.n_heads // self.n_kv_heads, ctx.max_kv_len)
-            scratch = ctx.workspace.get("attn.decode_scratch", (ops.decode_scratch_floats(self.n_heads, self.head_dim),),
-                                        torch.float32)
-            counters = ctx.workspace.get(
-                "attn.decode_counters", (ops.decode_counter_ints(ctx.n_seqs, self.n_kv_heads, self.n_heads // self.n_kv_heads),),
-                torch.int32, zero=True)
-            ops.attention_decode(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
-                                 cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, self.n_heads,
-                                 self.n_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, counters,
-                                 ctx.status)
+            self._decode(ctx, out, q, cache)
+
+    def _decode(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor | None, cache: PagedView, fused=None) -> None:
+        """Split-KV attention for the requests that bring one token; with ``fused`` = (product, rotation table,
+        write_cache) the kernel makes q, k and v of the new token from the product itself."""
+        nsplit = ops.decode_splits(ctx.n_seqs, self.n_kv_heads, self.n_heads // self.n_kv_heads, ctx.max_kv_len)
+        scratch = ctx.workspace.get("attn.decode_scratch", (ops.decode_scratch_floats(self.n_heads, self.head_dim),),
+                                    torch.float32)
+        counters = ctx.workspace.get(
+            "attn.decode_counters", (ops.decode_counter_ints(ctx.n_seqs, self.n_kv_heads, self.n_heads // self.n_kv_heads),),
+            torch.int32, zero=True)
+        window = self.window or 0
+        if fused is not None:
+            product, table, write_cache = fused
+            ops.attention_decode_fused(out, product, self.b_qkv, table, write_cache, ctx.seq_q_start, ctx.seq_q_len,
+                                       ctx.seq_kv_len, ctx.seq_slot, cache.block_table, cache.k_pages, cache.v_pages,
+                                       ctx.n_seqs, self.n_heads, self.n_kv_heads, self.head_dim, window, self.scale,
+                                       nsplit, scratch, counters, ctx.status)
+            return
+        ops.attention_decode(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
+                             cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, self.n_heads,
+                             self.n_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, counters,
+                             ctx.status)
 
     def _attend(self, ctx: StepContext, out: torch.Tensor, qkv: torch.Tensor, cache: PagedView) -> None:
         q = qkv[:, : self.q_size]

@@ -605,3 +605,57 @@ def test_gemm_tcgen05_pair_silu_mul(m, n, k):
     y = (x.float() @ w.float().t()).reshape(m, n // 16, 2, 8)
     want = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(m, n // 2)
     assert torch.allclose(out.float(), want, rtol=2e-2, atol=2e-2)
+
+
+# ---------------------------------------------------------------------------
+# decode attention that makes q, k and v of the new token itself
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (6, 3, 48), (8, 8, 16), (20, 2, 64)])
+@pytest.mark.parametrize("split_source", [False, True])
+@pytest.mark.parametrize("window", [0, 40])
+def test_decode_attention_fused_with_rotation_and_cache_write(hq, hkv, d, split_source, window):
+    """The fused kernel against the two kernels it replaces (bias + rotation + cache write, then decode
+    attention): the same attention output and the same cache contents, bit for bit, for requests whose
+    newest position is a page's first slot, its last slot, position 0 and somewhere in between."""
+    o = ops()
+    lengths = [1, 16 * 9 + 1, 16 * 11, 300]
+    page = 16
+    setup = paged_setup(lengths, page, hkv, d, torch.bfloat16, seed=hq + d)
+    n = len(lengths)
+    width = (hq + 2 * hkv) * d
+    g = torch.Generator().manual_seed(3)
+    bias = dev(torch.randn(width, generator=g))
+    inv = dev(1e4 ** (-torch.arange(0, d, 2, dtype=torch.float32) / d))
+    i32 = lambda v: dev(torch.tensor(v, dtype=torch.int32))
+    q_start, q_len, kv_len, slot = i32(list(range(n))), i32([1] * n), i32(lengths), i32(setup["slots"])
+    positions, seq_of = i32([m - 1 for m in lengths]), i32(list(range(n)))
+    if split_source:
+        slices = dev(torch.randn(5, n, width, generator=g))
+        source = o.SplitSum(slices)
+        dense = torch.zeros(n, width, device="cuda", dtype=torch.bfloat16)
+    else:
+        dense = dev(torch.randn(n, width, generator=g), torch.bfloat16)
+        source = None
+    ns = 3
+    scratch = torch.full((o.decode_scratch_floats(hq, d),), float("nan"), device="cuda")
+    counters = torch.zeros(o.decode_counter_ints(n, hkv, hq // hkv), dtype=torch.int32, device="cuda")
+    st = status()
+    # the two kernels
+    k_a, v_a = setup["k_pages"].clone(), setup["v_pages"].clone()
+    qkv_a = dense.clone()
+    o.rope_kv_write(qkv_a, bias, positions, seq_of, slot, setup["table"], inv, k_a, v_a, n, hq, hkv, d, True, st, source=source)
+    out_a = torch.full((n, hq * d), float("nan"), device="cuda", dtype=torch.bfloat16)
+    o.attention_decode(out_a, qkv_a[:, : hq * d], q_start, q_len, kv_len, slot, setup["table"], k_a, v_a, n, hq, hkv, d, window,
+                       d ** -0.5, ns, scratch, counters, st)
+    # the fused kernel, through both ways of merging the slices
+    for merge_in_scratch in (False, True):
+        k_b, v_b = setup["k_pages"].clone(), setup["v_pages"].clone()
+        out_b = torch.full((n, hq * d), float("nan"), device="cuda", dtype=torch.bfloat16)
+        o.attention_decode_fused(out_b, source if source is not None else dense, bias, inv, True, q_start, q_len, kv_len, slot,
+                                 setup["table"], k_b, v_b, n, hq, hkv, d, window, d ** -0.5, ns, scratch, counters, st,
+                                 merge_in_scratch=merge_in_scratch)
+        assert int(st) == 0
+        assert torch.equal(k_a.view(torch.int16), k_b.view(torch.int16)), "keys written differ"
+        assert torch.equal(v_a.view(torch.int16), v_b.view(torch.int16)), "values written differ"
+        assert not torch.isnan(out_b.float()).any()
+        assert torch.equal(out_a.view(torch.int16), out_b.view(torch.int16)), "attention output differs"
