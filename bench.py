@@ -187,14 +187,18 @@ def prefill_run(model, cfg, tokens: int, reps: int, warmup: int):
     for _ in range(warmup):
         runner.step(entry)
     torch.cuda.synchronize()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    begin.record()
+    # every repetition is timed by itself and the median is reported: a 25 ms burst of tensor-core work is
+    # sensitive to where the power management happens to be
+    times = []
     for _ in range(reps):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
         runner.step(entry)
-    end.record()
-    torch.cuda.synchronize()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(begin.elapsed_time(end))
     runner.check_status()
-    ms = begin.elapsed_time(end) / reps
+    ms = statistics.median(times)
     L, H, I, V = cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
     qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
     linear = 2.0 * tokens * L * (H * qkv + cfg.num_attention_heads * cfg.head_dim * H + 3 * H * I)
@@ -405,7 +409,7 @@ def main() -> int:
     kernels = main_run["kernels_per_step"]
     record["gpu_launches"] = int(kernels * args.steps) if kernels else int(main_run["eager_launches"])
     if not args.skip_extras:
-        pre = prefill_run(model, cfg, PREFILL_TOKENS, reps=3, warmup=3)
+        pre = prefill_run(model, cfg, PREFILL_TOKENS, reps=7, warmup=3)
         peak_flops = pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]) * 1e12
         record["prefill"] = {"value": round(pre["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pre["ms"], 3),
                              "frac": round(pre["flops"] / (pre["ms"] / 1e3) / peak_flops, 4)}

@@ -192,10 +192,14 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
     __shared__ int s_is_last;
     __shared__ float s_row_max[DEC_HEADS];
     __shared__ __align__(16) bf16 s_q[FUSED ? DEC_HEADS * D : 8];      // the rotated query heads, when the kernel makes them
-    tw_grid_wait();
+    // The request arrays and the block table are written before the step's first kernel starts, not by the
+    // kernel before this one: they are read before the wait for that kernel, while it is still finishing.
     const int s = blockIdx.z, kvh = blockIdx.y;
     const int split = blockIdx.x % nsplit, ht = blockIdx.x / nsplit;
-    if (seq_q_len[s] != 1) return;
+    if (seq_q_len[s] != 1) {
+        tw_grid_wait();             // a block never finishes before the kernel before this one has
+        return;
+    }
     const int G = Hq / Hkv, h0 = ht * DEC_HEADS;
     const int nheads = min(DEC_HEADS, G - h0);
     const int n = seq_q_start[s];
@@ -222,6 +226,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
             page_cache[i] = first_blk + i < table_stride ? table[first_blk + i] : -1;
     }
     __syncthreads();
+    tw_grid_wait();
 
     // ---- with FUSED: bias, rotation by position and the cache write of the step's new token, done here instead
     // of in a kernel of their own (same arithmetic and the same order of the slice sums as that kernel).

@@ -95,6 +95,9 @@ __device__ __forceinline__ void tw_grid_launch_dependents() {
 #endif
 }
 __device__ __forceinline__ void tw_grid_launch_dependents_late() { tw_grid_launch_dependents(); }
+// The exception, measured to pay: kernels whose successor is small (or whose own blocks are few) let it
+// become resident at once.  Used by the clustered norm and, on request, by the small-M product.
+__device__ __forceinline__ void tw_launch_dependents_now() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #ifndef __CUDA_ARCH__
 #include <stdlib.h>

@@ -145,7 +145,7 @@ add_rmsnorm_cluster_kernel(T* __restrict__ out, float* __restrict__ resid, const
     __shared__ float scratch[33];
     __shared__ float my_ss;
     tw_grid_wait();
-    tw_grid_launch_dependents();
+    tw_launch_dependents_now();     // 64 small blocks: the product that follows may settle on the SMs meanwhile (1 % of a decode step)
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int r = blockIdx.x / TW_NORM_CLUSTER;

@@ -462,10 +462,12 @@ def small_m_split(n: int, k: int) -> tuple[int, int]:
 
 
 def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kper: int | None = None,
-                 silu_mul_pairs: bool = False) -> None:
+                 silu_mul_pairs: bool = False, early_dependents: bool = False) -> None:
     """out[:m] = x[:m] @ w.T for m <= 64 rows.  ``out`` is bf16 or fp32 [>=m, n]; or, when the
     product is split over k (kper < k), fp32 slices [slices, m, n]; or, with ``silu_mul_pairs``
-    (rows of w in groups of eight gates and their eight ups), bf16 [>=m, n / 2] = silu(gate) * up."""
+    (rows of w in groups of eight gates and their eight ups), bf16 [>=m, n / 2] = silu(gate) * up.
+    ``early_dependents``: the kernel launched next may become resident while this one runs (it waits for
+    the result itself); worth it when that kernel is small."""
     _cuda(out, x, w)
     n, k = w.shape
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x.is_contiguous()
@@ -484,6 +486,8 @@ def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kp
         _need(out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= m and out.shape[1] == n
               and out.dtype in (torch.bfloat16, torch.float32), "gemm_small_m: bad output")
         mode, stride = (0 if out.dtype == torch.bfloat16 else 1), out.stride(0)
+    if early_dependents:
+        mode |= 16          # the kernel after this one may become resident while this one runs
     code = _fn("gemm_smallm", "tw_gemm_smallm")(_ptr(w), _ptr(x), c_int(m), c_int(n), c_int(k), c_int(kper), _ptr(out),
                                                 c_int(mode), c_int(stride), _stream())
     _check(code, "gemm_small_m")

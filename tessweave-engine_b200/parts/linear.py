@@ -41,7 +41,7 @@ def matmul_nt(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tens
 
 
 def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-           allow_split: bool = False):
+           allow_split: bool = False, small_consumer: bool = False):
     """``x @ w.T`` into the workspace buffer ``name``.
 
     Steps with few rows (decode) in bfloat16 go through hand-written kernels: up to 8 rows
@@ -49,7 +49,8 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
     csrc/gemm_tcgen05.cu with the weights as the 128-row operand.  When the matrix has too few
     rows to fill the GPU these kernels split k and, if the caller can take it
     (``allow_split``), the fp32 slices are returned as a ``SplitSum`` for the consuming kernel
-    to add.  Everything else is a library product.
+    to add.  Everything else is a library product.  ``small_consumer`` says that the kernel that follows is
+    a small one (a norm, a sampler): the weight-streaming kernel then lets it become resident early.
     """
     m, n = x.shape[0], w.shape[0]
     dtype = out_dtype or x.dtype
@@ -69,13 +70,13 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
         split, kper = ops.small_m_split(n, w.shape[1])
         if split > 1 and allow_split:
             slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
-            ops.gemm_small_m(slices, x, w, m, kper)
+            ops.gemm_small_m(slices, x, w, m, kper, early_dependents=small_consumer)
             return SplitSum(slices)
         if split > 1:
             slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
             ops.gemm_small_m(slices, x, w, m, kper)
             return SplitSum(slices).dense(dtype, ctx.workspace.get(name, (m, n), dtype))
         out = ctx.workspace.get(name, (m, n), dtype)
-        ops.gemm_small_m(out, x, w, m)
+        ops.gemm_small_m(out, x, w, m, early_dependents=small_consumer)
         return out
     return matmul_nt(ctx.workspace.get(name, (m, n), dtype), x, w)
