@@ -167,16 +167,32 @@ add_rmsnorm_cluster_kernel(T* __restrict__ out, float* __restrict__ resid, const
             if (d) {
                 dv = tw_to_float(d[i]);
             } else if (ps) {
-                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-                int k = 0;
-                for (; k + 4 <= nsplit; k += 4) {
-                    s0 += ps[(size_t)k * split_stride + i];
-                    s1 += ps[(size_t)(k + 1) * split_stride + i];
-                    s2 += ps[(size_t)(k + 2) * split_stride + i];
-                    s3 += ps[(size_t)(k + 3) * split_stride + i];
+                // The slices are summed in the order every consumer of a split product uses: whole groups of
+                // four into four sums by k mod 4, the rest into the first, then (s0 + s1) + (s2 + s3).  The
+                // first sixteen are loaded before anything is added, so that they are one round trip to L2
+                // and not one per group (this kernel is nothing but latency).
+                float t[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) t[u] = u < nsplit ? ps[(size_t)u * split_stride + i] : 0.f;
+                const int full = nsplit & ~3;
+                float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int u = 0; u < 16; ++u) {
+                    if (u < full) sum[u & 3] += t[u];
                 }
-                for (; k < nsplit; ++k) s0 += ps[(size_t)k * split_stride + i];
-                dv = (s0 + s1) + (s2 + s3);
+                int k = 16;
+                for (; k + 4 <= nsplit; k += 4) {
+                    sum[0] += ps[(size_t)k * split_stride + i];
+                    sum[1] += ps[(size_t)(k + 1) * split_stride + i];
+                    sum[2] += ps[(size_t)(k + 2) * split_stride + i];
+                    sum[3] += ps[(size_t)(k + 3) * split_stride + i];
+                }
+#pragma unroll
+                for (int u = 0; u < 16; ++u) {
+                    if (u >= full && u < nsplit) sum[0] += t[u];
+                }
+                for (k = max(k, full); k < nsplit; ++k) sum[0] += ps[(size_t)k * split_stride + i];
+                dv = (sum[0] + sum[1]) + (sum[2] + sum[3]);
             }
             v[j] = x[i] + dv;
             if (!rows && has_delta) x[i] = v[j];
