@@ -282,10 +282,9 @@ def prefer_tcgen05_attention(dtype: torch.dtype, head_dim: int, page_size: int, 
 def decode_splits(n_seqs: int, n_kv_heads: int, group: int, max_kv_len: int) -> int:
     """How many slices the keys of a request are cut into, so that the launch fills the GPU.
     Up to 16 slices merge inside a thread-block cluster, which saves 2-3 us over the merge through
-    scratch memory; clusters of 16 are only placed well when there are few of them, so with many
-    (request, head) groups 13..16 slices become 12 (measured on B200: batch 8, 4 key/value heads,
-    4096 keys: 24.2 us with 12 slices in clusters, 24.7 with 16 through scratch, 31.1 with 16 in
-    clusters)."""
+    scratch memory; clusters of 15 and 16 are only placed well when there are few of them, so with many
+    (request, head) groups 15 and 16 slices become 14 (measured on B200, batch 8, 4 key/value heads,
+    4096 keys, a whole decode step: 3.61 ms with 13 or 14 slices, 3.64 with 12, 3.94 with 16, 4.02 with 15)."""
     import os
     forced = os.environ.get("TESSWEAVE_DECODE_SPLITS")
     if forced:
@@ -296,11 +295,13 @@ def decode_splits(n_seqs: int, n_kv_heads: int, group: int, max_kv_len: int) -> 
     # the kernel fits four blocks on an SM; aim at a little under one full wave of blocks
     target = max(1, (7 * _SM_COUNT // 2) // groups)
     nsplit = max(1, min(tiles, target, 128, DECODE_SCRATCH_UNITS // max(1, n_seqs)))
-    if 12 < nsplit <= 16 and groups > 8 and max_kv_len < 8192:
-        nsplit = 12
+    if 14 < nsplit <= 16 and groups > 8 and max_kv_len < 8192:
+        nsplit = 14
     elif 16 < nsplit <= 64 and groups <= 8 and max_kv_len <= 8192:
         nsplit = 16
-    return nsplit
+    # the kernel cuts the keys into slices of a multiple of 64 keys: no slice without keys
+    per = -(-(-(-max_kv_len // nsplit)) // 64) * 64
+    return max(1, -(-max_kv_len // per))
 
 
 def decode_scratch_floats(n_q_heads: int, head_dim: int) -> int:
