@@ -610,7 +610,7 @@ def test_gemm_tcgen05_pair_silu_mul(m, n, k):
 # ---------------------------------------------------------------------------
 # decode attention that makes q, k and v of the new token itself
 # ---------------------------------------------------------------------------
-@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (6, 3, 48), (8, 8, 16), (20, 2, 64)])
+@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (6, 3, 48), (8, 8, 16), (20, 2, 64), (4, 2, 256)])
 @pytest.mark.parametrize("split_source", [False, True])
 @pytest.mark.parametrize("window", [0, 40])
 def test_decode_attention_fused_with_rotation_and_cache_write(hq, hkv, d, split_source, window):

@@ -180,11 +180,14 @@ CUTS = [[61], [7, 2, 13, 3, 2, 16, 1, 17], [1] * 61]
 
 
 # ---------------------------------------------------------------------------
-def test_layer_twice_and_layer_reading_anothers_cache():
-    """Schedule: layer 0, layer 1, layer 0 again (own cache), layer 1 reading the cache of its first run."""
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layer_twice_and_layer_reading_anothers_cache(dtype):
+    """Schedule: layer 0, layer 1, layer 0 again (own cache), layer 1 reading the cache of its first run.
+    In bfloat16 the single-token steps go through the decode attention that makes q, k and v itself: the run
+    that reads another run's cache must then rotate its query but write nothing."""
     spec = spec_of([block(attention()), block(attention())],
                    [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, cache_of=1)])
-    model, cache, runner, w = build(spec)
+    model, cache, runner, w = build(spec, dtype=dtype)
     assert len(cache.groups) == 1 and cache.groups[0].k.shape[0] == 3         # three caches for four runs
     pos = list(range(len(TOKENS)))
     x = w["embed.weight"][TOKENS]
@@ -193,9 +196,10 @@ def test_layer_twice_and_layer_reading_anothers_cache():
     x, _ = plain_attention_block(w, "layers.0", x, pos); x = plain_swiglu(w, "layers.0", x)
     x, _ = plain_attention_block(w, "layers.1", x, pos, keys_from=kv1); x = plain_swiglu(w, "layers.1", x)
     want = plain_head(w, x)
+    tol = 1e-4 if dtype == torch.float32 else 0.03 * max(1.0, float(want.abs().max()))
     for cuts in CUTS:
         got = run_cut(cache, runner, TOKENS, cuts)
-        assert float((got - want).abs().max()) <= 1e-4, cuts[:3]
+        assert float((got - want).abs().max()) <= tol, cuts[:3]
 
 
 def test_window_group_has_pages_of_its_own_and_returns_them():
