@@ -421,6 +421,12 @@ def main() -> int:
         e2e = e2e_run(model, cfg, args.batch, args.context, args.steps, args.warmup)
         record["e2e"] = {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms_per_step"], 4),
                          "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]}
+        # the dominant kernel of both regimes (the gate/up product) alone, against its own roofline
+        from tessweave_engine_b200.engine.kernel_bench import kernel_table
+        rows = kernel_table(cfg, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE,
+                            only=("gate/up",))
+        record["dominant_kernel"] = {r["op"]: {"kernel": r["kernel"], "us": r["us"], "frac": r["frac"], "bound": r["bound"]}
+                                     for r in rows}
     sampler.stop()
     record["clocks"] = clocks
     print(json.dumps(record))

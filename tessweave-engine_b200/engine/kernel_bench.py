@@ -52,7 +52,8 @@ def _copies(nbytes: int) -> int:
 
 
 def kernel_table(cfg, batch: int, context: int, prefill_tokens: int, hbm_gbs: float, tflops: float,
-                 page_size: int = 16) -> list[dict]:
+                 page_size: int = 16, only: tuple[str, ...] | None = None) -> list[dict]:
+    """All rows, or with ``only`` the rows whose operation name contains one of the given words."""
     dev = torch.device("cuda")
     bf = torch.bfloat16
     H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
@@ -62,6 +63,9 @@ def kernel_table(cfg, batch: int, context: int, prefill_tokens: int, hbm_gbs: fl
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)   # noqa: E731
 
+    def want(name: str) -> bool:
+        return only is None or any(word in name for word in only)
+
     def add(name, rows_m, us, nbytes, flops, kernel):
         floor = max(nbytes / (hbm_gbs * 1e9), flops / (tflops * 1e12)) * 1e6
         rows.append({"op": name, "rows": rows_m, "kernel": kernel, "us": round(us, 2), "mbytes": round(nbytes / 1e6, 2),
@@ -69,102 +73,128 @@ def kernel_table(cfg, batch: int, context: int, prefill_tokens: int, hbm_gbs: fl
                      "bound": "hbm" if nbytes / (hbm_gbs * 1e9) >= flops / (tflops * 1e12) else "tensor"})
 
     def product(name, m, n, k, fused_silu=False, out_dtype=None):
-        """x[m, k] @ w[n, k].T through the engine's routing; weights rotated beyond L2."""
+        """x[m, k] @ w[n, k].T the way the engine runs it; weights rotated beyond L2.  With ``fused_silu`` the
+        weights are gate/up rows and the step's SiLU.mul is part of the row where a kernel fuses it."""
+        fused = None
+        x = torch.randn(m, k, device=dev, dtype=bf)
+        probe = torch.empty(n, k, device=dev, dtype=bf)
+        if fused_silu and m <= ops.SMALL_M_LIMIT:
+            fused = "small"
+        elif fused_silu and ops.pair_product_preferred(x, probe, m):
+            fused = "pair"
+        del probe
+        if fused:
+            name += " + SiLU.mul"
+        if not want(name):
+            return
         copies = _copies(n * k * 2)
         ws = [torch.randn(n, k, device=dev, dtype=bf) * 0.02 for _ in range(copies)]
-        x = torch.randn(m, k, device=dev, dtype=bf)
         ctx = SimpleNamespace(workspace=Workspace(dev), status=status)
-        if fused_silu and m <= ops.SMALL_M_LIMIT:
-            out = torch.empty(m, n // 2, device=dev, dtype=bf)
+        out_cols = n
+        if fused == "small":
+            out_cols = n // 2
+            out = torch.empty(m, out_cols, device=dev, dtype=bf)
             calls = [(lambda w=w: ops.gemm_small_m(out, x, w, m, silu_mul_pairs=True)) for w in ws]
-            kernel = "gemm_smallm + SiLU.mul"
+            kernel = "gemm_smallm"
+        elif fused == "pair":
+            out_cols = n // 2
+            out = torch.empty(m, out_cols, device=dev, dtype=bf)
+            calls = [(lambda w=w: ops.gemm_tcgen05_pair(out, x, w, m, status, silu_mul_pairs=True)) for w in ws]
+            kernel = "gemm_tcgen05_pair (2-CTA)"
         else:
             calls = [(lambda w=w: linear(ctx, "p", x, w, out_dtype=out_dtype, allow_split=True)) for w in ws]
             kernel = ("gemm_smallm" if m <= ops.SMALL_M_LIMIT else
                       "gemm_tcgen05 (swap-AB)" if ops.TCGEN05_MIN_M <= m <= ops.TCGEN05_MAX_M else "library (cuBLAS)")
         us = _graph_us(calls)
-        out_bytes = m * (n // 2 if fused_silu and m <= ops.SMALL_M_LIMIT else n) * (4 if out_dtype == torch.float32 else 2)
+        out_bytes = m * out_cols * (4 if out_dtype == torch.float32 else 2)
         add(name, m, us, n * k * 2 + m * k * 2 + out_bytes, 2.0 * m * n * k, kernel)
         del ws
+        if fused_silu and not fused and want(name.split(":")[0] + ": SiLU.mul"):
+            gu = torch.randn(m, n, device=dev, dtype=bf)
+            act = torch.empty(m, n // 2, device=dev, dtype=bf)
+            us = _graph_us([lambda: ops.silu_mul(act, gu, m, True)], reps=4)
+            add(name.split(":")[0] + ": SiLU.mul", m, us, m * (n // 2) * 2 * 3, 0.0, "silu_mul")
 
     for m, phase in ((batch, "decode"), (prefill_tokens, "prefill")):
-        # residual add + RMSNorm
-        resid = torch.randn(m, H, device=dev)
-        delta = torch.randn(m, H, device=dev, dtype=bf)
-        weight = torch.ones(H, device=dev)
-        out = torch.empty(m, H, device=dev, dtype=bf)
-        us = _graph_us([lambda: ops.add_rmsnorm(out, resid, delta, weight, cfg.rms_norm_eps, m)], reps=8)
-        add(f"{phase}: residual add + RMSNorm", m, us, m * H * (4 + 4 + 2 + 2), 0.0, "add_rmsnorm")
+        elementwise = only is None or any(want(f"{phase}: {t}") for t in ("residual add + RMSNorm", "bias + RoPE + cache write",
+                                                                          "attention"))
+        if elementwise:
+            resid = torch.randn(m, H, device=dev)
+            delta = torch.randn(m, H, device=dev, dtype=bf)
+            weight = torch.ones(H, device=dev)
+            out = torch.empty(m, H, device=dev, dtype=bf)
+            us = _graph_us([lambda: ops.add_rmsnorm(out, resid, delta, weight, cfg.rms_norm_eps, m)], reps=8)
+            add(f"{phase}: residual add + RMSNorm", m, us, m * H * (4 + 4 + 2 + 2), 0.0, "add_rmsnorm")
         product(f"{phase}: qkv product", m, qkv_w, H)
-        # bias + RoPE + cache write
-        pages = -(-context // page_size) * batch if phase == "decode" else -(-m // page_size)
-        kp = torch.zeros(pages, Hkv, page_size, D, device=dev, dtype=bf)
-        vp = torch.zeros_like(kp)
-        qkv = torch.randn(m, qkv_w, device=dev, dtype=bf)
-        bias = torch.randn(qkv_w, device=dev)
-        inv = (cfg.rope_theta ** (-torch.arange(0, D, 2, dtype=torch.float32) / D)).to(dev)
-        if phase == "decode":
-            blocks = -(-context // page_size)
-            table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(batch, blocks)
-            positions, seq_of = i32([context - 1] * m), i32(list(range(m)))
-            slots = i32(list(range(batch)))
-        else:
-            table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, pages)
-            positions, seq_of = torch.arange(m, dtype=torch.int32, device=dev), torch.zeros(m, dtype=torch.int32, device=dev)
-            slots = i32([0])
-        us = _graph_us([lambda: ops.rope_kv_write(qkv, bias, positions, seq_of, slots, table, inv, kp, vp, m, Hq, Hkv, D,
-                                                  True, status)], reps=8)
-        add(f"{phase}: bias + RoPE + cache write", m, us, m * qkv_w * 2 * 2, 0.0, "rope_kv_write")
-        # attention
-        if phase == "decode":
-            nset = _copies(kp.numel() * 2 * 2)
-            sets = [(torch.randn_like(kp), torch.randn_like(vp)) for _ in range(nset)]
-            q = torch.randn(m, Hq * D, device=dev, dtype=bf)
-            ao = torch.empty_like(q)
-            qs, ql, kl = i32(list(range(m))), i32([1] * m), i32([context] * m)
-            ns = ops.decode_splits(m, Hkv, Hq // Hkv, context)
-            scratch = torch.empty(ops.decode_scratch_floats(Hq, D), device=dev)
-            counters = torch.zeros(ops.decode_counter_ints(m, Hkv, Hq // Hkv), dtype=torch.int32, device=dev)
-            calls = [(lambda k=k, v=v: ops.attention_decode(ao, q, qs, ql, kl, slots, table, k, v, m, Hq, Hkv, D, 0, D ** -0.5,
-                                                            ns, scratch, counters, status)) for k, v in sets]
-            us = _graph_us(calls)
-            add(f"decode: attention over {context} keys", m, us, m * context * Hkv * D * 2 * 2, 4.0 * m * Hq * D * context,
-                f"attn_decode ({ns} slices)")
-            del sets
-        else:
-            q = torch.randn(m, Hq * D, device=dev, dtype=bf)
-            ao = torch.empty_like(q)
-            kp.normal_(); vp.normal_()
-            args = (i32([0]), i32([m]), i32([m]), slots, table, kp, vp, 1, m, Hq, Hkv, D, 0, D ** -0.5, False, status)
-            tc5 = ops.prefer_tcgen05_attention(bf, D, page_size, m)
-            fn = ops.attention_prefill_tcgen05 if tc5 else ops.attention_prefill
-            us = _graph_us([lambda: fn(ao, q, *args)], reps=4)
-            add(f"prefill: causal attention, {m} tokens", m, us, m * (Hq + 2 * Hkv) * D * 2 + m * Hq * D * 2,
-                4.0 * Hq * D * m * (m + 1) / 2, "attn_prefill_tc5 (tcgen05)" if tc5 else "attn_prefill (mma.sync)")
+        if elementwise:
+            # bias + RoPE + cache write, and attention
+            pages = -(-context // page_size) * batch if phase == "decode" else -(-m // page_size)
+            kp = torch.zeros(pages, Hkv, page_size, D, device=dev, dtype=bf)
+            vp = torch.zeros_like(kp)
+            qkv = torch.randn(m, qkv_w, device=dev, dtype=bf)
+            bias = torch.randn(qkv_w, device=dev)
+            inv = (cfg.rope_theta ** (-torch.arange(0, D, 2, dtype=torch.float32) / D)).to(dev)
+            if phase == "decode":
+                blocks = -(-context // page_size)
+                table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(batch, blocks)
+                positions, seq_of = i32([context - 1] * m), i32(list(range(m)))
+                slots = i32(list(range(batch)))
+            else:
+                table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, pages)
+                positions = torch.arange(m, dtype=torch.int32, device=dev)
+                seq_of = torch.zeros(m, dtype=torch.int32, device=dev)
+                slots = i32([0])
+            if phase == "prefill":
+                us = _graph_us([lambda: ops.rope_kv_write(qkv, bias, positions, seq_of, slots, table, inv, kp, vp, m, Hq, Hkv, D,
+                                                          True, status)], reps=8)
+                add(f"{phase}: bias + RoPE + cache write", m, us, m * qkv_w * 2 * 2, 0.0, "rope_kv_write")
+                q = torch.randn(m, Hq * D, device=dev, dtype=bf)
+                ao = torch.empty_like(q)
+                kp.normal_(); vp.normal_()
+                args = (i32([0]), i32([m]), i32([m]), slots, table, kp, vp, 1, m, Hq, Hkv, D, 0, D ** -0.5, False, status)
+                tc5 = ops.prefer_tcgen05_attention(bf, D, page_size, m)
+                fn = ops.attention_prefill_tcgen05 if tc5 else ops.attention_prefill
+                us = _graph_us([lambda: fn(ao, q, *args)], reps=4)
+                add(f"prefill: causal attention, {m} tokens", m, us, m * (Hq + 2 * Hkv) * D * 2 + m * Hq * D * 2,
+                    4.0 * Hq * D * m * (m + 1) / 2, "attn_prefill_tc5 (tcgen05)" if tc5 else "attn_prefill (mma.sync)")
+            else:
+                # decode-only steps: one kernel adds the bias, rotates, writes the new key and value and attends
+                nset = _copies(kp.numel() * 2 * 2)
+                sets = [(torch.randn_like(kp), torch.randn_like(vp)) for _ in range(nset)]
+                ao = torch.empty(m, Hq * D, device=dev, dtype=bf)
+                qs, ql, kl = i32(list(range(m))), i32([1] * m), i32([context] * m)
+                ns = ops.decode_splits(m, Hkv, Hq // Hkv, context)
+                scratch = torch.empty(ops.decode_scratch_floats(Hq, D), device=dev)
+                counters = torch.zeros(ops.decode_counter_ints(m, Hkv, Hq // Hkv), dtype=torch.int32, device=dev)
+                nsl, _ = ops.small_m_split(qkv_w, H)
+                source = SplitSum(torch.randn(nsl, m, qkv_w, device=dev)) if nsl > 1 else qkv
+                calls = [(lambda k=k, v=v: ops.attention_decode_fused(ao, source, bias, inv, True, qs, ql, kl, slots, table, k, v, m,
+                                                                      Hq, Hkv, D, 0, D ** -0.5, ns, scratch, counters, status))
+                         for k, v in sets]
+                us = _graph_us(calls)
+                add(f"decode: bias + RoPE + cache write + attention over {context} keys", m, us,
+                    m * context * Hkv * D * 2 * 2 + nsl * m * qkv_w * 4, 4.0 * m * Hq * D * context,
+                    f"attn_decode fused ({ns} slices)")
+                del sets
+            del kp, vp
         product(f"{phase}: o_proj product", m, H, Hq * D)
-        product(f"{phase}: gate/up product" + (" + SiLU.mul" if m <= ops.SMALL_M_LIMIT else ""), m, 2 * I, H, fused_silu=True)
-        if m > ops.SMALL_M_LIMIT:
-            gu = torch.randn(m, 2 * I, device=dev, dtype=bf)
-            act = torch.empty(m, I, device=dev, dtype=bf)
-            us = _graph_us([lambda: ops.silu_mul(act, gu, m, True)], reps=4)
-            add(f"{phase}: SiLU.mul", m, us, m * I * 2 * 3, 0.0, "silu_mul")
-            del gu, act
+        product(f"{phase}: gate/up product", m, 2 * I, H, fused_silu=True)
         product(f"{phase}: down product", m, H, I)
-        del kp, vp
     product("decode: output matrix (logits, fp32)", batch, V, H, out_dtype=torch.float32)
-    logits = torch.randn(batch, V, device=dev)
-    ids = torch.zeros(batch, dtype=torch.int32, device=dev)
-    us = _graph_us([lambda: ops.sample(ids, logits, batch)], reps=8)
-    add("decode: greedy sampling", batch, us, batch * V * 4, 0.0, "sample")
+    if want("decode: greedy sampling"):
+        logits = torch.randn(batch, V, device=dev)
+        ids = torch.zeros(batch, dtype=torch.int32, device=dev)
+        us = _graph_us([lambda: ops.sample(ids, logits, batch)], reps=8)
+        add("decode: greedy sampling", batch, us, batch * V * 4, 0.0, "sample")
     if int(status) != 0:
         raise RuntimeError(f"a kernel reported status {int(status)} during the kernel table")
     return rows
 
 
 def format_table(rows: list[dict]) -> str:
-    head = f"{'operation':46s} {'rows':>5s} {'kernel':28s} {'us':>9s} {'MB':>9s} {'GFLOP':>9s} {'floor us':>9s} {'frac':>6s}"
+    head = f"{'operation':62s} {'rows':>5s} {'kernel':28s} {'us':>9s} {'MB':>9s} {'GFLOP':>9s} {'floor us':>9s} {'frac':>6s}"
     lines = [head, "-" * len(head)]
     for r in rows:
-        lines.append(f"{r['op']:46s} {r['rows']:5d} {r['kernel']:28s} {r['us']:9.2f} {r['mbytes']:9.2f} {r['gflop']:9.2f} "
+        lines.append(f"{r['op']:62s} {r['rows']:5d} {r['kernel']:28s} {r['us']:9.2f} {r['mbytes']:9.2f} {r['gflop']:9.2f} "
                      f"{r['floor_us']:9.2f} {r['frac']:6.3f}")
     return "\n".join(lines)
