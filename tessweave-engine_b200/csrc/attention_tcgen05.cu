@@ -61,7 +61,7 @@ constexpr int TRACE_SLOTS = 12, TRACE_TILES = 80, TRACE_ROLES = 10;     // a rol
 __device__ long long g_trace[TRACE_ROLES * TRACE_TILES * TRACE_SLOTS];
 #define TW_TRACE_AT(role, tile, slot)                                                              \
     do {                                                                                           \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) < TRACE_TILES)         \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (tile) < TRACE_TILES)         \
             g_trace[((role) * TRACE_TILES + (tile)) * TRACE_SLOTS + (slot)] = clock64();           \
     } while (0)
 #else
@@ -111,14 +111,18 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         int num_pages, int window, float scale_log2e, int skip_single, int* status) {
     extern __shared__ unsigned char smem_raw[];
     tw_grid_wait();
-    const int s = blockIdx.z, kvh = blockIdx.y;
+    // Blocks start in the order of blockIdx.x, and a block's work grows with the position of its rows: x counts
+    // (row tile, key/value head) with the head fastest and the last row tile first, so that the longest blocks of
+    // all heads start first and the short ones fill the gaps (with the head as blockIdx.y, the long blocks of
+    // the last heads started late: 78 us against 58 us for 2,048 tokens).
+    const int s = blockIdx.y, kvh = (int)blockIdx.x % Hkv, xt = (int)blockIdx.x / Hkv;
     const int q_len = seq_q_len[s];
     if (q_len <= 0 || (skip_single && q_len == 1)) return;
     const int G = Hq / Hkv;
     const int rows_total = q_len * G;
     const int mtiles = (rows_total + NQ * BM - 1) / (NQ * BM);
-    if ((int)blockIdx.x >= mtiles) return;
-    const int row0 = (mtiles - 1 - (int)blockIdx.x) * (NQ * BM);      // the rows with the most keys first
+    if (xt >= mtiles) return;
+    const int row0 = (mtiles - 1 - xt) * (NQ * BM);                  // the rows with the most keys first
     const int kv_len = seq_kv_len[s];
     const int pos0 = kv_len - q_len;                                 // position of the first token of this portion
     const int n0 = seq_q_start[s];
@@ -480,7 +484,7 @@ TW_EXPORT int tw_attn_prefill_tc5(void* out, int out_stride, const void* q, int 
     if (int e = get_map(k_cache, rows, D, box_rows, &mk)) return e;
     if (int e = get_map(v_cache, rows, D, box_rows, &mv)) return e;
     const int G = Hq / Hkv;
-    dim3 grid((max_q_len * G + NQ * BM - 1) / (NQ * BM), Hkv, n_seqs);
+    dim3 grid(((max_q_len * G + NQ * BM - 1) / (NQ * BM)) * Hkv, n_seqs);
     return tw_launch(attn_prefill_tc5_kernel, grid, dim3(THREADS), (size_t)SMEM, stream, 1, mk, mv, (bf16*)out, out_stride,
                      (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, table_stride,
                      Hq, Hkv, page_size, num_pages, window, scale * 1.4426950408889634f, skip_single, status);
