@@ -54,6 +54,8 @@ class ModelRunner:
         self.device = model.runtime.device
         self.max_tokens = int(max_step_tokens)
         self.max_seqs = int(max_step_seqs)
+        # batch sizes for which decode-only steps are captured: powers of two below the largest batch, and that batch
+        self.buckets = tuple(b for b in GRAPH_BUCKETS if b < self.max_seqs) + (self.max_seqs,)
         self.max_rows = max(int(max_logit_rows or max_step_tokens), self.max_seqs)
         self.workspace = Workspace(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -183,7 +185,7 @@ class ModelRunner:
         """Run the tokens of ``entries`` and return fp32 logits ``[wanted rows, vocab]`` on the
         device, in the order of the entries and of their ``want`` lists."""
         if self.use_graphs and entries and all(len(e.tokens) == 1 for e in entries):
-            bucket = next((b for b in GRAPH_BUCKETS if len(entries) <= b <= self.max_seqs), None)
+            bucket = next((b for b in self.buckets if len(entries) <= b), None)
             if bucket is not None:
                 return self._graph_step(entries, bucket)
         ctx, m = self._stage(entries)
@@ -200,10 +202,9 @@ class ModelRunner:
         logits = self.workspace.get("runner.logits", (self.max_rows, self.vocab), torch.float32)
         ctx = self._padding_context(self.max_tokens, self.max_rows)
         self.model.forward(ctx, self.cache.views(), self._d["logit_rows"], self.max_rows, logits)
-        for bucket in GRAPH_BUCKETS:
-            if bucket <= self.max_seqs:       # decode-only kernels may use buffers of their own
-                ctx = self._padding_context(bucket, bucket)
-                self.model.forward(ctx, self.cache.views(), self._d["logit_rows"], bucket, logits)
+        for bucket in self.buckets:           # decode-only kernels may use buffers of their own
+            ctx = self._padding_context(bucket, bucket)
+            self.model.forward(ctx, self.cache.views(), self._d["logit_rows"], bucket, logits)
         torch.cuda.current_stream().synchronize()
         self.status.zero_()
         self.workspace.frozen = True
@@ -233,9 +234,8 @@ class ModelRunner:
         if not self._graphs:
             # capture every bucket at the first decode step, so that a batch that shrinks or grows
             # later does not pay for a capture in the middle of generation
-            for b in GRAPH_BUCKETS:
-                if b <= self.max_seqs:
-                    self._capture(b)
+            for b in self.buckets:
+                self._capture(b)
         graph, logits = self._graphs.get(bucket) or self._capture(bucket)
         wanted = [i for i, e in enumerate(entries) if e.want]
         for e in entries:
