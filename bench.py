@@ -286,7 +286,7 @@ def workload_run(name: str, layers: int | None) -> dict:
         jobs = [(toks(rand(128, 2048)), rand(64, 512)) for _ in range(32)]
         pages = sum(-(-(len(p) + m) // PAGE_SIZE) for p, m in jobs) + 8
         engine = tw.Engine(model, tw.EngineConfig(block_size=PAGE_SIZE, kv_blocks=pages, max_context=2560, max_active=32,
-                                                  max_queue=32, prefill_chunk=512, max_step_tokens=512 + 32))
+                                                  max_queue=32, prefill_chunk=512, max_step_tokens=512))
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         reqs = [engine.submit(p, max_tokens=m, ignore_eos=True) for p, m in jobs]

@@ -497,10 +497,17 @@ def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kp
 # ---------------------------------------------------------------------------
 # matrix products on tcgen05 tensor cores fed by TMA
 # ---------------------------------------------------------------------------
-TCGEN05_MIN_M, TCGEN05_MAX_M = 9, 32     # rows for which the swap-AB tcgen05 kernel is the product path
+TCGEN05_MIN_M, TCGEN05_MAX_M = 9, 32     # rows the swap-AB tcgen05 kernel is meant for (see tcgen05_supported)
 
 
 def tcgen05_supported(x: torch.Tensor, w: torch.Tensor, m: int) -> bool:
+    """Whether a product with ``m`` rows goes to the swap-AB tcgen05 kernel.  Off unless TESSWEAVE_SWAP_AB=1:
+    measured on B200 the library is faster for 9..32 rows (a decode step at batch 16 / 32 of the 7B sizes
+    4.16 / 4.86 ms against 4.21 / 5.02; at the 14B sizes 15 / 13 / 47 / 27 us against 23 / 19 / 58 / 42 for
+    the four products of a layer), so these steps take the library's products."""
+    import os
+    if os.environ.get("TESSWEAVE_SWAP_AB", "0") != "1":
+        return False
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and TCGEN05_MIN_M <= m <= TCGEN05_MAX_M
             and w.shape[1] % 8 == 0 and w.is_contiguous() and x.is_contiguous()
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)

@@ -104,7 +104,7 @@ def kernel_table(cfg, batch: int, context: int, prefill_tokens: int, hbm_gbs: fl
         else:
             calls = [(lambda w=w: linear(ctx, "p", x, w, out_dtype=out_dtype, allow_split=True)) for w in ws]
             kernel = ("gemm_smallm" if m <= ops.SMALL_M_LIMIT else
-                      "gemm_tcgen05 (swap-AB)" if ops.TCGEN05_MIN_M <= m <= ops.TCGEN05_MAX_M else "library (cuBLAS)")
+                      "gemm_tcgen05 (swap-AB)" if ops.tcgen05_supported(x, ws[0], m) else "library (cuBLAS)")
         us = _graph_us(calls)
         out_bytes = m * out_cols * (4 if out_dtype == torch.float32 else 2)
         add(name, m, us, n * k * 2 + m * k * 2 + out_bytes, 2.0 * m * n * k, kernel)

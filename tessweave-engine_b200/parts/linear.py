@@ -44,10 +44,10 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
            allow_split: bool = False, small_consumer: bool = False):
     """``x @ w.T`` into the workspace buffer ``name``.
 
-    Steps with few rows (decode) in bfloat16 go through hand-written kernels: up to 8 rows
-    the weight-streaming kernel of csrc/gemm_smallm.cu, 9 to 32 rows the tcgen05/TMA kernel of
-    csrc/gemm_tcgen05.cu with the weights as the 128-row operand.  When the matrix has too few
-    rows to fill the GPU these kernels split k and, if the caller can take it
+    Steps with up to 8 rows (decode) in bfloat16 go through the weight-streaming kernel of
+    csrc/gemm_smallm.cu.  (The tcgen05/TMA kernel of csrc/gemm_tcgen05.cu with the weights as the
+    128-row operand takes 9 to 32 rows when TESSWEAVE_SWAP_AB=1; the library measured faster there.)
+    When the matrix has too few rows to fill the GPU these kernels split k and, if the caller can take it
     (``allow_split``), the fp32 slices are returned as a ``SplitSum`` for the consuming kernel
     to add.  Everything else is a library product.  ``small_consumer`` says that the kernel that follows is
     a small one (a norm, a sampler): the weight-streaming kernel then lets it become resident early.
