@@ -232,7 +232,7 @@ __device__ __forceinline__ void tw_store4(__nv_bfloat16* p, float4 v) {
 
 // Many rows (prompt portions): four values per thread and access, one pass, values kept in registers.
 // Dense delta only; hidden a multiple of 4 and at most 4 * 256 * TW_NORM_V4 wide.
-#define TW_NORM_V4 4
+#define TW_NORM_V4 8          // float4 per thread: rows up to 8,192 wide
 template <typename T>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_vec4_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,

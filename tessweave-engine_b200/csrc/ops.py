@@ -293,7 +293,7 @@ def decode_splits(n_seqs: int, n_kv_heads: int, group: int, max_kv_len: int) -> 
     tiles = max(1, -(-max_kv_len // 64))
     groups = max(1, n_seqs * n_kv_heads * head_tiles)
     # the kernel fits four blocks on an SM; aim at a little under one full wave of blocks
-    target = max(1, (7 * _SM_COUNT // 2) // groups)
+    target = max(1, (7 * _SM_COUNT // 2 + groups // 2) // groups)        # rounded: 1.9 blocks' worth of room is two slices
     nsplit = max(1, min(tiles, target, 128, DECODE_SCRATCH_UNITS // max(1, n_seqs)))
     if 14 < nsplit <= 16 and groups > 8 and max_kv_len < 8192:
         nsplit = 14
