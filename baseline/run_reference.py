@@ -1,5 +1,5 @@
 """The reference arm of bench.py: the unmodified reference package (installed under
-``baseline/_ref`` with pip) driven through its own public API --
+``baseline/_ref`` with pip, without its dependencies) driven through its own public API --
 ``flow_engine.model.CausalLM``, ``flow_engine.engine.Engine.submit/step`` -- on its stock code
 path (its default ``attention="sdpa"``).  Nothing of this repository's engine, kernels or models
 is on that path.  The reference has no random-weights mode; its model class is constructed on
