@@ -51,10 +51,16 @@ struct Frag {          // 16 consecutive values of k of one row
     uint4 lo, hi;
 };
 
-template <int NT>
+// KS = 1: the block's four warps take four 16-row tiles.  KS = 2: two tiles, each by two warps that
+// share its values of k and add their sums through shared memory: twice the warps for a matrix with few
+// row tiles whose k cannot be split over blocks (the SiLU.mul output needs whole sums): 27,648 x 5,120
+// at 8 rows 52 -> 45 us.
+template <int NT, int KS>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M, int N, int K, int kper,
                    void* __restrict__ out, int out_mode, int out_stride) {
+    constexpr int TILES = WARPS / KS;                  // 16-row tiles of a block
+    __shared__ float s_part[KS > 1 ? TILES * 32 * NT * 4 : 1];
     tw_grid_wait();
     // With OUT_EARLY_DEPENDENTS the kernel launched after this one may become resident right away (it waits
     // for this kernel's results itself).  That pays when the next kernel is small, like the residual add +
@@ -64,12 +70,16 @@ gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M
     out_mode &= ~OUT_EARLY_DEPENDENTS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
-    const int r0 = blockIdx.x * ROWS_PER_BLOCK + warp * 16;
-    if (r0 >= N) return;
-    const int kbeg = blockIdx.y * kper;
-    const int kend = min(K, kbeg + kper);
+    const int tile = warp % TILES, khalf = warp / TILES;
+    const int r0 = blockIdx.x * (TILES * 16) + tile * 16;
+    if (KS == 1 && r0 >= N) return;
+    const int kbeg0 = blockIdx.y * kper, kend0 = min(K, kbeg0 + kper);
+    // with KS > 1: this warp's share of the block's values of k, in whole steps
+    const int span = KS > 1 ? ((kend0 - kbeg0 + KS - 1) / KS + CHUNK - 1) / CHUNK * CHUNK : 0;
+    const int kbeg = KS > 1 ? kbeg0 + khalf * span : kbeg0;
+    const int kend = KS > 1 ? min(kend0, kbeg + span) : kend0;
     const int ra = r0 + g, rb = r0 + g + 8;
-    const bool va = ra < N, vb = rb < N;
+    const bool va = ra < N && (KS == 1 || kbeg < kend), vb = rb < N && (KS == 1 || kbeg < kend);
     const bf16* wa = w + (size_t)(va ? ra : 0) * K;
     const bf16* wb = w + (size_t)(vb ? rb : 0) * K;
     const bf16* xr[NT];
@@ -117,6 +127,19 @@ gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M
         a_nxt = a_far; b_nxt = b_far;
     }
     tw_grid_launch_dependents_late();     // the stream of weights is over: the next kernel may be scheduled
+    if (KS > 1) {
+        // the warps of the later values of k hand their sums to the first warp of their tile
+        float* mine = s_part + (tile * 32 + lane) * NT * 4;
+        if (khalf > 0) {
+#pragma unroll
+            for (int t = 0; t < NT; ++t) { mine[4 * t] = acc[t][0]; mine[4 * t + 1] = acc[t][1]; mine[4 * t + 2] = acc[t][2]; mine[4 * t + 3] = acc[t][3]; }
+        }
+        __syncthreads();
+        if (khalf > 0) return;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) { acc[t][0] += mine[4 * t]; acc[t][1] += mine[4 * t + 1]; acc[t][2] += mine[4 * t + 2]; acc[t][3] += mine[4 * t + 3]; }
+    }
+    const bool wa_ok = ra < N, wb_ok = rb < N;        // rows of the matrix (va / vb also say whether this warp had values of k)
     // acc[t][0..1]: weight row ra, tokens t*8 + 2c, +1;  acc[t][2..3]: weight row rb
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
@@ -127,20 +150,20 @@ gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M
             if (out_mode == OUT_SILU_MUL) {
                 // weight rows come in groups of 16: eight gate rows, then the eight up rows that belong to
                 // them, so row ra is a gate and row rb its up: out[tok, r0 / 2 + g] = silu(gate) * up
-                if (vb) {
+                if (wb_ok) {
                     const float gt = acc[t][e], up = acc[t][2 + e];
                     reinterpret_cast<bf16*>(out)[(size_t)tok * out_stride + (r0 >> 1) + g] =
                         __float2bfloat16_rn(gt / (1.0f + expf(-gt)) * up);
                 }
             } else if (out_mode == OUT_BF16) {
                 bf16* o = reinterpret_cast<bf16*>(out) + (size_t)tok * out_stride;
-                if (va) o[ra] = __float2bfloat16_rn(acc[t][e]);
-                if (vb) o[rb] = __float2bfloat16_rn(acc[t][2 + e]);
+                if (wa_ok) o[ra] = __float2bfloat16_rn(acc[t][e]);
+                if (wb_ok) o[rb] = __float2bfloat16_rn(acc[t][2 + e]);
             } else {
                 float* o = reinterpret_cast<float*>(out) +
                            (out_mode == OUT_PARTIAL ? ((size_t)blockIdx.y * M + tok) * out_stride : (size_t)tok * out_stride);
-                if (va) o[ra] = acc[t][e];
-                if (vb) o[rb] = acc[t][2 + e];
+                if (wa_ok) o[ra] = acc[t][e];
+                if (wb_ok) o[rb] = acc[t][2 + e];
             }
         }
     }
@@ -173,14 +196,25 @@ TW_EXPORT int tw_gemm_smallm(const void* w, const void* x, int M, int N, int K, 
     dim3 grid((N + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK, ksplit);
     const bf16* wp = (const bf16*)w;
     const bf16* xp = (const bf16*)x;
-    if (M <= 8)
-        tw_launch(gemm_smallm_kernel<1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
+    // few blocks for the GPU (under 3.2 per SM, six fit) and a long k: two warps per row tile
+    const bool pair_warps = M <= 8 && (long)grid.x * grid.y * 10 <= (long)sm_count * 32 && kper >= 2048 && K >= 2048;
+    if (pair_warps) {
+        grid.x = (N + (WARPS / 2) * 16 - 1) / ((WARPS / 2) * 16);
+        tw_launch(gemm_smallm_kernel<1, 2>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
+    } else if (M <= 8)
+        tw_launch(gemm_smallm_kernel<1, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
     else if (M <= 16)
-        tw_launch(gemm_smallm_kernel<2>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<2, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
     else if (M <= 32)
-        tw_launch(gemm_smallm_kernel<4>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<4, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
     else
-        tw_launch(gemm_smallm_kernel<8>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<8, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
     return TW_LAUNCH_CHECK();
 }
 

@@ -514,12 +514,13 @@ def test_gemm_small_m(m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 5, 8])
-def test_gemm_small_m_fused_silu(m):
-    """gate/up rows in groups of eight: the kernel writes silu(gate) * up directly."""
+@pytest.mark.parametrize("inter,k", [(200, 96), (328, 4160)])
+def test_gemm_small_m_fused_silu(m, inter, k):
+    """gate/up rows in groups of eight: the kernel writes silu(gate) * up directly.  The second shape (few
+    row tiles, long k) takes the variant in which two warps share a row tile's values of k."""
     torch.manual_seed(m)
-    inter, k = 200, 96
     x = dev(torch.randn(m, k), torch.bfloat16)
-    wg, wu = torch.randn(inter, k) * 0.2, torch.randn(inter, k) * 0.2
+    wg, wu = torch.randn(inter, k) * 0.2 * (96 / k) ** 0.5, torch.randn(inter, k) * 0.2 * (96 / k) ** 0.5
     packed = torch.stack((wg.reshape(inter // 8, 8, k), wu.reshape(inter // 8, 8, k)), 1).reshape(2 * inter, k)
     w = dev(packed, torch.bfloat16)
     out = torch.full((m, inter), float("nan"), device="cuda", dtype=torch.bfloat16)
