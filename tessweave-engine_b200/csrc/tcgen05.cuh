@@ -50,8 +50,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     return true;
 }
 
-// The same without ever suspending the thread (mbarrier.test_wait): for the one thread whose
-// wake-up latency is on the critical path.
+// One look at a barrier without ever suspending the thread (mbarrier.test_wait): for a thread that has
+// other work to issue if the phase has not completed yet.
 __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -60,19 +60,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, int* status) {
-    if (mbar_test_wait(bar, parity)) return true;
-    const long long start = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int k = 0; k < 64; ++k)
-            if (mbar_test_wait(bar, parity)) return true;
-        if (clock64() - start > WAIT_CYCLES) {
-            atomicOr(status, TW_ERR_WAIT);
-            return false;
-        }
-    }
 }
 
 // Generic-proxy writes to shared memory (st.shared) become visible to the async proxy (the
