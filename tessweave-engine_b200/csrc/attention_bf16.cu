@@ -143,6 +143,8 @@ struct FusedQkv {
     const float* inv_freq;       // [D / 2]; null: no rotation
     bf16* k_cache;               // where the new key and value go; null: the cache is not written
     bf16* v_cache;
+    const void* next_weights;    // what the kernel after this one streams (or null): prefetched into L2 after the keys
+    long long next_bytes;
 };
 
 // fp32 values of NC columns of one row of the q/k/v product, bias included.  The slices of a split product are
@@ -179,6 +181,27 @@ __device__ __forceinline__ void product_cols(const FusedQkv& fq, size_t row, int
     }
 }
 
+// -DTW_TRACE: every block of the decode kernel records clock64() at its phase boundaries and the global
+// timer (ns) at its start and end, for a timeline of one launch (tw_attn_decode_trace_ptr gives the
+// buffer: [block][slot]).  Off in the product.
+#ifdef TW_TRACE
+constexpr int DTRACE_BLOCKS = 2048, DTRACE_SLOTS = 12;
+__device__ long long g_dec_trace[DTRACE_BLOCKS * DTRACE_SLOTS];
+__device__ __forceinline__ long long global_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TW_DTRACE(slot)                                                                                 \
+    do {                                                                                                \
+        const int b_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                  \
+        if (threadIdx.x == 0 && b_ < DTRACE_BLOCKS)                                                     \
+            g_dec_trace[b_ * DTRACE_SLOTS + (slot)] = ((slot) >= 10) ? global_ns() : clock64();         \
+    } while (0)
+#else
+#define TW_DTRACE(slot) do {} while (0)
+#endif
+
 template <bool CLUSTER, bool FUSED>
 __global__ void __launch_bounds__(DEC_WARPS * 32, (D <= 128 ? 4 : 2))
 attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
@@ -196,6 +219,9 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
     // kernel before this one: they are read before the wait for that kernel, while it is still finishing.
     const int s = blockIdx.z, kvh = blockIdx.y;
     const int split = blockIdx.x % nsplit, ht = blockIdx.x / nsplit;
+    TW_TIMELINE_SCOPE(TW_K_ATTN_DECODE);
+    TW_DTRACE(10);
+    TW_DTRACE(0);
     if (seq_q_len[s] != 1) {
         tw_grid_wait();             // a block never finishes before the kernel before this one has
         return;
@@ -226,7 +252,10 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
             page_cache[i] = first_blk + i < table_stride ? table[first_blk + i] : -1;
     }
     __syncthreads();
+    TW_DTRACE(1);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
+    TW_DTRACE(2);
 
     // ---- with FUSED: bias, rotation by position and the cache write of the step's new token, done here instead
     // of in a kernel of their own (same arithmetic and the same order of the slice sums as that kernel).
@@ -322,15 +351,18 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
     };
 
     KFrag ka_next, kb_next;
-    stage_tile(0, 0);
-    load_k(0, 0, ka_next, kb_next);
-    stage_tile(1, 1);
+    TW_DTRACE(3);
+    // With FUSED: this block's query heads (computed once per block, rotated, into shared memory, from where every
+    // warp takes its fragments).  Their loads go out first: they come from L2, and issued behind the first keys
+    // and values they would stand in the same queue as those.  Up to four slices are kept apart in registers
+    // while the keys' copies are issued; more are added afterwards, with the keys on their way.
+    constexpr int PQ = (DEC_HEADS * half + DEC_WARPS * 32 - 1) / (DEC_WARPS * 32);     // pairs per thread
+    int cols[FUSED ? 2 * PQ : 1];
+    float x[FUSED ? 2 * PQ : 1];
+    float raw[FUSED ? 2 * PQ : 1][4];
+    float freq[FUSED ? PQ : 1];
+    const bool early_q = FUSED && fq.partial && fq.nslices <= 4;
     if constexpr (FUSED) {
-        // While the first keys and values are on their way: this block's query heads, rotated, into shared memory
-        // (computed once for the block), from where every warp takes its fragments.
-        constexpr int PQ = (DEC_HEADS * half + DEC_WARPS * 32 - 1) / (DEC_WARPS * 32);     // pairs per thread
-        int cols[2 * PQ];
-        float x[2 * PQ];
 #pragma unroll
         for (int j = 0; j < PQ; ++j) {
             const int p = threadIdx.x + j * DEC_WARPS * 32;
@@ -338,8 +370,35 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
             const bool live = p < DEC_HEADS * half && head < nheads;
             cols[2 * j] = live ? (kvh * G + h0 + head) * D + i : 0;
             cols[2 * j + 1] = cols[2 * j] + half;
+            freq[j] = (fq.inv_freq && live) ? fq.inv_freq[i] : 0.f;
         }
-        product_cols<2 * PQ>(fq, (size_t)n, width, cols, x);
+        if (early_q) {
+            const float* prow = fq.partial + (size_t)n * width;
+#pragma unroll
+            for (int j = 0; j < 2 * PQ; ++j) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) raw[j][u] = u < fq.nslices ? prow[(size_t)u * fq.slice_stride + cols[j]] : 0.f;
+                x[j] = fq.bias ? fq.bias[cols[j]] : 0.f;
+            }
+        }
+    }
+    stage_tile(0, 0);
+    load_k(0, 0, ka_next, kb_next);
+    stage_tile(1, 1);
+    TW_DTRACE(4);
+    if constexpr (FUSED) {
+        if (early_q) {
+            // the sums product_cols makes: four slices pairwise, fewer one after the other
+#pragma unroll
+            for (int j = 0; j < 2 * PQ; ++j) {
+                const float sum = fq.nslices == 4 ? (raw[j][0] + raw[j][1]) + (raw[j][2] + raw[j][3])
+                                                  : ((raw[j][0] + raw[j][1]) + raw[j][2]);
+                x[j] = fq.bias ? sum + x[j] : sum;
+            }
+        } else {
+            product_cols<2 * PQ>(fq, (size_t)n, width, cols, x);
+        }
+        TW_DTRACE(5);
 #pragma unroll
         for (int j = 0; j < PQ; ++j) {
             const int p = threadIdx.x + j * DEC_WARPS * 32;
@@ -348,7 +407,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
                 float y1 = 0.f, y2 = 0.f;
                 if (head < nheads) {
                     float sn = 0.f, cs = 1.f;
-                    if (fq.inv_freq) sincosf((float)pos * fq.inv_freq[i], &sn, &cs);
+                    if (fq.inv_freq) sincosf((float)pos * freq[j], &sn, &cs);
                     y1 = x[2 * j] * cs - x[2 * j + 1] * sn;
                     y2 = x[2 * j + 1] * cs + x[2 * j] * sn;
                 }
@@ -362,6 +421,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         for (int jb = 0; jb < DB32; ++jb) qf.blk[jb] = *reinterpret_cast<const uint4*>(qrow + 32 * jb + 8 * c);
         qf.tail = DTAIL16 ? *reinterpret_cast<const uint2*>(qrow + 32 * DB32 + 4 * c) : make_uint2(0u, 0u);
     }
+    TW_DTRACE(6);
     for (int t = 0; t < ntiles; ++t) {
         const int st = t % DEC_STAGES;
         const KFrag ka = ka_next, kb_ = kb_next;
@@ -421,6 +481,11 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         __syncwarp();
     }
     cp_async_wait<0>();
+    // the keys and values are in: while the slices merge, the memory system may fetch the next kernel's weights
+    if constexpr (FUSED) {
+        if (threadIdx.x == 0) tw_prefetch_l2_share(fq.next_weights, fq.next_bytes);
+    }
+    TW_DTRACE(7);
     // sums over the keys of the other threads with the same heads
 #pragma unroll
     for (int o = 4; o < 32; o <<= 1) {
@@ -482,6 +547,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         // i.  Every block merges its share of the outputs, reading all slices in slice order:
         //   out = sum_i o_i 2^(m_i - M) / sum_i l_i 2^(m_i - M)
         cg::cluster_group cluster = cg::this_cluster();
+        TW_DTRACE(8);
         cluster.sync();
         for (int idx = split * (DEC_WARPS * 32) + threadIdx.x; idx < nheads * D; idx += nsplit * (DEC_WARPS * 32)) {
             const int row = idx / D, d = idx - row * D;
@@ -498,6 +564,8 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
             out[(size_t)n * out_stride + (size_t)(kvh * G + h0 + row) * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
         }
         cluster.sync();          // nobody leaves while a neighbour may still read its shared memory
+        TW_DTRACE(9);
+        TW_DTRACE(11);
         return;
     }
 
@@ -591,7 +659,9 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
                     const bf16* __restrict__ v_cache, int Hq, int Hkv, int page_size, int num_pages, int window,
                     float scale_log2e, int skip_single, int* status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    TW_TIMELINE_SCOPE(TW_K_ATTN_PREFILL);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     tw_grid_launch_dependents();
     const int s = blockIdx.z, kvh = blockIdx.y;
     const int q_len = seq_q_len[s];
@@ -853,6 +923,13 @@ bool decode_cluster_ok(int size) {
 
 TW_EXPORT int tw_attn_head_dim() { return D; }
 
+#ifdef TW_TRACE
+TW_EXPORT int tw_attn_decode_trace_ptr(void** ptr, int* blocks, int* slots) {
+    *blocks = DTRACE_BLOCKS; *slots = DTRACE_SLOTS;
+    return (int)cudaGetSymbolAddress(ptr, g_dec_trace);
+}
+#endif
+
 // Most slices that merge through a cluster; more go through scratch memory.
 TW_EXPORT int tw_attn_decode_cluster_slices() { return DEC_MAX_CLUSTER; }
 
@@ -900,8 +977,9 @@ TW_EXPORT int tw_attn_decode_fused(void* out, int out_stride, const float* parti
                                    const int* seq_slot, const int* block_table, int table_stride, void* k_cache,
                                    void* v_cache, int n_seqs, int Hq, int Hkv, int page_size, int num_pages, int window,
                                    float scale, int nsplit, int flags, float* scratch, int* counters, int* status,
-                                   cudaStream_t stream) {
+                                   const void* next_weights, long long next_bytes, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
+    if ((uintptr_t)next_weights & 15) return (int)cudaErrorMisalignedAddress;
     if (Hkv <= 0 || Hq % Hkv || nsplit < 1 || (nsplit > 1 && (!scratch || !counters)) || (!partial && !dense) ||
         (partial && nslices < 1))
         return (int)cudaErrorInvalidValue;
@@ -915,6 +993,7 @@ TW_EXPORT int tw_attn_decode_fused(void* out, int out_stride, const float* parti
     fq.dense = (const bf16*)dense; fq.dense_stride = dense_stride; fq.bias = bias; fq.inv_freq = inv_freq;
     fq.k_cache = write_cache ? (bf16*)k_cache : nullptr;
     fq.v_cache = write_cache ? (bf16*)v_cache : nullptr;
+    fq.next_weights = next_weights; fq.next_bytes = next_weights ? next_bytes : 0;
     dim3 grid(nsplit * htiles, Hkv, n_seqs);
     if (nsplit > 1 && !(flags & 1) && decode_cluster_ok(nsplit))
         return tw_launch(attn_decode_kernel<true, true>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, nsplit,

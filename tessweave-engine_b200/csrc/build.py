@@ -118,14 +118,37 @@ def compile_library(name: str, defines: dict[str, int | str] | None = None, verb
     return out
 
 
+def timeline_enabled() -> bool:
+    """``TESSWEAVE_TIMELINE=1``: every library is compiled with the device-side timeline (see common.cuh)."""
+    return os.environ.get("TESSWEAVE_TIMELINE") == "1"
+
+
+_timeline_buffer: list[int] = [0]     # device address handed to every library loaded with the timeline
+
+
+def set_timeline_buffer(address: int) -> None:
+    """Hand the timeline buffer (device address; 0 = none) to the loaded libraries and to those loaded later."""
+    with _lock:
+        _timeline_buffer[0] = address
+        for lib in _loaded.values():
+            if hasattr(lib, "tw_timeline_set"):
+                code = lib.tw_timeline_set(ctypes.c_void_p(address))
+                if code != 0:
+                    raise BuildError(f"tw_timeline_set failed with CUDA error {code}")
+
+
 def load_library(name: str, defines: dict[str, int | str] | None = None) -> ctypes.CDLL:
     """The loaded library of ``<name>.cu``; compiled at the first call if need be."""
+    if timeline_enabled():
+        defines = dict(defines or {}, TW_TIMELINE=1)
     key = name + repr(sorted((defines or {}).items()))
     with _lock:
         lib = _loaded.get(key)
         if lib is None:
             lib = ctypes.CDLL(str(compile_library(name, defines)))
             _loaded[key] = lib
+            if _timeline_buffer[0] and hasattr(lib, "tw_timeline_set"):
+                lib.tw_timeline_set(ctypes.c_void_p(_timeline_buffer[0]))
         return lib
 
 

@@ -78,6 +78,51 @@ __device__ __forceinline__ float tw_block_max(float v, float* scratch) {
 #define TW_LAUNCH_CHECK() (int)cudaGetLastError()
 
 // ---------------------------------------------------------------------------------------
+// Device-side timeline (-DTW_TIMELINE, off in the product): every block of an instrumented kernel appends
+// {kernel id | blocks of its grid << 16, its linear index, start, time after its wait for the kernel before,
+// end} to a buffer the host hands over with tw_timeline_set (global timer, ns).  Sorted by time this shows
+// how the kernels of a step overlap, where SMs stand idle between them and how long the tails are.
+// ---------------------------------------------------------------------------------------
+enum : int {
+    TW_K_EMBED = 1, TW_K_NORM = 2, TW_K_NORM_CLUSTER = 3, TW_K_ROPE = 4, TW_K_GEMM_SMALLM = 5, TW_K_ATTN_DECODE = 6,
+    TW_K_ATTN_PREFILL = 7, TW_K_SAMPLE = 8, TW_K_SILU_MUL = 9, TW_K_REDUCE_PARTIAL = 10, TW_K_OTHER = 11,
+};
+#ifdef TW_TIMELINE
+__device__ unsigned long long* g_tw_timeline = nullptr;      // [0] entries so far, [1] capacity, then 5 words per entry
+__device__ __forceinline__ unsigned long long tw_global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+struct TwTimelineScope {
+    unsigned long long t0, t1;
+    int id;
+    __device__ __forceinline__ explicit TwTimelineScope(int id_) : t0(tw_global_ns()), t1(0), id(id_) {}
+    __device__ __forceinline__ void mark() { t1 = tw_global_ns(); }
+    __device__ __forceinline__ ~TwTimelineScope() {
+        if (threadIdx.x == 0 && threadIdx.y == 0 && g_tw_timeline) {
+            const unsigned long long i = atomicAdd(g_tw_timeline, 1ull);
+            if (i < g_tw_timeline[1]) {
+                unsigned long long* e = g_tw_timeline + 2 + 5 * i;
+                const unsigned long long nblocks = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+                e[0] = (unsigned long long)id | (nblocks << 16);
+                e[1] = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+                e[2] = t0; e[3] = t1; e[4] = tw_global_ns();
+            }
+        }
+    }
+};
+#define TW_TIMELINE_SCOPE(id) TwTimelineScope tw_timeline_scope_(id)
+#define TW_TIMELINE_MARK() tw_timeline_scope_.mark()
+TW_EXPORT int tw_timeline_set(void* buffer) {
+    return (int)cudaMemcpyToSymbol(g_tw_timeline, &buffer, sizeof(buffer));
+}
+#else
+#define TW_TIMELINE_SCOPE(id) ((void)0)
+#define TW_TIMELINE_MARK() ((void)0)
+#endif
+
+// ---------------------------------------------------------------------------------------
 // Programmatic dependent launch.  Every kernel of this engine starts with tw_grid_wait():
 // nothing it reads that an earlier kernel wrote, and nothing it writes, is touched before.
 // Kernels are launched with the programmatic-serialization attribute, so inside a CUDA graph
@@ -98,6 +143,23 @@ __device__ __forceinline__ void tw_grid_launch_dependents_late() { tw_grid_launc
 // The exception, measured to pay: kernels whose successor is small (or whose own blocks are few) let it
 // become resident at once.  Used by the clustered norm and, on request, by the small-M product.
 __device__ __forceinline__ void tw_launch_dependents_now() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// A hint to bring this block's share of [ptr, ptr + bytes) into L2: what the next kernel will stream (its
+// weights), asked for while this kernel's last blocks finish and the memory system has little to do.  One
+// thread issues bulk prefetches of up to 16 KB; `ptr` is 16-byte aligned.  Nothing waits for them.
+__device__ __forceinline__ void tw_prefetch_l2_share(const void* ptr, long long bytes) {
+    if (!ptr || bytes <= 0) return;
+    const long long nblk = (long long)gridDim.x * gridDim.y * gridDim.z;
+    const long long b = blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z);
+    const long long share = (((bytes + nblk - 1) / nblk) + 127) & ~127ll;
+    const long long beg = b * share;
+    long long end = beg + share < bytes ? beg + share : bytes;
+    end &= ~15ll;
+    for (long long o = beg; o < end; o += 16384) {
+        const unsigned size = (unsigned)(end - o < 16384 ? end - o : 16384);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"((const char*)ptr + o), "r"(size) : "memory");
+    }
+}
 
 #ifndef __CUDA_ARCH__
 #include <stdlib.h>

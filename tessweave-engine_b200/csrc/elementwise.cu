@@ -19,7 +19,9 @@ template <typename T>
 __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ table,
                              const int* __restrict__ ids, const int* __restrict__ device_tokens, int n_device_tokens,
                              int hidden, int vocab, int* status) {
+    TW_TIMELINE_SCOPE(TW_K_EMBED);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     tw_grid_launch_dependents();
     const int n = blockIdx.x;
     int id = ids[n];
@@ -69,7 +71,9 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __re
                    const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
+    TW_TIMELINE_SCOPE(TW_K_NORM);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     tw_grid_launch_dependents();
     const int src = rows ? rows[r] : r;
     float* x = resid + (size_t)src * hidden;
@@ -143,15 +147,25 @@ add_rmsnorm_cluster_kernel(T* __restrict__ out, float* __restrict__ resid, const
                            const float* __restrict__ partial, int nsplit, size_t split_stride,
                            const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
     __shared__ float scratch[33];
-    __shared__ float my_ss;
-    tw_grid_wait();
-    tw_launch_dependents_now();     // 64 small blocks: the product that follows may settle on the SMs meanwhile (1 % of a decode step)
+    __shared__ float all_ss[TW_NORM_CLUSTER];      // every block's sum of squares, written here by the blocks themselves
+    TW_TIMELINE_SCOPE(TW_K_NORM_CLUSTER);
+    // What no kernel of the step writes (the row indices, the norm's weights) is read before the wait for the
+    // kernel before this one: this kernel is a chain of round trips, and these two need not be in it.
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int r = blockIdx.x / TW_NORM_CLUSTER;
     const int src = rows ? rows[r] : r;
     const int chunk = (hidden + TW_NORM_CLUSTER - 1) / TW_NORM_CLUSTER;
     const int c0 = rank * chunk, c1 = min(hidden, c0 + chunk);
+    float wv[TW_NORM_CMAXV];
+#pragma unroll
+    for (int j = 0; j < TW_NORM_CMAXV; ++j) {
+        const int i = c0 + threadIdx.x + j * TW_NORM_CTHREADS;
+        wv[j] = i < c1 ? weight[i] : 0.f;
+    }
+    tw_grid_wait();
+    TW_TIMELINE_MARK();
+    tw_launch_dependents_now();     // 64 small blocks: the product that follows may settle on the SMs meanwhile (1 % of a decode step)
     float* x = resid + (size_t)src * hidden;
     const T* d = delta ? delta + (size_t)src * hidden : nullptr;
     const float* ps = partial ? partial + (size_t)src * hidden : nullptr;
@@ -200,18 +214,19 @@ add_rmsnorm_cluster_kernel(T* __restrict__ out, float* __restrict__ resid, const
         }
     }
     ss = tw_block_sum(ss, scratch);
-    if (threadIdx.x == 0) my_ss = ss;
+    // every block hands its sum to all blocks of the cluster (one remote store each), so that after one
+    // cluster barrier each block finds the eight sums in its own shared memory and nobody reads a neighbour's
+    if (threadIdx.x < TW_NORM_CLUSTER) *cluster.map_shared_rank(&all_ss[rank], threadIdx.x) = ss;
     cluster.sync();
     float total = 0.f;
 #pragma unroll
-    for (int k = 0; k < TW_NORM_CLUSTER; ++k) total += *cluster.map_shared_rank(&my_ss, k);
-    cluster.sync();      // nobody leaves while a neighbour may still read its shared memory
+    for (int k = 0; k < TW_NORM_CLUSTER; ++k) total += all_ss[k];       // in rank order
     const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
     T* o = out + (size_t)r * hidden;
 #pragma unroll
     for (int j = 0; j < TW_NORM_CMAXV; ++j) {
         const int i = c0 + threadIdx.x + j * TW_NORM_CTHREADS;
-        if (i < c1) o[i] = tw_from_float<T>((v[j] * inv) * weight[i]);
+        if (i < c1) o[i] = tw_from_float<T>((v[j] * inv) * wv[j]);
     }
 }
 
@@ -238,7 +253,9 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_vec4_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,
                         const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
     __shared__ float scratch[33];
+    TW_TIMELINE_SCOPE(TW_K_NORM);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     tw_grid_launch_dependents();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -333,7 +350,9 @@ rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const float* __restric
                      const int* __restrict__ block_table, int table_stride, const float* __restrict__ inv_freq,
                      T* __restrict__ k_cache, T* __restrict__ v_cache, int Hq, int Hkv, int D, int page_size,
                      int num_pages, int write_cache, int* status) {
+    TW_TIMELINE_SCOPE(TW_K_ROPE);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     tw_grid_launch_dependents();
     const int n = blockIdx.x;
     const int s = seq_of_token[n];
@@ -413,7 +432,9 @@ rope_kv_write_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, int qkv_stride, con
                             const float* __restrict__ inv_freq, __nv_bfloat16* __restrict__ k_cache,
                             __nv_bfloat16* __restrict__ v_cache, int Hq, int Hkv, int D, int page_size, int num_pages,
                             int write_cache, int* status) {
+    TW_TIMELINE_SCOPE(TW_K_ROPE);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     tw_grid_launch_dependents();
     const int n = blockIdx.x;
     const int s = seq_of_token[n];
@@ -527,7 +548,9 @@ TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, 
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, long total,
                                 int interleaved) {
+    TW_TIMELINE_SCOPE(TW_K_SILU_MUL);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     tw_grid_launch_dependents();
     long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     const long step = (long)gridDim.x * blockDim.x;
@@ -546,7 +569,9 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_
 // bf16 with the intermediate size a multiple of 8: a thread handles 8 outputs with 16-byte accesses.
 __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate_up,
                                        int inter, long total8, int interleaved) {
+    TW_TIMELINE_SCOPE(TW_K_SILU_MUL);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     tw_grid_launch_dependents();
     long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     const long step = (long)gridDim.x * blockDim.x;

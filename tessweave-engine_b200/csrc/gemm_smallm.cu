@@ -56,12 +56,14 @@ struct Frag {          // 16 consecutive values of k of one row
 // row tiles whose k cannot be split over blocks (the SiLU.mul output needs whole sums): 27,648 x 5,120
 // at 8 rows 52 -> 45 us.
 template <int NT, int KS>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, (NT == 1 ? 5 : 0))
 gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M, int N, int K, int kper,
                    void* __restrict__ out, int out_mode, int out_stride) {
     constexpr int TILES = WARPS / KS;                  // 16-row tiles of a block
     __shared__ float s_part[KS > 1 ? TILES * 32 * NT * 4 : 1];
+    TW_TIMELINE_SCOPE(TW_K_GEMM_SMALLM);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     // With OUT_EARLY_DEPENDENTS the kernel launched after this one may become resident right away (it waits
     // for this kernel's results itself).  That pays when the next kernel is small, like the residual add +
     // norm after the o_proj and down products (measured: 0.5 % of a decode step); before the attention or
@@ -112,19 +114,37 @@ gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M
 
     Frag a_cur = load_w(wa, va, kbeg), b_cur = load_w(wb, vb, kbeg);
     Frag a_nxt = load_w(wa, va, kbeg + CHUNK), b_nxt = load_w(wb, vb, kbeg + CHUNK);
-    for (int k = kbeg; k < kend; k += CHUNK) {
-        // two steps ahead: the loads of step k + 2 CHUNK are in flight while step k is multiplied
-        const Frag a_far = load_w(wa, va, k + 2 * CHUNK), b_far = load_w(wb, vb, k + 2 * CHUNK);
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            const Frag xf = load_x(xr[t], vx[t], k);
-            mma_bf16(acc[t], a_cur.lo.x, b_cur.lo.x, a_cur.lo.y, b_cur.lo.y, xf.lo.x, xf.lo.y);
-            mma_bf16(acc[t], a_cur.lo.z, b_cur.lo.z, a_cur.lo.w, b_cur.lo.w, xf.lo.z, xf.lo.w);
-            mma_bf16(acc[t], a_cur.hi.x, b_cur.hi.x, a_cur.hi.y, b_cur.hi.y, xf.hi.x, xf.hi.y);
-            mma_bf16(acc[t], a_cur.hi.z, b_cur.hi.z, a_cur.hi.w, b_cur.hi.w, xf.hi.z, xf.hi.w);
+    if constexpr (NT == 1) {
+        // Up to 8 tokens: their values come one step ahead as well.  They are shared by all blocks and sit in L1
+        // or L2, but a matrix with few values of k per warp (o_proj and q/k/v at batch 8: six steps) would
+        // otherwise wait one L2 round trip in every step.
+        Frag x_nxt = load_x(xr[0], vx[0], kbeg);
+        for (int k = kbeg; k < kend; k += CHUNK) {
+            const Frag a_far = load_w(wa, va, k + 2 * CHUNK), b_far = load_w(wb, vb, k + 2 * CHUNK);
+            const Frag xf = x_nxt;
+            x_nxt = load_x(xr[0], vx[0], k + CHUNK);
+            mma_bf16(acc[0], a_cur.lo.x, b_cur.lo.x, a_cur.lo.y, b_cur.lo.y, xf.lo.x, xf.lo.y);
+            mma_bf16(acc[0], a_cur.lo.z, b_cur.lo.z, a_cur.lo.w, b_cur.lo.w, xf.lo.z, xf.lo.w);
+            mma_bf16(acc[0], a_cur.hi.x, b_cur.hi.x, a_cur.hi.y, b_cur.hi.y, xf.hi.x, xf.hi.y);
+            mma_bf16(acc[0], a_cur.hi.z, b_cur.hi.z, a_cur.hi.w, b_cur.hi.w, xf.hi.z, xf.hi.w);
+            a_cur = a_nxt; b_cur = b_nxt;
+            a_nxt = a_far; b_nxt = b_far;
         }
-        a_cur = a_nxt; b_cur = b_nxt;
-        a_nxt = a_far; b_nxt = b_far;
+    } else {
+        for (int k = kbeg; k < kend; k += CHUNK) {
+            // two steps ahead: the loads of step k + 2 CHUNK are in flight while step k is multiplied
+            const Frag a_far = load_w(wa, va, k + 2 * CHUNK), b_far = load_w(wb, vb, k + 2 * CHUNK);
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const Frag xf = load_x(xr[t], vx[t], k);
+                mma_bf16(acc[t], a_cur.lo.x, b_cur.lo.x, a_cur.lo.y, b_cur.lo.y, xf.lo.x, xf.lo.y);
+                mma_bf16(acc[t], a_cur.lo.z, b_cur.lo.z, a_cur.lo.w, b_cur.lo.w, xf.lo.z, xf.lo.w);
+                mma_bf16(acc[t], a_cur.hi.x, b_cur.hi.x, a_cur.hi.y, b_cur.hi.y, xf.hi.x, xf.hi.y);
+                mma_bf16(acc[t], a_cur.hi.z, b_cur.hi.z, a_cur.hi.w, b_cur.hi.w, xf.hi.z, xf.hi.w);
+            }
+            a_cur = a_nxt; b_cur = b_nxt;
+            a_nxt = a_far; b_nxt = b_far;
+        }
     }
     tw_grid_launch_dependents_late();     // the stream of weights is over: the next kernel may be scheduled
     if (KS > 1) {
@@ -172,7 +192,9 @@ gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M
 // Sum of the slices into a dense result (for consumers that cannot add slices themselves).
 template <typename T>
 __global__ void reduce_partial_kernel(T* __restrict__ out, const float* __restrict__ partial, int nsplit, long total) {
+    TW_TIMELINE_SCOPE(TW_K_REDUCE_PARTIAL);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     tw_grid_launch_dependents();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
@@ -202,8 +224,8 @@ TW_EXPORT int tw_gemm_smallm(const void* w, const void* x, int M, int N, int K, 
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
     }
-    // few blocks for the GPU (under 3.2 per SM, six fit) and a long k: two warps per row tile
-    const bool pair_warps = M <= 8 && (long)grid.x * grid.y * 10 <= (long)sm_count * 32 && kper >= 2048 && K >= 2048;
+    // few blocks for the GPU (under 3.2 per SM, five fit) and enough k for two warps: two warps per row tile
+    const bool pair_warps = M <= 8 && (long)grid.x * grid.y * 10 <= (long)sm_count * 32 && kper >= 512;
     if (pair_warps) {
         grid.x = (N + (WARPS / 2) * 16 - 1) / ((WARPS / 2) * 16);
         tw_launch(gemm_smallm_kernel<1, 2>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);

@@ -351,6 +351,13 @@ def attention_decode(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block
     _check(code, "attention_decode")
 
 
+def weight_prefetch_enabled() -> bool:
+    """TESSWEAVE_WEIGHT_PREFETCH=0: kernels of decode steps do not ask for the next kernel's weights to be
+    brought into L2 while they finish."""
+    import os
+    return os.environ.get("TESSWEAVE_WEIGHT_PREFETCH", "1") != "0"
+
+
 def fused_decode_enabled() -> bool:
     """TESSWEAVE_FUSED_DECODE=0 keeps bias, rotation and cache write of decode-only steps in a kernel of their own."""
     import os
@@ -359,11 +366,14 @@ def fused_decode_enabled() -> bool:
 
 def attention_decode_fused(out, source, bias, inv_freq, write_cache, seq_q_start, seq_q_len, seq_kv_len, seq_slot,
                            block_table, k_pages, v_pages, n_seqs, n_q_heads, n_kv_heads, head_dim, window, scale,
-                           nsplit, scratch, counters, status, merge_in_scratch: bool = False) -> None:
+                           nsplit, scratch, counters, status, merge_in_scratch: bool = False,
+                           prefetch: torch.Tensor | None = None) -> None:
     """Decode attention straight from the q/k/v product of a decode-only step: the kernel adds ``bias``,
     rotates q and k by position (``inv_freq``), writes the new key and value into their cache pages
     (``write_cache``) and attends.  ``source`` is the product: a ``SplitSum`` of fp32 slices or a bf16
-    [rows, (Hq + 2 Hkv) D] tensor.  The other arguments are those of ``attention_decode``."""
+    [rows, (Hq + 2 Hkv) D] tensor.  ``prefetch``: a contiguous tensor the next kernel streams (its weights);
+    the blocks ask for it to be brought into L2 once their keys are in.  The other arguments are those of
+    ``attention_decode``."""
     width = (n_q_heads + 2 * n_kv_heads) * head_dim
     partial = dense = None
     nslices = slice_stride = dense_stride = 0
@@ -403,7 +413,8 @@ def attention_decode_fused(out, source, bias, inv_freq, write_cache, seq_q_start
         _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages),
         c_int(n_seqs), c_int(n_q_heads), c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]),
         c_int(window), c_float(scale), c_int(nsplit), c_int(1 if merge_in_scratch else 0), _ptr(scratch), _ptr(counters),
-        _ptr(status), _stream())
+        _ptr(status), _ptr(prefetch), ctypes.c_longlong(prefetch.numel() * prefetch.element_size() if prefetch is not None else 0),
+        _stream())
     _check(code, "attention_decode_fused")
 
 
@@ -450,13 +461,14 @@ def small_m_supported(x: torch.Tensor, w: torch.Tensor, m: int) -> bool:
             and w.shape[1] % 8 == 0 and w.is_contiguous() and x.is_contiguous())
 
 
-def small_m_split(n: int, k: int) -> tuple[int, int]:
+def small_m_split(n: int, k: int, max_slices: int = 12) -> tuple[int, int]:
     """(slices, k per slice): enough slices that rows / 16 * slices warps fill the GPU, each
-    slice a multiple of 32 wide and at least 256."""
+    slice a multiple of 32 wide and at least 256.  ``max_slices``: the most slices the consumer wants to add
+    (the kernel then gives a row tile to two warps where that fills the GPU better)."""
     tiles = -(-n // 16)
     if tiles >= 1024:          # enough rows to fill the GPU without slices
         return 1, -(-k // 32) * 32
-    want = max(1, min(12, -(-_TARGET_WARPS // tiles)))
+    want = max(1, min(12, max_slices, -(-_TARGET_WARPS // tiles)))
     kper = max(256, -(-(-(-k // want)) // 32) * 32)
     kper = min(kper, -(-k // 32) * 32)
     return -(-k // kper), kper

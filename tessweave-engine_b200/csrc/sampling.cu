@@ -32,7 +32,9 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
     __shared__ float swarp[32];
     __shared__ float sbcast[2];
     __shared__ int sbest;
+    TW_TIMELINE_SCOPE(TW_K_SAMPLE);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     tw_grid_launch_dependents();
     const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* x = logits + (size_t)r * vocab;

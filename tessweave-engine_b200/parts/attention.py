@@ -63,13 +63,15 @@ class GQAAttention(Mixer):
             raise TypeError("gqa_attention needs a paged key/value cache")
         n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
         table = self.position.fused_rotary_table(self.head_dim)
-        qkv = linear(ctx, "attn.qkv", h, self.w_qkv, allow_split=table is not None)
+        fused_decode = (table is not None and ctx.decode_only and ops.fused_decode_enabled()
+                        and ops.tensor_core_attention_supported(dt, self.head_dim))
+        # the decode kernel reads the product once per block: up to four slices are one round trip to L2 for it
+        qkv = linear(ctx, "attn.qkv", h, self.w_qkv, allow_split=table is not None, max_slices=4 if fused_decode else 12)
         source = None
         if isinstance(qkv, SplitSum):       # the fused kernel below adds the slices itself
             source, qkv = qkv, ws.get("attn.qkv", (n, self.qkv_width), dt)
         out = ws.get("attn.out", (n, self.q_size), dt)
-        if (table is not None and ctx.decode_only and ops.fused_decode_enabled()
-                and ops.tensor_core_attention_supported(dt, self.head_dim)):
+        if fused_decode:
             # decode-only step: the attention kernel adds the bias, rotates, writes the new key and value and attends
             self._decode(ctx, out, None, cache, fused=(source if source is not None else qkv, table, write_cache))
             return linear(ctx, "mixer.delta", out, self.w_o, allow_split=ctx.split_ok, small_consumer=True)
@@ -120,7 +122,8 @@ class GQAAttention(Mixer):
             ops.attention_decode_fused(out, product, self.b_qkv, table, write_cache, ctx.seq_q_start, ctx.seq_q_len,
                                        ctx.seq_kv_len, ctx.seq_slot, cache.block_table, cache.k_pages, cache.v_pages,
                                        ctx.n_seqs, self.n_heads, self.n_kv_heads, self.head_dim, window, self.scale,
-                                       nsplit, scratch, counters, ctx.status)
+                                       nsplit, scratch, counters, ctx.status,
+                                       prefetch=self.w_o if ops.weight_prefetch_enabled() else None)
             return
         ops.attention_decode(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
                              cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, self.n_heads,

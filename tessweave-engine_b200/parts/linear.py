@@ -41,7 +41,7 @@ def matmul_nt(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tens
 
 
 def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-           allow_split: bool = False, small_consumer: bool = False):
+           allow_split: bool = False, small_consumer: bool = False, max_slices: int = 12):
     """``x @ w.T`` into the workspace buffer ``name``.
 
     Steps with up to 8 rows (decode) in bfloat16 go through the weight-streaming kernel of
@@ -51,6 +51,7 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
     (``allow_split``), the fp32 slices are returned as a ``SplitSum`` for the consuming kernel
     to add.  Everything else is a library product.  ``small_consumer`` says that the kernel that follows is
     a small one (a norm, a sampler): the weight-streaming kernel then lets it become resident early.
+    ``max_slices``: the most slices the consumer of a ``SplitSum`` wants to add.
     """
     m, n = x.shape[0], w.shape[0]
     dtype = out_dtype or x.dtype
@@ -67,7 +68,7 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
         ops.gemm_tcgen05(out, x, w, m, ctx.status, swap=True)
         return out
     if x.is_cuda and ops.small_m_supported(x, w, m):
-        split, kper = ops.small_m_split(n, w.shape[1])
+        split, kper = ops.small_m_split(n, w.shape[1], max_slices if allow_split else 12)
         if split > 1 and allow_split:
             slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
             ops.gemm_small_m(slices, x, w, m, kper, early_dependents=small_consumer)

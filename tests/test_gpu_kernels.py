@@ -491,7 +491,7 @@ def test_gemm_small_m(m, n, k):
     out16 = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
     ops().gemm_small_m(out16, x, w, m)
     assert torch.allclose(out16.float(), want, atol=tol["atol"] + 8e-3 * float(want.abs().max()), rtol=0)
-    for kper in (32, 256, 416):
+    for kper in (32, 256, 416, 896):         # 896: few blocks and long slices, two warps share a row tile (m <= 8)
         if kper >= k:
             continue
         split = -(-k // kper)
@@ -612,12 +612,14 @@ def test_gemm_tcgen05_pair_silu_mul(m, n, k):
 # decode attention that makes q, k and v of the new token itself
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (6, 3, 48), (8, 8, 16), (20, 2, 64), (4, 2, 256)])
-@pytest.mark.parametrize("split_source", [False, True])
+@pytest.mark.parametrize("split_source", [0, 2, 3, 4, 5, 9])
 @pytest.mark.parametrize("window", [0, 40])
 def test_decode_attention_fused_with_rotation_and_cache_write(hq, hkv, d, split_source, window):
     """The fused kernel against the two kernels it replaces (bias + rotation + cache write, then decode
     attention): the same attention output and the same cache contents, bit for bit, for requests whose
-    newest position is a page's first slot, its last slot, position 0 and somewhere in between."""
+    newest position is a page's first slot, its last slot, position 0 and somewhere in between.  The product
+    comes as bf16 rows (0) or as that many fp32 slices: up to four are loaded ahead of the keys, more afterwards.
+    One of the two runs also asks for a tensor to be prefetched into L2, which changes nothing."""
     o = ops()
     lengths = [1, 16 * 9 + 1, 16 * 11, 300]
     page = 16
@@ -631,7 +633,7 @@ def test_decode_attention_fused_with_rotation_and_cache_write(hq, hkv, d, split_
     q_start, q_len, kv_len, slot = i32(list(range(n))), i32([1] * n), i32(lengths), i32(setup["slots"])
     positions, seq_of = i32([m - 1 for m in lengths]), i32(list(range(n)))
     if split_source:
-        slices = dev(torch.randn(5, n, width, generator=g))
+        slices = dev(torch.randn(split_source, n, width, generator=g))
         source = o.SplitSum(slices)
         dense = torch.zeros(n, width, device="cuda", dtype=torch.bfloat16)
     else:
@@ -654,7 +656,7 @@ def test_decode_attention_fused_with_rotation_and_cache_write(hq, hkv, d, split_
         out_b = torch.full((n, hq * d), float("nan"), device="cuda", dtype=torch.bfloat16)
         o.attention_decode_fused(out_b, source if source is not None else dense, bias, inv, True, q_start, q_len, kv_len, slot,
                                  setup["table"], k_b, v_b, n, hq, hkv, d, window, d ** -0.5, ns, scratch, counters, st,
-                                 merge_in_scratch=merge_in_scratch)
+                                 merge_in_scratch=merge_in_scratch, prefetch=None if merge_in_scratch else bias)
         assert int(st) == 0
         assert torch.equal(k_a.view(torch.int16), k_b.view(torch.int16)), "keys written differ"
         assert torch.equal(v_a.view(torch.int16), v_b.view(torch.int16)), "values written differ"

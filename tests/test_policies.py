@@ -27,3 +27,37 @@ def test_small_m_split_covers_k(n, k):
 def test_products_route_by_rows():
     assert ops.SMALL_M_LIMIT == 8 and ops.PAIR_MIN_M >= 256
     assert ops.TCGEN05_MIN_M == ops.SMALL_M_LIMIT + 1
+
+
+def test_split_policy_respects_the_consumers_limit():
+    """A consumer that adds at most four slices gets at most four; the default stays at up to twelve."""
+    from tessweave_engine_b200.csrc import ops
+    slices, kper = ops.small_m_split(4608, 3584, max_slices=4)
+    assert slices == 4 and kper % 32 == 0 and slices * kper >= 3584
+    wide, _ = ops.small_m_split(4608, 3584)
+    assert 4 < wide <= 12
+    assert ops.small_m_split(152064, 3584, max_slices=4)[0] == 1       # enough rows: no slices at all
+
+
+def test_timeline_groups_blocks_into_launches():
+    """Blocks of two launches of one kernel in a row (told apart by their count), a second kernel overlapping
+    the first, and the gap between launches."""
+    import torch
+    from tessweave_engine_b200.engine.timeline import group_launches, format_launches
+    tag = lambda kernel, blocks: kernel | (blocks << 16)
+    rows = []
+    for b in range(3):                                   # kernel 5, 3 blocks: 1000..1400
+        rows.append([tag(5, 3), b, 1000 + 10 * b, 1000 + 10 * b, 1300 + 50 * b])
+    for b in range(2):                                   # kernel 3, 2 blocks, resident early, waits until 1400
+        rows.append([tag(3, 2), b, 1200 + b, 1400, 1500 + b])
+    for b in range(3):                                   # kernel 5 again, 3 blocks
+        rows.append([tag(5, 3), b, 1600 + b, 1600 + b, 1900])
+    entries = torch.tensor(rows, dtype=torch.int64)[torch.randperm(len(rows), generator=torch.Generator().manual_seed(0))]
+    launches = group_launches(entries)
+    assert [(l["kernel"], l["blocks"], l["seen"]) for l in launches] == [
+        ("gemm_smallm", 3, 3), ("norm (cluster)", 2, 2), ("gemm_smallm", 3, 3)]
+    assert launches[0]["start"] == 0.0 and abs(launches[0]["end"] - 0.4) < 1e-9 and abs(launches[0]["ramp"] - 0.02) < 1e-9
+    assert launches[1]["gap"] < 0 and 0.199 <= launches[1]["waited"] <= 0.2            # launched while the first ran
+    assert abs(launches[2]["gap"] - 0.099) < 1e-9                                      # after the later of the two ends
+    assert "gemm_smallm" in format_launches(launches)
+    assert group_launches(torch.zeros(0, 5, dtype=torch.int64)) == []
