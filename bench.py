@@ -332,6 +332,48 @@ def reference_arm(args) -> int:
     return 0
 
 
+def timeline_run(args) -> int:
+    """One decode step of ``--layers`` layers recorded on the device: every launch with its start, the gap to
+    the launch before, how long its blocks took to start and waited, and when its first and last block ended."""
+    import torch
+    import tessweave_engine_b200 as tw
+    from tessweave_engine_b200.engine.runner import ModelRunner, StepEntry
+    from tessweave_engine_b200.engine.timeline import Timeline, format_launches
+    timeline = Timeline()
+    model, cfg = build_model(args.layers)
+    batch, total = args.batch, max(4, args.warmup) + 1
+    start = max(1, args.context - total)
+    pages = batch * (-(-(start + total) // PAGE_SIZE))
+    cache = tw.CacheManager(model.cache_needs(), PAGE_SIZE, pages, batch, start + total, model.runtime.dtype,
+                            model.runtime.device, prefix_cache=False)
+    for g in cache.groups:
+        g.k.normal_(0, 0.5)
+        g.v.normal_(0, 0.5)
+    runner = ModelRunner(model, cache, max_step_tokens=batch, max_step_seqs=batch, cuda_graphs=not args.no_graphs)
+    leases = [cache.admit(None) for _ in range(batch)]
+    for lease in leases:
+        cache.ensure(lease, start + total)
+
+    def one(i):
+        runner.step([StepEntry(leases[b].slot, [(7 * i + b) % cfg.vocab_size], start + i, [0]) for b in range(batch)])
+
+    for i in range(total - 1):
+        one(i)
+    timeline.reset()
+    one(total - 1)
+    rows = timeline.launches()
+    runner.check_status()
+    print(format_launches(rows), file=sys.stderr)
+    by_kernel: dict[str, list[float]] = {}
+    for r in rows:
+        by_kernel.setdefault(f"{r['kernel']} x{r['blocks']}", []).append(r["end"] - r["start"] - r["waited"])
+    # per kernel and grid size: launches, and the median time from the end of its blocks' wait to its last block's end
+    summary = {k: {"launches": len(v), "median_us": round(sorted(v)[len(v) // 2], 2)} for k, v in by_kernel.items()}
+    print(json.dumps({"timeline": "one decode step", "layers": args.layers, "batch": batch, "context": args.context,
+                      "launches": len(rows), "step_us": round(rows[-1]["end"], 1) if rows else None, "kernels": summary}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -347,6 +389,9 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--kernels", action="store_true",
                     help="time every operation of a layer and the output head alone and print each with its roofline")
+    ap.add_argument("--timeline", action="store_true",
+                    help="record one decode step block by block on the device (kernels compiled with their recorder) "
+                         "and print its launches in time order; for looking at, not a measurement")
     ap.add_argument("--workload", choices=sorted(WORKLOAD_SIZES), default=None,
                     help="run a whole-engine workload at 14B / 32B layer sizes instead of the headline measurement")
     args = ap.parse_args()
@@ -374,6 +419,9 @@ def main() -> int:
         print(json.dumps({"kernels": rows, "peaks": pk, "peaks_source": pk_source, "batch": args.batch,
                           "context": args.context, "prefill_tokens": PREFILL_TOKENS}))
         return 0
+    if args.timeline:
+        os.environ["TESSWEAVE_TIMELINE"] = "1"       # before the first kernel library is loaded
+        return timeline_run(args)
     model, cfg = build_model(args.layers)
     if args.only == "prefill":
         print(json.dumps({"only": "prefill", "layers": args.layers, **prefill_run(model, cfg, PREFILL_TOKENS, args.steps, args.warmup)}))
