@@ -33,6 +33,20 @@ __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ ta
     }
     const T* row = table + (size_t)id * hidden;
     float* dst = resid + (size_t)n * hidden;
+    if constexpr (sizeof(T) == 2) {
+        // 16 bytes per load where the row allows: a decode step waits for this kernel's one round trip to memory
+        if ((hidden & 7) == 0 && (reinterpret_cast<uintptr_t>(table) & 15) == 0 && (reinterpret_cast<uintptr_t>(resid) & 15) == 0) {
+            for (int i = threadIdx.x; i < (hidden >> 3); i += blockDim.x) {
+                const uint4 raw = reinterpret_cast<const uint4*>(row)[i];
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                const float2 a = __bfloat1622float2(h2[0]), b = __bfloat1622float2(h2[1]);
+                const float2 c = __bfloat1622float2(h2[2]), d = __bfloat1622float2(h2[3]);
+                reinterpret_cast<float4*>(dst)[2 * i] = make_float4(a.x, a.y, b.x, b.y);
+                reinterpret_cast<float4*>(dst)[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+            }
+            return;
+        }
+    }
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = tw_to_float(row[i]);
 }
 

@@ -597,3 +597,86 @@ def gemm_tcgen05_pair(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: in
     code = _fn("gemm_tcgen05_pair", "tw_gemm_tcgen05_pair")(_ptr(x), _ptr(w), c_int(m), c_int(n), c_int(k), _ptr(out),
                                                             c_int(mode), c_int(out.stride(0)), _ptr(status), _stream())
     _check(code, "gemm_tcgen05_pair")
+
+
+# ---------------------------------------------------------------------------
+# matrix products of decode steps with more requests than the small-M kernel takes
+# ---------------------------------------------------------------------------
+STREAM_MIN_M, STREAM_MAX_M = 9, 128     # rows the persistent weight-streaming tcgen05 kernel takes
+STREAM_MIN_WEIGHTS = 48_000_000         # elements of w from which it is the product path
+
+
+def stream_product_preferred(x: torch.Tensor, w: torch.Tensor, m: int) -> bool:
+    """Whether a product of ``m`` rows runs on ``gemm_tcgen05_stream`` (persistent, the weights as the 128-row
+    operand): 9 to 64 rows and a large matrix.  Measured on B200 at 7B layer sizes, 16 / 64 rows: down 25.9 / 28.1
+    us against the library's 28.9 / 31.1, gate/up with SiLU.mul 47.5 / 51.7 against 46.6 / 48.1 plus 2.5 / 3.5 for
+    the separate SiLU.mul kernel, logits 171 / 181 against 179 / 183; the smaller q/k/v and o_proj products
+    (8.8 / 10.7 against 8.6 / 8.9) stay with the library, whose split over k is reduced inside its kernel.
+    TESSWEAVE_STREAM_GEMM=0 keeps the library everywhere; TESSWEAVE_STREAM_MAX_M and TESSWEAVE_STREAM_MIN_WEIGHTS
+    move the bounds."""
+    import os
+    if os.environ.get("TESSWEAVE_STREAM_GEMM", "1") == "0":
+        return False
+    top = min(STREAM_MAX_M, int(os.environ.get("TESSWEAVE_STREAM_MAX_M", "64")))
+    least = int(os.environ.get("TESSWEAVE_STREAM_MIN_WEIGHTS", str(STREAM_MIN_WEIGHTS)))
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and STREAM_MIN_M <= m <= top
+            and w.numel() >= least and w.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+_stream_sms: list[int] = [0]
+
+
+def stream_split(n: int, k: int, allow: bool = True, sms: int | None = None) -> tuple[int, int]:
+    """(slices, k per slice) for the persistent kernel: its work items are (128-row tile of w, slice of k), dealt
+    round robin to one block per SM.  The choice minimises the k-blocks of the busiest block, each item charged
+    four more for its start and its result; up to 12 slices."""
+    kbs = -(-k // 64)
+    if not allow:
+        return 1, kbs * 64
+    if sms is None:
+        if not _stream_sms[0]:
+            _stream_sms[0] = int(_fn("gemm_tcgen05_stream", "tw_gemm_tcgen05_stream_sm_count")())
+        sms = _stream_sms[0]
+    tiles = -(-n // 128)
+    best = None
+    for want in range(1, 13):
+        per = -(-kbs // want)
+        real = -(-kbs // per)
+        cost = -(-tiles * real // sms) * (per + 4)
+        if best is None or cost < best[0]:
+            best = (cost, real, per * 64)
+    return best[1], best[2]
+
+
+def gemm_tcgen05_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, status: torch.Tensor,
+                        kper: int | None = None, silu_mul_pairs: bool = False) -> None:
+    """out[:m] = x[:m] @ w.T for up to 128 rows on the 5th-generation tensor cores, the weights streamed once by a
+    persistent kernel.  ``out`` is bf16 or fp32 [>=m, n]; fp32 slices [slices, m, n] when ``kper`` (a multiple of
+    64) is less than k; with ``silu_mul_pairs`` (rows of w in groups of eight gates and their eight ups) bf16
+    [>=m, n / 2] = silu(gate) * up."""
+    _cuda(out, x, w, status)
+    n, k = w.shape
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x.is_contiguous()
+          and x.shape[1] == k and k % 8 == 0 and 0 < m <= STREAM_MAX_M and x.shape[0] >= m,
+          "gemm_tcgen05_stream: contiguous bf16 operands, k a multiple of 8, up to 128 rows")
+    _need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0, "gemm_tcgen05_stream: operands must be 16-byte aligned")
+    kper = kper or -(-k // 64) * 64
+    _need(kper % 64 == 0, "gemm_tcgen05_stream: k per slice must be a multiple of 64")
+    split = -(-k // kper)
+    if silu_mul_pairs:
+        _need(split == 1 and n % 16 == 0 and out.dtype == torch.bfloat16 and out.dim() == 2 and out.stride(1) == 1
+              and out.shape[0] >= m and out.shape[1] == n // 2, "gemm_tcgen05_stream: bad fused SiLU.mul output")
+        mode, stride = 3, out.stride(0)
+    elif split > 1:
+        _need(out.dtype == torch.float32 and out.dim() == 3 and tuple(out.shape) == (split, m, n) and out.is_contiguous(),
+              "gemm_tcgen05_stream: split output must be fp32 [slices, m, n]")
+        mode, stride = 2, n
+    else:
+        _need(out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= m and out.shape[1] == n
+              and out.dtype in (torch.bfloat16, torch.float32), "gemm_tcgen05_stream: bad output")
+        mode, stride = (0 if out.dtype == torch.bfloat16 else 1), out.stride(0)
+    # the token rows the kernel reads: exactly m (rows beyond are filled with zeros by the copy engine)
+    code = _fn("gemm_tcgen05_stream", "tw_gemm_tcgen05_stream")(_ptr(x), _ptr(w), c_int(m), c_int(n), c_int(k), c_int(kper),
+                                                                _ptr(out), c_int(mode), c_int(stride), _ptr(status), _stream())
+    _check(code, "gemm_tcgen05_stream")

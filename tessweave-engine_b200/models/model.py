@@ -99,7 +99,9 @@ class Model:
 
     def head_logits(self, ctx: StepContext, logits: torch.Tensor, y: torch.Tensor, n_rows: int) -> None:
         """logits = y @ head.T in fp32 (reference: flow_engine/model.py:204)."""
-        if ops.tcgen05_supported(y, self.head, n_rows):
+        if ops.stream_product_preferred(y, self.head, n_rows):
+            ops.gemm_tcgen05_stream(logits[:n_rows], y, self.head, n_rows, ctx.status)
+        elif ops.tcgen05_supported(y, self.head, n_rows):
             ops.gemm_tcgen05(logits[:n_rows], y, self.head, n_rows, ctx.status, swap=True)
         elif ops.small_m_supported(y, self.head, n_rows):
             ops.gemm_small_m(logits[:n_rows], y, self.head, n_rows)

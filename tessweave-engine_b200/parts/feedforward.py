@@ -45,6 +45,10 @@ class SwiGLU(FeedForward):
         act = ws.get("ffn.act", (n, self.intermediate), dt)
         if self.interleaved and ops.small_m_supported(h, self.w_gate_up, n):
             ops.gemm_small_m(act, h, self.w_gate_up, n, silu_mul_pairs=True)
+        elif self.interleaved and ops.stream_product_preferred(h, self.w_gate_up, n):
+            # decode steps of 9 to 64 requests: persistent tcgen05 kernel, weights as the 128-row operand,
+            # SiLU.mul in its epilogue
+            ops.gemm_tcgen05_stream(act, h, self.w_gate_up, n, ctx.status, silu_mul_pairs=True)
         elif self.interleaved and ops.pair_product_preferred(h, self.w_gate_up, n):
             # prompt steps: 256 x 256 tiles on pairs of thread blocks (tcgen05.mma.cta_group::2), SiLU.mul in the
             # epilogue, so the [tokens, 2 * intermediate] product never reaches memory

@@ -45,7 +45,8 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
     """``x @ w.T`` into the workspace buffer ``name``.
 
     Steps with up to 8 rows (decode) in bfloat16 go through the weight-streaming kernel of
-    csrc/gemm_smallm.cu.  (The tcgen05/TMA kernel of csrc/gemm_tcgen05.cu with the weights as the
+    csrc/gemm_smallm.cu; products of 9 to 64 rows with a large matrix (down, logits) through the persistent
+    tcgen05 kernel of csrc/gemm_tcgen05_stream.cu.  (The tcgen05/TMA kernel of csrc/gemm_tcgen05.cu with the weights as the
     128-row operand takes 9 to 32 rows when TESSWEAVE_SWAP_AB=1; the library measured faster there.)
     When the matrix has too few rows to fill the GPU these kernels split k and, if the caller can take it
     (``allow_split``), the fp32 slices are returned as a ``SplitSum`` for the consuming kernel
@@ -66,6 +67,19 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
             return SplitSum(slices).dense(dtype, ctx.workspace.get(name, (m, n), dtype))
         out = ctx.workspace.get(name, (m, n), dtype)
         ops.gemm_tcgen05(out, x, w, m, ctx.status, swap=True)
+        return out
+    if ops.stream_product_preferred(x, w, m):
+        # decode steps of 9 to 64 requests, large matrices: the weights stream once through the persistent
+        # tcgen05 kernel (csrc/gemm_tcgen05_stream.cu); slices only where the consumer adds them itself
+        split, kper = ops.stream_split(n, w.shape[1])
+        if split > 1:
+            slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
+            ops.gemm_tcgen05_stream(slices, x, w, m, ctx.status, kper=kper)
+            if allow_split:
+                return SplitSum(slices)
+            return SplitSum(slices).dense(dtype, ctx.workspace.get(name, (m, n), dtype))
+        out = ctx.workspace.get(name, (m, n), dtype)
+        ops.gemm_tcgen05_stream(out, x, w, m, ctx.status)
         return out
     if x.is_cuda and ops.small_m_supported(x, w, m):
         split, kper = ops.small_m_split(n, w.shape[1], max_slices if allow_split else 12)

@@ -30,7 +30,11 @@ def big(tmp_path_factory):
 def test_benchmark_layer_sizes_against_plain(dtype, big, tmp_path):
     folder, tokens, want = big
     tol = 1e-4 if dtype == "float32" else 0.03 * max(1.0, float(np.abs(want).max()))
-    for name, steps in (("whole", schedule_whole({"r": tokens})), ("tail", schedule_tail({"r": tokens}, tail=10))):
+    # portions of 9 to 64 rows: in bfloat16 their large products (gate/up, down, logits) run on the persistent
+    # tcgen05 weight-streaming kernel
+    from helpers import schedule_portions
+    for name, steps in (("whole", schedule_whole({"r": tokens})), ("tail", schedule_tail({"r": tokens}, tail=10)),
+                        ("portions", schedule_portions({"r": tokens}, sizes=(12, 40, 64, 9, 25)))):
         rows = replay_in_process(folder, dtype, steps, tmp_path / name)
         worst = max(float(np.abs(rows[("r", p)] - want[p]).max()) for p in range(len(tokens)))
         assert worst <= tol, f"{dtype} {name}: off by {worst:.3e} (logits up to {np.abs(want).max():.2f})"

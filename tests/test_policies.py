@@ -61,3 +61,17 @@ def test_timeline_groups_blocks_into_launches():
     assert abs(launches[2]["gap"] - 0.099) < 1e-9                                      # after the later of the two ends
     assert "gemm_smallm" in format_launches(launches)
     assert group_launches(torch.zeros(0, 5, dtype=torch.int64)) == []
+
+
+def test_stream_split_balances_items_over_the_blocks():
+    """The persistent kernel's slices: none where the row tiles alone fill the GPU twice over, enough where a matrix
+    has few rows, never more than twelve, k per slice a multiple of 64 that covers k."""
+    from tessweave_engine_b200.csrc import ops
+    assert ops.stream_split(37888, 3584, sms=148)[0] == 1          # 296 tiles: two items per block
+    assert ops.stream_split(152064, 3584, sms=148)[0] == 1
+    slices, kper = ops.stream_split(3584, 18944, sms=148)          # 28 tiles
+    assert 4 <= slices <= 6 and kper % 64 == 0 and slices * kper >= 18944 and (slices - 1) * kper < 18944
+    assert ops.stream_split(3584, 18944, allow=False, sms=148) == (1, 18944)
+    for n, k in ((100, 64), (5120, 13824), (128, 100000)):
+        slices, kper = ops.stream_split(n, k, sms=148)
+        assert 1 <= slices <= 12 and kper % 64 == 0 and (slices - 1) * kper < k <= slices * kper
