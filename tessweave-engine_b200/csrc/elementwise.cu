@@ -609,6 +609,69 @@ __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __
     }
 }
 
+// The same from the fp32 slices of a gate/up product split over k ([slice][row][2 * inter], `split_stride` floats
+// apart): the slices are added in the order every consumer of a split product uses (whole groups of four into
+// four sums by slice mod 4, the rest into the first, then (s0 + s1) + (s2 + s3)), then silu(gate) * up, bf16 out.
+// Four outputs per thread; inter a multiple of 8 when interleaved, of 4 otherwise.
+__device__ __forceinline__ float4 tw_sum_slices4(const float* p, int nsplit, size_t split_stride) {
+    float4 s[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) s[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    int k = 0;
+    for (; k + 4 <= nsplit; k += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float4 v = *reinterpret_cast<const float4*>(p + (size_t)(k + u) * split_stride);
+            s[u].x += v.x; s[u].y += v.y; s[u].z += v.z; s[u].w += v.w;
+        }
+    }
+    for (; k < nsplit; ++k) {
+        const float4 v = *reinterpret_cast<const float4*>(p + (size_t)k * split_stride);
+        s[0].x += v.x; s[0].y += v.y; s[0].z += v.z; s[0].w += v.w;
+    }
+    return make_float4((s[0].x + s[1].x) + (s[2].x + s[3].x), (s[0].y + s[1].y) + (s[2].y + s[3].y),
+                       (s[0].z + s[1].z) + (s[2].z + s[3].z), (s[0].w + s[1].w) + (s[2].w + s[3].w));
+}
+
+__global__ void silu_mul_slices_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ partial, int nsplit,
+                                       size_t split_stride, int inter, long total4, int interleaved) {
+    TW_TIMELINE_SCOPE(TW_K_SILU_MUL);
+    tw_grid_wait();
+    TW_TIMELINE_MARK();
+    tw_grid_launch_dependents();
+    long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long step = (long)gridDim.x * blockDim.x;
+    const int quads = inter >> 2;
+    for (; idx < total4; idx += step) {
+        const long n = idx / quads;
+        const int i = (int)(idx - n * quads) * 4;                       // first of this thread's four outputs
+        const int gcol = interleaved ? ((i >> 3) << 4) + (i & 7) : i;
+        const int ucol = interleaved ? gcol + 8 : inter + i;
+        const float* row = partial + (size_t)n * 2 * inter;
+        const float4 g = tw_sum_slices4(row + gcol, nsplit, split_stride);
+        const float4 u = tw_sum_slices4(row + ucol, nsplit, split_stride);
+        uint2 packed;
+        *reinterpret_cast<__nv_bfloat162*>(&packed.x) =
+            __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+        *reinterpret_cast<__nv_bfloat162*>(&packed.y) =
+            __floats2bfloat162_rn(g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w);
+        *reinterpret_cast<uint2*>(out + n * (long)inter + i) = packed;
+    }
+}
+
+TW_EXPORT int tw_silu_mul_slices(void* out, const float* partial, int nsplit, long split_stride, int n_rows, int inter,
+                                 int interleaved, cudaStream_t stream) {
+    if (n_rows <= 0 || inter <= 0) return 0;
+    if (nsplit < 1 || (inter & 3) || (interleaved && (inter & 7)) || (split_stride & 3) ||
+        ((uintptr_t)partial & 15) || ((uintptr_t)out & 7))
+        return (int)cudaErrorInvalidValue;
+    const long total4 = (long)n_rows * (inter >> 2);
+    const long blocks = (total4 + 255) / 256;
+    tw_launch(silu_mul_slices_kernel, dim3((int)(blocks > 4096 ? 4096 : blocks)), dim3(256), 0, stream, 1, (__nv_bfloat16*)out,
+              partial, nsplit, (size_t)split_stride, inter, total4, interleaved);
+    return TW_LAUNCH_CHECK();
+}
+
 TW_EXPORT int tw_silu_mul(void* out, const void* gate_up, int n_rows, int inter, int interleaved, int dtype,
                           cudaStream_t stream) {
     const long total = (long)n_rows * inter;

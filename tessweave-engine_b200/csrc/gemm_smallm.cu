@@ -198,9 +198,16 @@ __global__ void reduce_partial_kernel(T* __restrict__ out, const float* __restri
     tw_grid_launch_dependents();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
-    float s = 0.f;
-    for (int i = 0; i < nsplit; ++i) s += partial[(size_t)i * total + idx];
-    out[idx] = tw_from_float<T>(s);
+    // the order every consumer of a split product uses: whole groups of four slices into four sums by slice mod 4,
+    // the rest into the first, then (s0 + s1) + (s2 + s3)
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    int i = 0;
+    for (; i + 4 <= nsplit; i += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) s[u] += partial[(size_t)(i + u) * total + idx];
+    }
+    for (; i < nsplit; ++i) s[0] += partial[(size_t)i * total + idx];
+    out[idx] = tw_from_float<T>((s[0] + s[1]) + (s[2] + s[3]));
 }
 
 }  // namespace

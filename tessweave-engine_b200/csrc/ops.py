@@ -197,11 +197,23 @@ def rotate_heads(rows: torch.Tensor, bias: torch.Tensor | None, positions: torch
     _check(code, "rotate_heads")
 
 
-def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, n_rows: int, interleaved: bool = False) -> None:
+def silu_mul(out: torch.Tensor, gate_up, n_rows: int, interleaved: bool = False) -> None:
     """out[n, i] = silu(gate[n, i]) * up[n, i].  Columns of ``gate_up`` are [all gates | all ups],
-    or with ``interleaved`` groups of 16: eight gates followed by their eight ups."""
-    _cuda(out, gate_up)
+    or with ``interleaved`` groups of 16: eight gates followed by their eight ups.  ``gate_up`` may be a
+    ``SplitSum`` (fp32 slices of the product, added here in slice order); ``out`` is then bfloat16."""
     inter = out.shape[1]
+    if isinstance(gate_up, SplitSum):
+        slices = gate_up.slices
+        _cuda(out, slices)
+        _need(out.dtype == torch.bfloat16 and out.is_contiguous() and slices.dtype == torch.float32 and slices.dim() == 3
+              and slices.shape[1] >= n_rows and slices.shape[2] == 2 * inter and slices[0].is_contiguous()
+              and inter % 4 == 0 and (not interleaved or inter % 8 == 0) and out.shape[0] >= n_rows,
+              "silu_mul: slices must be fp32 [slices, rows, 2I], the output bf16 [rows, I], I a multiple of 4 (8 interleaved)")
+        code = _fn("elementwise", "tw_silu_mul_slices")(_ptr(out), _ptr(slices), c_int(slices.shape[0]), c_long(slices.stride(0)),
+                                                        c_int(n_rows), c_int(inter), c_int(1 if interleaved else 0), _stream())
+        _check(code, "silu_mul_slices")
+        return
+    _cuda(out, gate_up)
     _need(gate_up.shape[1] == 2 * inter and gate_up.is_contiguous() and out.is_contiguous()
           and gate_up.dtype == out.dtype, "silu_mul: gate_up must be contiguous [n, 2I] of the output type")
     _need(not interleaved or inter % 8 == 0, "silu_mul: interleaved columns need a multiple of 8")
@@ -627,6 +639,30 @@ def stream_product_preferred(x: torch.Tensor, w: torch.Tensor, m: int) -> bool:
 _stream_sms: list[int] = [0]
 
 
+def _stream_sm_count() -> int:
+    if not _stream_sms[0]:
+        _stream_sms[0] = int(_fn("gemm_tcgen05_stream", "tw_gemm_tcgen05_stream_sm_count")())
+    return _stream_sms[0]
+
+
+def stream_whole_k_balanced(n: int, sms: int | None = None) -> bool:
+    """Whether the 128-row tiles of a matrix of ``n`` rows, not split over k (the SiLU.mul epilogue needs whole
+    sums), keep the persistent kernel's blocks evenly busy: 296 tiles on 148 SMs do (two each), 216 do not (68
+    blocks get two, 80 one; the 14B gate/up product measured slower than the library that way)."""
+    sms = sms or _stream_sm_count()
+    tiles = -(-n // 128)
+    return tiles / sms >= 0.85 * -(-tiles // sms)
+
+
+def stream_split_gate_up_enabled() -> bool:
+    """TESSWEAVE_STREAM_SPLIT_GATE_UP=1: a gate/up product whose row tiles alone do not balance (14B: 216 tiles)
+    runs on the persistent kernel in slices over k that the SiLU.mul kernel adds.  Off by default: measured at 14B
+    layer sizes a decode step is 1 % shorter with it at batch 12 and 24 and 2.5 % longer at batch 32, where the
+    library's product is at its best."""
+    import os
+    return os.environ.get("TESSWEAVE_STREAM_SPLIT_GATE_UP", "0") == "1"
+
+
 def stream_split(n: int, k: int, allow: bool = True, sms: int | None = None) -> tuple[int, int]:
     """(slices, k per slice) for the persistent kernel: its work items are (128-row tile of w, slice of k), dealt
     round robin to one block per SM.  The choice minimises the k-blocks of the busiest block, each item charged
@@ -634,10 +670,7 @@ def stream_split(n: int, k: int, allow: bool = True, sms: int | None = None) -> 
     kbs = -(-k // 64)
     if not allow:
         return 1, kbs * 64
-    if sms is None:
-        if not _stream_sms[0]:
-            _stream_sms[0] = int(_fn("gemm_tcgen05_stream", "tw_gemm_tcgen05_stream_sm_count")())
-        sms = _stream_sms[0]
+    sms = sms or _stream_sm_count()
     tiles = -(-n // 128)
     best = None
     for want in range(1, 13):

@@ -45,10 +45,18 @@ class SwiGLU(FeedForward):
         act = ws.get("ffn.act", (n, self.intermediate), dt)
         if self.interleaved and ops.small_m_supported(h, self.w_gate_up, n):
             ops.gemm_small_m(act, h, self.w_gate_up, n, silu_mul_pairs=True)
-        elif self.interleaved and ops.stream_product_preferred(h, self.w_gate_up, n):
-            # decode steps of 9 to 64 requests: persistent tcgen05 kernel, weights as the 128-row operand,
-            # SiLU.mul in its epilogue
-            ops.gemm_tcgen05_stream(act, h, self.w_gate_up, n, ctx.status, silu_mul_pairs=True)
+        elif (self.interleaved and ops.stream_product_preferred(h, self.w_gate_up, n)
+              and (ops.stream_whole_k_balanced(2 * self.intermediate) or ops.stream_split_gate_up_enabled())):
+            # decode steps of 9 to 64 requests: persistent tcgen05 kernel, weights as the 128-row operand
+            if ops.stream_whole_k_balanced(2 * self.intermediate):
+                ops.gemm_tcgen05_stream(act, h, self.w_gate_up, n, ctx.status, silu_mul_pairs=True)    # SiLU.mul in its epilogue
+            else:
+                # the row tiles alone would leave half of the blocks with half of the work: slices over k, added
+                # by the SiLU.mul kernel
+                split, kper = ops.stream_split(2 * self.intermediate, self.hidden)
+                slices = ws.get("ffn.gate_up.slices", (split, n, 2 * self.intermediate), torch.float32)
+                ops.gemm_tcgen05_stream(slices if split > 1 else slices[0], h, self.w_gate_up, n, ctx.status, kper=kper)
+                ops.silu_mul(act, ops.SplitSum(slices), n, True)
         elif self.interleaved and ops.pair_product_preferred(h, self.w_gate_up, n):
             # prompt steps: 256 x 256 tiles on pairs of thread blocks (tcgen05.mma.cta_group::2), SiLU.mul in the
             # epilogue, so the [tokens, 2 * intermediate] product never reaches memory

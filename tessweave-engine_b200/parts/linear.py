@@ -72,15 +72,15 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
         # decode steps of 9 to 64 requests, large matrices: the weights stream once through the persistent
         # tcgen05 kernel (csrc/gemm_tcgen05_stream.cu); slices only where the consumer adds them itself
         split, kper = ops.stream_split(n, w.shape[1])
-        if split > 1:
+        if split > 1 and allow_split:
             slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
             ops.gemm_tcgen05_stream(slices, x, w, m, ctx.status, kper=kper)
-            if allow_split:
-                return SplitSum(slices)
-            return SplitSum(slices).dense(dtype, ctx.workspace.get(name, (m, n), dtype))
-        out = ctx.workspace.get(name, (m, n), dtype)
-        ops.gemm_tcgen05_stream(out, x, w, m, ctx.status)
-        return out
+            return SplitSum(slices)
+        if split == 1:
+            out = ctx.workspace.get(name, (m, n), dtype)
+            ops.gemm_tcgen05_stream(out, x, w, m, ctx.status)
+            return out
+        # slices that nobody would add: the library's product below, which reduces its own split inside the kernel
     if x.is_cuda and ops.small_m_supported(x, w, m):
         split, kper = ops.small_m_split(n, w.shape[1], max_slices if allow_split else 12)
         if split > 1 and allow_split:

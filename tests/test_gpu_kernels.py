@@ -656,6 +656,32 @@ def test_gemm_tcgen05_stream_silu_mul(m, n, k):
     assert torch.allclose(out.float(), want, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("nslices", [1, 2, 5, 9])
+@pytest.mark.parametrize("interleaved,inter", [(True, 200), (False, 100), (True, 13824)])
+def test_silu_mul_from_slices(nslices, interleaved, inter):
+    """SiLU.mul straight from the fp32 slices of a gate/up product split over k: the slices are added in the
+    order the other consumers of a split product use, so the result equals densify-then-SiLU.mul bit for bit."""
+    m = 11
+    g = torch.Generator().manual_seed(nslices + inter)
+    slices = dev(torch.randn(nslices, m, 2 * inter, generator=g))
+    out = torch.full((m, inter), float("nan"), device="cuda", dtype=torch.bfloat16)
+    o = ops()
+    o.silu_mul(out, o.SplitSum(slices), m, interleaved)
+    dense = slices.sum(0)
+    if interleaved:
+        y = dense.reshape(m, inter // 8, 2, 8)
+        gate, up = y[:, :, 0].reshape(m, inter), y[:, :, 1].reshape(m, inter)
+    else:
+        gate, up = dense[:, :inter], dense[:, inter:]
+    want = torch.nn.functional.silu(gate) * up
+    assert torch.allclose(out.float(), want, rtol=1e-2, atol=1e-2)
+    # bit for bit against the two-kernel way (slices added by the reduce kernel in fp32, then SiLU.mul in fp32)
+    summed = o.SplitSum(slices).dense(torch.float32)
+    two = torch.empty(m, inter, device="cuda")
+    o.silu_mul(two, summed, m, interleaved)
+    assert torch.equal(out, two.to(torch.bfloat16))
+
+
 def test_gemm_tcgen05_stream_refuses_what_it_cannot_do():
     x = dev(torch.randn(130, 64), torch.bfloat16)
     w = dev(torch.randn(32, 64), torch.bfloat16)

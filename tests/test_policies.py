@@ -75,3 +75,10 @@ def test_stream_split_balances_items_over_the_blocks():
     for n, k in ((100, 64), (5120, 13824), (128, 100000)):
         slices, kper = ops.stream_split(n, k, sms=148)
         assert 1 <= slices <= 12 and kper % 64 == 0 and (slices - 1) * kper < k <= slices * kper
+
+
+def test_fused_gate_up_needs_evenly_busy_blocks():
+    from tessweave_engine_b200.csrc import ops
+    assert ops.stream_whole_k_balanced(37888, sms=148)           # 296 tiles: two per block
+    assert not ops.stream_whole_k_balanced(27648, sms=148)       # 216 tiles: 68 blocks with two, 80 with one
+    assert ops.stream_whole_k_balanced(55296, sms=148)           # 432 tiles: 2.92 of 3
