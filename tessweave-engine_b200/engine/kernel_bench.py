@@ -80,6 +80,8 @@ def kernel_table(cfg, batch: int, context: int, prefill_tokens: int, hbm_gbs: fl
         probe = torch.empty(n, k, device=dev, dtype=bf)
         if fused_silu and m <= ops.SMALL_M_LIMIT:
             fused = "small"
+        elif fused_silu and ops.stream_product_preferred(x, probe, m) and ops.stream_whole_k_balanced(n):
+            fused = "stream"
         elif fused_silu and ops.pair_product_preferred(x, probe, m):
             fused = "pair"
         del probe
@@ -96,6 +98,11 @@ def kernel_table(cfg, batch: int, context: int, prefill_tokens: int, hbm_gbs: fl
             out = torch.empty(m, out_cols, device=dev, dtype=bf)
             calls = [(lambda w=w: ops.gemm_small_m(out, x, w, m, silu_mul_pairs=True)) for w in ws]
             kernel = "gemm_smallm"
+        elif fused == "stream":
+            out_cols = n // 2
+            out = torch.empty(m, out_cols, device=dev, dtype=bf)
+            calls = [(lambda w=w: ops.gemm_tcgen05_stream(out, x, w, m, status, silu_mul_pairs=True)) for w in ws]
+            kernel = "gemm_tcgen05_stream"
         elif fused == "pair":
             out_cols = n // 2
             out = torch.empty(m, out_cols, device=dev, dtype=bf)
@@ -104,6 +111,7 @@ def kernel_table(cfg, batch: int, context: int, prefill_tokens: int, hbm_gbs: fl
         else:
             calls = [(lambda w=w: linear(ctx, "p", x, w, out_dtype=out_dtype, allow_split=True)) for w in ws]
             kernel = ("gemm_smallm" if m <= ops.SMALL_M_LIMIT else
+                      "gemm_tcgen05_stream" if ops.stream_product_preferred(x, ws[0], m) else
                       "gemm_tcgen05 (swap-AB)" if ops.tcgen05_supported(x, ws[0], m) else "library (cuBLAS)")
         us = _graph_us(calls)
         out_bytes = m * out_cols * (4 if out_dtype == torch.float32 else 2)
