@@ -32,7 +32,7 @@ constexpr int EPI_WARPS = 4;
 constexpr int THREADS = 64 + EPI_WARPS * 32;
 constexpr int A_BYTES = BM * BK * 2;
 
-enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_PARTIAL = 2, OUT_SILU_MUL = 3 };
+enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_PARTIAL = 2, OUT_SILU_MUL = 3, OUT_EARLY_DEPENDENTS = 16 /* flag, or-ed in */ };
 
 template <int BN> struct Config {
     static constexpr int B_BYTES = BN * BK * 2 < 1024 ? 1024 : BN * BK * 2;
@@ -61,6 +61,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     TW_TIMELINE_SCOPE(TW_K_OTHER);
     tw_grid_wait();
     TW_TIMELINE_MARK();
+    // a small kernel after this one (a norm) may become resident at once; it waits for the result itself
+    if (out_mode & OUT_EARLY_DEPENDENTS) tw_launch_dependents_now();
+    out_mode &= ~OUT_EARLY_DEPENDENTS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_items = ((n_rows + BM - 1) / BM) * ksplit;
 
@@ -216,12 +219,13 @@ int launch(const void* w, int n, const void* x, int m, int K, int kper, int kspl
 TW_EXPORT int tw_gemm_tcgen05_stream(const void* x, const void* w, int m, int n, int k, int kper, void* out, int out_mode,
                                      int out_stride, int* status, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
-    if (m > 128 || k <= 0 || (k & 7) || kper <= 0 || (kper & 63) || out_mode < 0 || out_mode > 3 ||
+    const int mode = out_mode & ~OUT_EARLY_DEPENDENTS;
+    if (m > 128 || k <= 0 || (k & 7) || kper <= 0 || (kper & 63) || mode < 0 || mode > 3 ||
         (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
         return (int)cudaErrorInvalidValue;
     const int ksplit = (k + kper - 1) / kper;
-    if (ksplit > 1 && out_mode != OUT_PARTIAL) return (int)cudaErrorInvalidValue;
-    if (out_mode == OUT_SILU_MUL && (n & 15)) return (int)cudaErrorInvalidValue;
+    if (ksplit > 1 && mode != OUT_PARTIAL) return (int)cudaErrorInvalidValue;
+    if (mode == OUT_SILU_MUL && (n & 15)) return (int)cudaErrorInvalidValue;
     static int sm_count = 0;
     if (!sm_count) {
         int dev = 0;

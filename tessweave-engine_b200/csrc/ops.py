@@ -683,7 +683,7 @@ def stream_split(n: int, k: int, allow: bool = True, sms: int | None = None) -> 
 
 
 def gemm_tcgen05_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, status: torch.Tensor,
-                        kper: int | None = None, silu_mul_pairs: bool = False) -> None:
+                        kper: int | None = None, silu_mul_pairs: bool = False, early_dependents: bool = False) -> None:
     """out[:m] = x[:m] @ w.T for up to 128 rows on the 5th-generation tensor cores, the weights streamed once by a
     persistent kernel.  ``out`` is bf16 or fp32 [>=m, n]; fp32 slices [slices, m, n] when ``kper`` (a multiple of
     64) is less than k; with ``silu_mul_pairs`` (rows of w in groups of eight gates and their eight ups) bf16
@@ -709,6 +709,8 @@ def gemm_tcgen05_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: 
         _need(out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= m and out.shape[1] == n
               and out.dtype in (torch.bfloat16, torch.float32), "gemm_tcgen05_stream: bad output")
         mode, stride = (0 if out.dtype == torch.bfloat16 else 1), out.stride(0)
+    if early_dependents:
+        mode |= 16          # the kernel after this one may become resident while this one runs
     # the token rows the kernel reads: exactly m (rows beyond are filled with zeros by the copy engine)
     code = _fn("gemm_tcgen05_stream", "tw_gemm_tcgen05_stream")(_ptr(x), _ptr(w), c_int(m), c_int(n), c_int(k), c_int(kper),
                                                                 _ptr(out), c_int(mode), c_int(stride), _ptr(status), _stream())

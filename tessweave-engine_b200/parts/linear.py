@@ -74,11 +74,11 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
         split, kper = ops.stream_split(n, w.shape[1])
         if split > 1 and allow_split:
             slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
-            ops.gemm_tcgen05_stream(slices, x, w, m, ctx.status, kper=kper)
+            ops.gemm_tcgen05_stream(slices, x, w, m, ctx.status, kper=kper, early_dependents=small_consumer)
             return SplitSum(slices)
         if split == 1:
             out = ctx.workspace.get(name, (m, n), dtype)
-            ops.gemm_tcgen05_stream(out, x, w, m, ctx.status)
+            ops.gemm_tcgen05_stream(out, x, w, m, ctx.status, early_dependents=small_consumer)
             return out
         # slices that nobody would add: the library's product below, which reduces its own split inside the kernel
     if x.is_cuda and ops.small_m_supported(x, w, m):
