@@ -608,36 +608,41 @@ def test_gemm_tcgen05_pair_silu_mul(m, n, k):
     assert torch.allclose(out.float(), want, rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("m,n,k,kper", [(9, 300, 200, None), (16, 256, 128, None), (33, 1000, 512, 128),
-                                        (64, 4608, 3584, 896), (100, 520, 3592, None), (128, 130, 8 * 75, 192),
-                                        (20, 40000, 256, None)])
+@pytest.mark.parametrize("m,n,k", [(9, 300, 200), (16, 256, 128), (100, 520, 3592), (20, 40000, 256)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-def test_gemm_tcgen05_stream(m, n, k, kper, out_dtype):
-    """The persistent weight-streaming kernel against fp32 torch: every token tile width (16, 32, 64, 128), rows
-    and k with ragged tails, more work items than blocks (the last shape), whole and as slices over k."""
+def test_gemm_tcgen05_stream(m, n, k, out_dtype):
+    """The persistent weight-streaming kernel against fp32 torch: token tile widths 16, 32 and 128, rows and k
+    with ragged tails, more work items than blocks (the last shape)."""
     g = torch.Generator().manual_seed(m + n)
     x = dev(torch.randn(m + 3, k, generator=g) * 0.5, torch.bfloat16)          # rows beyond m must not be read into the result
     w = dev(torch.randn(n, k, generator=g) * 0.05, torch.bfloat16)
     want = x[:m].float() @ w.float().t()
     st = status()
-    if kper is not None:
-        if out_dtype == torch.bfloat16:
-            pytest.skip("slices are fp32")
-        split = -(-k // kper)
-        slices = torch.full((split, m, n), float("nan"), device="cuda")
-        ops().gemm_tcgen05_stream(slices, x, w, m, st, kper=kper)
-        assert int(st) == 0
-        assert torch.allclose(slices.sum(0), want, atol=2e-3 * max(1.0, float(want.abs().max())), rtol=0)
-        for i in range(split):          # each slice is the product over its own values of k
-            part = x[:m, i * kper:(i + 1) * kper].float() @ w[:, i * kper:(i + 1) * kper].float().t()
-            assert torch.allclose(slices[i], part, atol=2e-3 * max(1.0, float(part.abs().max())), rtol=0)
-        return
     out = torch.full((m + 1, n), float("nan"), device="cuda", dtype=out_dtype)
     ops().gemm_tcgen05_stream(out, x, w, m, st)
     assert int(st) == 0
     tol = dict(rtol=2e-2, atol=2e-2) if out_dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-3)
     assert torch.allclose(out[:m].float(), want, **tol)
     assert bool(torch.isnan(out[m].float()).all()), "a row beyond m was written"
+
+
+@pytest.mark.parametrize("m,n,k,kper", [(33, 1000, 512, 128), (64, 4608, 3584, 896), (128, 130, 8 * 75, 192)])
+def test_gemm_tcgen05_stream_slices(m, n, k, kper):
+    """The same as fp32 slices over k (token tile widths 64 and 128 among them, a last slice shorter than the
+    others): each slice is the product over its own values of k."""
+    g = torch.Generator().manual_seed(m + n)
+    x = dev(torch.randn(m + 3, k, generator=g) * 0.5, torch.bfloat16)
+    w = dev(torch.randn(n, k, generator=g) * 0.05, torch.bfloat16)
+    want = x[:m].float() @ w.float().t()
+    st = status()
+    split = -(-k // kper)
+    slices = torch.full((split, m, n), float("nan"), device="cuda")
+    ops().gemm_tcgen05_stream(slices, x, w, m, st, kper=kper)
+    assert int(st) == 0
+    assert torch.allclose(slices.sum(0), want, atol=2e-3 * max(1.0, float(want.abs().max())), rtol=0)
+    for i in range(split):
+        part = x[:m, i * kper:(i + 1) * kper].float() @ w[:, i * kper:(i + 1) * kper].float().t()
+        assert torch.allclose(slices[i], part, atol=2e-3 * max(1.0, float(part.abs().max())), rtol=0)
 
 
 @pytest.mark.parametrize("m,n,k", [(17, 48, 64), (24, 37888, 512), (64, 1040, 3584), (9, 16, 72)])
