@@ -305,7 +305,12 @@ def decode_splits(n_seqs: int, n_kv_heads: int, group: int, max_kv_len: int) -> 
     tiles = max(1, -(-max_kv_len // 64))
     groups = max(1, n_seqs * n_kv_heads * head_tiles)
     # the kernel fits four blocks on an SM; aim at a little under one full wave of blocks
-    target = max(1, (7 * _SM_COUNT // 2 + groups // 2) // groups)        # rounded: 1.9 blocks' worth of room is two slices
+    room = 7 * _SM_COUNT // 2
+    target = max(1, (room + groups // 2) // groups)        # rounded: 1.9 blocks' worth of room is two slices
+    if target > 4 and target * groups > room:
+        # clusters of five and more blocks are no longer all placed at once when the launch has more than 3.5 blocks
+        # per SM (batch 12, 4 key/value heads, a whole decode step: 3.81 ms with 10 slices, 4.21 with 11)
+        target = max(4, room // groups)
     nsplit = max(1, min(tiles, target, 128, DECODE_SCRATCH_UNITS // max(1, n_seqs)))
     if 14 < nsplit <= 16 and groups > 8 and max_kv_len < 8192:
         nsplit = 14

@@ -82,3 +82,19 @@ def test_fused_gate_up_needs_evenly_busy_blocks():
     assert ops.stream_whole_k_balanced(37888, sms=148)           # 296 tiles: two per block
     assert not ops.stream_whole_k_balanced(27648, sms=148)       # 216 tiles: 68 blocks with two, 80 with one
     assert ops.stream_whole_k_balanced(55296, sms=148)           # 432 tiles: 2.92 of 3
+
+
+def test_decode_slices_leave_room_for_their_clusters():
+    """Launches whose slices merge in clusters of five blocks and more stay under 3.5 blocks per SM: with more, some
+    clusters start a wave late (batch 12 with 4 key/value heads took 11 slices = 528 blocks before, 10 now)."""
+    from tessweave_engine_b200.csrc import ops
+    room = 7 * ops._SM_COUNT // 2
+    for batch in range(1, 65):
+        for kv_heads, group, keys in ((4, 7, 4096), (8, 5, 1024), (2, 7, 16384)):
+            n = ops.decode_splits(batch, kv_heads, group, keys)
+            assert n >= 1
+            if n > 4:
+                assert n * batch * kv_heads * ((group + 7) // 8) <= room, (batch, kv_heads, group, keys, n)
+    assert ops.decode_splits(12, 4, 7, 4096) == 10
+    assert ops.decode_splits(8, 4, 7, 4096) == 13
+    assert ops.decode_splits(16, 4, 7, 4096) == 8
