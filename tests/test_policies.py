@@ -96,6 +96,7 @@ def test_decode_slices_leave_room_for_their_clusters():
             if n > 4:
                 assert n * batch * kv_heads * ((group + 7) // 8) <= room, (batch, kv_heads, group, keys, n)
     assert ops.decode_splits(12, 4, 7, 4096) == 10
+    assert ops.decode_splits(8, 4, 7, 16384) <= 14 and ops.decode_splits(8, 4, 7, 32768) <= 14
     assert ops.decode_splits(44, 4, 7, 4096) == 3 and ops.decode_splits(48, 4, 7, 4096) == 2
     assert ops.decode_splits(8, 4, 7, 4096) == 13
     assert ops.decode_splits(16, 4, 7, 4096) == 8
