@@ -582,18 +582,35 @@ def gemm_tcgen05(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, st
     _check(code, "gemm_tcgen05")
 
 
-PAIR_MIN_M = 512           # rows from which the fused gate/up product runs on block pairs
+PAIR_MIN_M = 768           # rows from which the fused gate/up product may run on block pairs
+
+
+def pair_tiles_efficiency(m: int, n: int, sms: int | None = None) -> float:
+    """The share of the block pairs' time that is useful work: rows padded to tiles of 256, and the 256 x 256 tiles
+    dealt to sms / 2 pairs in whole rounds."""
+    pairs = max(1, (sms or _SM_COUNT) // 2)
+    tiles_m, tiles_n = -(-m // 256), -(-n // 256)
+    tiles = tiles_m * tiles_n
+    return (m / (tiles_m * 256)) * (tiles / pairs) / -(-tiles // pairs)
 
 
 def pair_product_preferred(x: torch.Tensor, w: torch.Tensor, m: int) -> bool:
-    """Whether the gate/up product with the SiLU.mul epilogue runs on ``gemm_tcgen05_pair``: measured on
-    B200 at 2,048 x 37,888 x 3,584 it takes 387 us against 347 + 49 us for the library's product and
-    the separate SiLU.mul kernel.  TESSWEAVE_PAIR_GEMM=0 keeps the library."""
+    """Whether the gate/up product with the SiLU.mul epilogue runs on ``gemm_tcgen05_pair``.  Measured on B200
+    against the library's product plus the separate SiLU.mul kernel: at 37,888 x 3,584 the pairs take 155.7 /
+    200.5 / 280.4 / 387 us at 768 / 1,024 / 1,536 / 2,048 rows against 156.2 / 204.8 / 298.0 / 396, but 146.8
+    against 124.0 at 544 rows (padded to 768) and 109.6 against 108.1 at 512; at 27,648 x 5,120 they lose where
+    the tiles do not fill whole rounds of pairs (1,280 rows: 271.9 against 260.7).  So: from 768 rows, and only
+    where padding and rounds leave at least 93 % of the pairs' time useful.  TESSWEAVE_PAIR_GEMM=0 keeps the library,
+    =force takes the pairs for every shape beyond 64 rows."""
     import os
-    if os.environ.get("TESSWEAVE_PAIR_GEMM", "1") == "0":
+    choice = os.environ.get("TESSWEAVE_PAIR_GEMM", "1")
+    if choice == "0":
         return False
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and m >= PAIR_MIN_M and w.shape[0] % 16 == 0
-            and w.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous())
+    takes = (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[0] % 16 == 0
+             and w.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous())
+    if choice == "force":          # every shape the kernel takes (tests run whole models through it this way)
+        return takes and m > 64
+    return takes and m >= PAIR_MIN_M and pair_tiles_efficiency(m, w.shape[0]) >= 0.93
 
 
 def gemm_tcgen05_pair(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, status: torch.Tensor,

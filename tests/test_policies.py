@@ -100,3 +100,11 @@ def test_decode_slices_leave_room_for_their_clusters():
     assert ops.decode_splits(44, 4, 7, 4096) == 3 and ops.decode_splits(48, 4, 7, 4096) == 2
     assert ops.decode_splits(8, 4, 7, 4096) == 13
     assert ops.decode_splits(16, 4, 7, 4096) == 8
+
+
+def test_pair_product_only_where_its_tiles_fill_the_pairs():
+    from tessweave_engine_b200.csrc import ops
+    eff = lambda m, n: ops.pair_tiles_efficiency(m, n, sms=148)
+    assert eff(2048, 37888) == 1.0 and eff(768, 37888) == 1.0
+    assert eff(544, 37888) < 0.75                       # padded to 768 rows
+    assert eff(1280, 27648) < 0.93 <= eff(1536, 27648)  # 540 tiles: 7.3 rounds of 74 pairs; 648 tiles: 8.76
