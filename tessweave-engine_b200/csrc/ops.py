@@ -316,10 +316,13 @@ def decode_splits(n_seqs: int, n_kv_heads: int, group: int, max_kv_len: int) -> 
         # but not to the last slot (batch 48: 576 blocks, 6.56 ms against 5.59 with 2)
         target = max(1, (15 * _SM_COUNT // 4) // groups)
     nsplit = max(1, min(tiles, target, 128, DECODE_SCRATCH_UNITS // max(1, n_seqs)))
+    if 16 < nsplit <= 64 and max_kv_len <= 8192:
+        # up to 8,192 keys the merge inside a cluster beats more slices merged through scratch memory (4,096 keys:
+        # batch 3 / 4 / 6 steps take 3.24 / 3.26 / 3.37 ms with 14-16 slices against 3.30 / 3.33 / 3.52 with 21-32);
+        # with longer contexts and few requests more slices win (16,384 keys, batch 2: 3.62 ms with 64, 3.83 with 16)
+        nsplit = 16
     if 14 < nsplit <= 16 and groups > 8:
         nsplit = 14          # at every context length: 16,384 keys 4.53 ms with 14 slices, 5.20 with 16; 32,768 keys 5.85 and 7.05
-    elif 16 < nsplit <= 64 and groups <= 8 and max_kv_len <= 8192:
-        nsplit = 16
     # the kernel cuts the keys into slices of a multiple of 64 keys: no slice without keys
     per = -(-(-(-max_kv_len // nsplit)) // 64) * 64
     return max(1, -(-max_kv_len // per))
