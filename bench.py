@@ -164,11 +164,8 @@ def decode_run(model, cfg, batch: int, context: int, steps: int, warmup: int, gr
 def decode_bytes(model, cfg, batch: int, context: float) -> float:
     """Bytes a decode step has to read: every weight it uses once (all blocks, final norm,
     output matrix; of the embedding only ``batch`` rows) and the cache of the live requests."""
-    weights = model.weight_bytes() - model.embedding.numel() * model.embedding.element_size() \
-        + batch * cfg.hidden_size * 2
-    if model.spec.tie_word_embeddings:
-        weights += model.embedding.numel() * model.embedding.element_size()
-    return weights + batch * context * cfg.kv_bytes_per_token(2)
+    element = 2 if model.runtime.dtype == __import__("torch").bfloat16 else 4
+    return model.step_weight_bytes(batch) + batch * context * model.cache_bytes_per_token(element)
 
 
 def prefill_run(model, cfg, tokens: int, reps: int, warmup: int):

@@ -10,7 +10,7 @@ this engine carries one architecture.
 from __future__ import annotations
 
 import json
-from dataclasses import dataclass, replace, asdict
+from dataclasses import dataclass, replace
 from pathlib import Path
 
 
@@ -146,10 +146,3 @@ class Qwen2Config:
         if self.eos_token_ids:
             d["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) > 1 else self.eos_token_ids[0]
         return d
-
-    def kv_bytes_per_token(self, element_bytes: int) -> int:
-        """K and V of every layer for one token (flow_engine/config.py:64-65)."""
-        return 2 * self.num_hidden_layers * self.num_key_value_heads * self.head_dim * element_bytes
-
-    def as_dict(self) -> dict:
-        return asdict(self)

@@ -207,10 +207,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, (D <= 128 ? 4 : 2))
 attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
                    const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                    const int* __restrict__ seq_kv_len, const int* __restrict__ seq_slot,
-                   const int* __restrict__ block_table, int table_stride, const bf16* __restrict__ k_cache,
-                   const bf16* __restrict__ v_cache, int Hq, int Hkv, int page_size, int num_pages, int window,
+                   const int* __restrict__ block_table, int table_stride, const bf16* k_cache,
+                   const bf16* v_cache, int Hq, int Hkv, int page_size, int num_pages, int window,
                    float scale_log2e, int nsplit, float* __restrict__ partial_o, float* __restrict__ partial_ml,
                    int* __restrict__ counters, int* status, const FusedQkv fq) {
+    // k_cache and v_cache carry no __restrict__: with FUSED the block that holds the newest position writes that
+    // position's key and value through fq.k_cache / fq.v_cache, which are the same memory, and reads them back
+    // below.  The keys are read with ld.global.cg (L2, coherent) and the values with cp.async.cg, never through
+    // the non-coherent path, which may hold a line from before the write.
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_is_last;
     __shared__ float s_row_max[DEC_HEADS];
@@ -343,11 +347,11 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         const long long oa = t < ntiles ? offs[g] : -1, ob = t < ntiles ? offs[g + 8] : -1;
 #pragma unroll
         for (int jb = 0; jb < DB32; ++jb) {
-            ka.blk[jb] = oa >= 0 ? *reinterpret_cast<const uint4*>(k_cache + oa + 32 * jb + 8 * c) : make_uint4(0u, 0u, 0u, 0u);
-            kb_.blk[jb] = ob >= 0 ? *reinterpret_cast<const uint4*>(k_cache + ob + 32 * jb + 8 * c) : make_uint4(0u, 0u, 0u, 0u);
+            ka.blk[jb] = oa >= 0 ? __ldcg(reinterpret_cast<const uint4*>(k_cache + oa + 32 * jb + 8 * c)) : make_uint4(0u, 0u, 0u, 0u);
+            kb_.blk[jb] = ob >= 0 ? __ldcg(reinterpret_cast<const uint4*>(k_cache + ob + 32 * jb + 8 * c)) : make_uint4(0u, 0u, 0u, 0u);
         }
-        ka.tail = (DTAIL16 && oa >= 0) ? *reinterpret_cast<const uint2*>(k_cache + oa + 32 * DB32 + 4 * c) : make_uint2(0u, 0u);
-        kb_.tail = (DTAIL16 && ob >= 0) ? *reinterpret_cast<const uint2*>(k_cache + ob + 32 * DB32 + 4 * c) : make_uint2(0u, 0u);
+        ka.tail = (DTAIL16 && oa >= 0) ? __ldcg(reinterpret_cast<const uint2*>(k_cache + oa + 32 * DB32 + 4 * c)) : make_uint2(0u, 0u);
+        kb_.tail = (DTAIL16 && ob >= 0) ? __ldcg(reinterpret_cast<const uint2*>(k_cache + ob + 32 * DB32 + 4 * c)) : make_uint2(0u, 0u);
     };
 
     KFrag ka_next, kb_next;
@@ -940,6 +944,21 @@ TW_EXPORT long long tw_attn_decode_scratch_floats(int n_seqs, int Hq, int nsplit
     return (long long)n_seqs * Hq * nsplit * (D + 2);
 }
 
+// Most slices a request's keys may be cut into.  The merge through scratch memory keeps two floats per
+// (head, slice) in the block's dynamic shared memory; beyond this limit they would not fit at every head size.
+constexpr int DEC_MAX_SPLITS = 128;
+static_assert(2 * DEC_HEADS * DEC_MAX_SPLITS * 4 <= DEC_SMEM, "the merge factors of the most slices must fit the block's shared memory");
+
+TW_EXPORT int tw_attn_decode_max_splits() { return DEC_MAX_SPLITS; }
+
+// What every decode entry point refuses before it launches: more slices than the merge has room for, and a
+// query that the kernel's 16-byte loads cannot read.
+static int decode_refuses(int nsplit, const void* q, int q_stride) {
+    if (nsplit < 1 || nsplit > DEC_MAX_SPLITS) return (int)cudaErrorInvalidValue;
+    if (q && (((uintptr_t)q & 15) || (q_stride & 7))) return (int)cudaErrorMisalignedAddress;
+    return 0;
+}
+
 TW_EXPORT int tw_attn_decode(void* out, int out_stride, const void* q, int q_stride, const int* seq_q_start,
                              const int* seq_q_len, const int* seq_kv_len, const int* seq_slot, const int* block_table,
                              int table_stride, const void* k_cache, const void* v_cache, int n_seqs, int Hq, int Hkv,
@@ -947,6 +966,7 @@ TW_EXPORT int tw_attn_decode(void* out, int out_stride, const void* q, int q_str
                              float* scratch, int* counters, int* status, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv || nsplit < 1 || (nsplit > 1 && (!scratch || !counters))) return (int)cudaErrorInvalidValue;
+    if (int r = decode_refuses(nsplit, q, q_stride)) return r;
     // the merge reads the partial results 16 bytes at a time and writes 8 bytes of the result at a time
     if (((uintptr_t)out & 7) || (out_stride & 3) || ((uintptr_t)scratch & 15)) return (int)cudaErrorMisalignedAddress;
     if (int e = set_attrs()) return e;
@@ -983,6 +1003,7 @@ TW_EXPORT int tw_attn_decode_fused(void* out, int out_stride, const float* parti
     if (Hkv <= 0 || Hq % Hkv || nsplit < 1 || (nsplit > 1 && (!scratch || !counters)) || (!partial && !dense) ||
         (partial && nslices < 1))
         return (int)cudaErrorInvalidValue;
+    if (int r = decode_refuses(nsplit, nullptr, 0)) return r;
     if (((uintptr_t)out & 7) || (out_stride & 3) || ((uintptr_t)scratch & 15)) return (int)cudaErrorMisalignedAddress;
     if (int e = set_attrs()) return e;
     const int G = Hq / Hkv, htiles = (G + DEC_HEADS - 1) / DEC_HEADS;
@@ -1052,6 +1073,12 @@ TW_EXPORT int tw_attn_decode_static(void* out, int out_stride, const void* q, in
     if (n_seqs <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv || nsplit < 1) return (int)cudaErrorInvalidValue;
     if (((uintptr_t)out & 7) || (out_stride & 3)) return (int)cudaErrorMisalignedAddress;
+    if (int r = decode_refuses(nsplit, q, q_stride)) {
+        snprintf(g_static_error, sizeof(g_static_error),
+                 "tw_attn_decode_static: at most %d slices; q must be 16-byte aligned with a row stride that is a multiple of 8",
+                 DEC_MAX_SPLITS);
+        return r;
+    }
     const int G = Hq / Hkv, htiles = (G + DEC_HEADS - 1) / DEC_HEADS;
     const size_t partial_bytes = sizeof(float) * (size_t)n_seqs * Hq * nsplit * (D + 2);
     const size_t counter_bytes = sizeof(int) * (size_t)n_seqs * Hkv * htiles;

@@ -26,6 +26,9 @@
 //     call; nothing else needs a defined start.  Two calls that run on the GPU at the same
 //     time (different streams, or different threads without ordering) race on the array and
 //     give wrong results: order them on one stream or with events.
+//   * nsplit is at most 128 (tw_attn_decode_max_splits()), q must be 16-byte aligned and q_stride a
+//     multiple of 8 elements: the kernel reads the query 16 bytes at a time.  Other values are refused
+//     with cudaErrorInvalidValue / cudaErrorMisalignedAddress before anything is launched.
 //   * Inputs and outputs are passed exactly as to tw_attn_decode (see attention_bf16.cu);
 //     only `scratch` and `counters` are gone.  The head size is the one the library was
 //     compiled for (tw_attn_head_dim()).

@@ -258,6 +258,7 @@ def sample(out: torch.Tensor, logits: torch.Tensor, n_rows: int, temperature: to
 # ---------------------------------------------------------------------------
 # bf16 tensor-core attention (one compiled library per head size)
 # ---------------------------------------------------------------------------
+DECODE_MAX_SPLITS = 128          # most slices of a request's keys (the merge keeps two floats per head and slice in shared memory)
 DECODE_SCRATCH_UNITS = 1024      # most (request, split) pairs whose partial results fit the scratch buffer
 _SM_COUNT = 148
 
@@ -360,6 +361,8 @@ def attention_decode(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block
     _cuda(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, scratch, counters, status)
     _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim)
     _need(out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0, "attention_decode: output rows must be 8-byte aligned")
+    _need(q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0, "attention_decode: rows of q must be 16-byte aligned")
+    _need(1 <= nsplit <= DECODE_MAX_SPLITS, f"attention_decode: 1 to {DECODE_MAX_SPLITS} slices, not {nsplit}")
     if nsplit > 1:
         _need(scratch is not None and scratch.dtype == torch.float32 and scratch.data_ptr() % 16 == 0
               and scratch.numel() >= n_seqs * n_q_heads * nsplit * (head_dim + 2), "attention_decode: scratch too small")
@@ -425,6 +428,7 @@ def attention_decode_fused(out, source, bias, inv_freq, write_cache, seq_q_start
     _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == width), "attention_decode_fused: bias must be fp32")
     _need(inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2),
           "attention_decode_fused: inv_freq must be fp32 [D/2]")
+    _need(1 <= nsplit <= DECODE_MAX_SPLITS, f"attention_decode_fused: 1 to {DECODE_MAX_SPLITS} slices, not {nsplit}")
     if nsplit > 1:
         _need(scratch is not None and scratch.dtype == torch.float32 and scratch.data_ptr() % 16 == 0
               and scratch.numel() >= n_seqs * n_q_heads * nsplit * (head_dim + 2), "attention_decode: scratch too small")
@@ -531,60 +535,8 @@ def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kp
 
 
 # ---------------------------------------------------------------------------
-# matrix products on tcgen05 tensor cores fed by TMA
+# matrix products of prompt steps on pairs of thread blocks
 # ---------------------------------------------------------------------------
-TCGEN05_MIN_M, TCGEN05_MAX_M = 9, 32     # rows the swap-AB tcgen05 kernel is meant for (see tcgen05_supported)
-
-
-def tcgen05_supported(x: torch.Tensor, w: torch.Tensor, m: int) -> bool:
-    """Whether a product with ``m`` rows goes to the swap-AB tcgen05 kernel.  Off unless TESSWEAVE_SWAP_AB=1:
-    measured on B200 the library is faster for 9..32 rows (a decode step at batch 16 / 32 of the 7B sizes
-    4.16 / 4.86 ms against 4.21 / 5.02; at the 14B sizes 15 / 13 / 47 / 27 us against 23 / 19 / 58 / 42 for
-    the four products of a layer), so these steps take the library's products."""
-    import os
-    if os.environ.get("TESSWEAVE_SWAP_AB", "0") != "1":
-        return False
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and TCGEN05_MIN_M <= m <= TCGEN05_MAX_M
-            and w.shape[1] % 8 == 0 and w.is_contiguous() and x.is_contiguous()
-            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-
-
-def tcgen05_split(n: int, k: int) -> tuple[int, int]:
-    """(slices, k per slice) for the swap-AB use: about one block per SM, slices multiples of 64 wide."""
-    tiles = -(-n // 128)
-    want = max(1, min(16, round(_SM_COUNT / tiles))) if tiles < _SM_COUNT else 1
-    kper = max(256, -(-(-(-k // want)) // 64) * 64)
-    kper = min(kper, -(-k // 64) * 64)
-    return -(-k // kper), kper
-
-
-def gemm_tcgen05(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, status: torch.Tensor,
-                 kper: int | None = None, swap: bool | None = None) -> None:
-    """out[:m] = x[:m] @ w.T on the tcgen05 tensor cores (bf16 operands, fp32 accumulation in TMEM).
-    ``swap`` (default: m <= 64) makes the weights the 128-row operand; k may then be split into
-    slices of ``kper`` and ``out`` is fp32 [slices, m, n]."""
-    _cuda(out, x, w, status)
-    n, k = w.shape
-    swap = (m <= 64) if swap is None else swap
-    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x.is_contiguous()
-          and x.shape[1] == k and k % 8 == 0, "gemm_tcgen05: contiguous bf16 operands, k a multiple of 8")
-    _need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0, "gemm_tcgen05: operands must be 16-byte aligned")
-    kper = kper or -(-k // 64) * 64
-    split = -(-k // kper)
-    if split > 1:
-        _need(out.dtype == torch.float32 and out.dim() == 3 and tuple(out.shape) == (split, m, n) and out.is_contiguous(),
-              "gemm_tcgen05: split output must be fp32 [slices, m, n]")
-        mode, stride = 2, n
-    else:
-        _need(out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= m and out.shape[1] == n
-              and out.dtype in (torch.bfloat16, torch.float32), "gemm_tcgen05: bad output")
-        mode, stride = (0 if out.dtype == torch.bfloat16 else 1), out.stride(0)
-    code = _fn("gemm_tcgen05", "tw_gemm_tcgen05")(_ptr(x), _ptr(w), c_int(m), c_int(n), c_int(k), c_int(kper), _ptr(out),
-                                                  c_int(mode), c_int(stride), c_int(1 if swap else 0), _ptr(status),
-                                                  _stream())
-    _check(code, "gemm_tcgen05")
-
-
 PAIR_MIN_M = 768           # rows from which the fused gate/up product may run on block pairs
 
 

@@ -21,7 +21,7 @@ from ..cache.manager import CacheManager
 from ..csrc import ops
 from ..models.model import Model
 from ..parts.base import StepContext, Workspace
-from ..parts.linear import configure_matmul_precision
+from ..parts.linear import configure_matmul_precision, verify_true_fp32
 
 
 @dataclass
@@ -50,6 +50,8 @@ class ModelRunner:
         if model.runtime.device.type != "cuda":
             raise RuntimeError("the step function runs on a CUDA device only; there is no CPU path")
         configure_matmul_precision()
+        if model.runtime.dtype == torch.float32:
+            verify_true_fp32(model.runtime.device)
         self.model, self.cache = model, cache
         self.device = model.runtime.device
         self.max_tokens = int(max_step_tokens)
@@ -90,9 +92,12 @@ class ModelRunner:
         self.launches = 0
 
     # ------------------------------------------------------------------ batch building
-    def _stage(self, entries: list[StepEntry], pad_to: int = 0, all_rows: bool = False) -> tuple[StepContext, int]:
+    def _stage(self, entries: list[StepEntry], pad_to: int = 0, all_rows: bool = False,
+               device_refs: bool = False) -> tuple[StepContext, int]:
         """Fill the staging buffer for ``entries`` and copy it to the device.  ``pad_to`` pads the
-        batch with rows that belong to no request; ``all_rows`` asks for the logits of every row."""
+        batch with rows that belong to no request; ``all_rows`` asks for the logits of every row.
+        ``device_refs``: a token id -(i + 1) names the i-th token the step before chose (``launch``
+        says so for a step it launches behind another); otherwise a negative id is refused here."""
         h = self._n
         self._staged.synchronize()       # the previous step's copy has read the pinned buffer
         n = sum(len(e.tokens) for e in entries)
@@ -126,6 +131,9 @@ class ModelRunner:
         if m > self.max_rows:
             raise ValueError(f"{m} wanted rows exceed the runner's limit of {self.max_rows}")
         h["token_ids"][:n] = ids
+        lowest = int(h["token_ids"][:n].min())
+        if lowest < (-self.max_rows if device_refs else 0):
+            raise ValueError(f"token id {lowest} is negative" + (" and names no token of the step before" if device_refs else ""))
         h["positions"][:n] = pos
         h["seq_of_token"][:n] = sot
         if rows_total > n:
@@ -153,7 +161,7 @@ class ModelRunner:
             seq_kv_len=d["seq_kv_len"][:seqs_total], status=self.status,
             host_slot=slot, host_q_start=qs, host_q_len=ql, host_kv_len=kl,
             max_q_len=max(ql), max_kv_len=max(kl), decode_only=all(t == 1 for t in ql), fixed_shape=bool(pad_to),
-            device_tokens=self.sampled)
+            device_tokens=self.sampled if (device_refs or pad_to) else None)
         return ctx, m
 
     def _padding_context(self, rows: int, logit_rows: int) -> StepContext:
@@ -181,14 +189,14 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ the step
     @torch.inference_mode()
-    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+    def step(self, entries: list[StepEntry], device_refs: bool = False) -> torch.Tensor:
         """Run the tokens of ``entries`` and return fp32 logits ``[wanted rows, vocab]`` on the
         device, in the order of the entries and of their ``want`` lists."""
         if self.use_graphs and entries and all(len(e.tokens) == 1 for e in entries):
             bucket = next((b for b in self.buckets if len(entries) <= b), None)
             if bucket is not None:
-                return self._graph_step(entries, bucket)
-        ctx, m = self._stage(entries)
+                return self._graph_step(entries, bucket, device_refs)
+        ctx, m = self._stage(entries, device_refs=device_refs)
         logits = self.workspace.get("runner.logits", (max(m, 1), self.vocab), torch.float32)
         self.model.forward(ctx, self.cache.views(), self._d["logit_rows"], m, logits)
         return logits[:m]
@@ -230,7 +238,7 @@ class ModelRunner:
         self._graphs[bucket] = (graph, logits)
         return self._graphs[bucket]
 
-    def _graph_step(self, entries: list[StepEntry], bucket: int) -> torch.Tensor:
+    def _graph_step(self, entries: list[StepEntry], bucket: int, device_refs: bool = False) -> torch.Tensor:
         if not self._graphs:
             # capture every bucket at the first decode step, so that a batch that shrinks or grows
             # later does not pay for a capture in the middle of generation
@@ -242,7 +250,8 @@ class ModelRunner:
             e_want = e.want
             if e_want and e_want != [0]:
                 raise ValueError("a single-token entry can only want place 0")
-        self._stage([StepEntry(e.slot, e.tokens, e.start, []) for e in entries], pad_to=bucket, all_rows=True)
+        self._stage([StepEntry(e.slot, e.tokens, e.start, []) for e in entries], pad_to=bucket, all_rows=True,
+                    device_refs=device_refs)
         graph.replay()
         if wanted == list(range(len(wanted))):
             return logits[:len(wanted)]
@@ -277,13 +286,14 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ steps in flight
     @torch.inference_mode()
-    def launch(self, entries: list[StepEntry], temperature: list[float], seed: list[int], counter: list[int]):
+    def launch(self, entries: list[StepEntry], temperature: list[float], seed: list[int], counter: list[int],
+               device_refs: bool = False):
         """Launch a whole step -- forward, token selection, copy of the chosen ids to the host --
-        and return without waiting.  A token id -(i + 1) in an entry stands for the i-th token
-        chosen by the step launched just before, which is still on the device; so the next
+        and return without waiting.  With ``device_refs`` a token id -(i + 1) in an entry stands for the
+        i-th token chosen by the step launched just before, which is still on the device; so the next
         step can be launched before this one's tokens have reached the host.  ``finish`` waits."""
         self.stage_sampling(temperature, seed, counter)
-        logits = self.step(entries)
+        logits = self.step(entries, device_refs)
         m = logits.shape[0]
         host = self._sampled_hosts[self._launched % 2]
         self._launched += 1

@@ -31,8 +31,10 @@ def qwen2_spec(cfg: Qwen2Config) -> ModelSpec:
         architecture=cfg.architecture, vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
         layers=tuple(LayerSpec(block, f"model.layers.{i}") for i in range(n)),
         schedule=tuple(ScheduleEntry(i) for i in range(n)),
-        final_norm=norm, final_norm_prefix="model.norm", embedding_name="model.embed_tokens.weight",
-        head_name="lm_head.weight", tie_word_embeddings=cfg.tie_word_embeddings,
+        embedding=PartSpec("token_embedding", {"vocab": cfg.vocab_size, "hidden": cfg.hidden_size}),
+        embedding_prefix="model.embed_tokens", final_norm=norm, final_norm_prefix="model.norm",
+        head=PartSpec("linear_head", {"vocab": cfg.vocab_size, "hidden": cfg.hidden_size}), head_prefix="lm_head",
+        tie_word_embeddings=cfg.tie_word_embeddings,
         max_position_embeddings=cfg.max_position_embeddings, eos_token_ids=cfg.eos_token_ids,
         init_std=cfg.initializer_range, ignored_suffixes=("rotary_emb.inv_freq",))
 

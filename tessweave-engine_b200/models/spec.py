@@ -28,11 +28,13 @@ class ModelSpec:
     hidden_size: int
     layers: tuple[LayerSpec, ...]
     schedule: tuple[ScheduleEntry, ...]      # the order in which layers run; a layer may appear twice
+    embedding: PartSpec
+    embedding_prefix: str                     # its weights are "<prefix>.<name the part declares>"
     final_norm: PartSpec
     final_norm_prefix: str
-    embedding_name: str
-    head_name: str                            # name of the output matrix in an untied checkpoint
-    tie_word_embeddings: bool
+    head: PartSpec
+    head_prefix: str
+    tie_word_embeddings: bool                 # the head shares the embedding's matrix; the checkpoint has no tensor for it
     max_position_embeddings: int
     eos_token_ids: tuple[int, ...] = ()
     init_std: float = 0.02

@@ -1,10 +1,10 @@
-"""Parts a model is put together from: norms, position encodings, mixers,
-feed-forwards and their arrangement in a block."""
-from .base import (Block, FeedForward, FixedState, Mixer, Norm, PagedKV, PagedView, Part, PartSpec,
-                   PositionEncoding, ResidualStream, Runtime, StateView, StepContext, WeightDecl, Workspace,
-                   build_part, register_part, registered)
-from . import norms, positions, attention, feedforward, block  # noqa: F401  (register the built-in kinds)
+"""Parts a model is put together from: embeddings, norms, position encodings, mixers,
+feed-forwards, their arrangement in a block, and output heads."""
+from .base import (Block, Embedding, FeedForward, FixedState, Head, Mixer, Norm, PagedKV, PagedView, Part, PartSpec,
+                   PositionEncoding, ResidualStream, Runtime, SplitSum, StateView, StepContext, WeightDecl, Workspace,
+                   build_part, dense_delta, register_part, registered)
+from . import embedding, norms, positions, attention, feedforward, block, heads  # noqa: F401  (register the built-in kinds)
 
-__all__ = ["Block", "FeedForward", "FixedState", "Mixer", "Norm", "PagedKV", "PagedView", "Part", "PartSpec",
-           "PositionEncoding", "ResidualStream", "Runtime", "StateView", "StepContext", "WeightDecl", "Workspace",
-           "build_part", "register_part", "registered"]
+__all__ = ["Block", "Embedding", "FeedForward", "FixedState", "Head", "Mixer", "Norm", "PagedKV", "PagedView", "Part",
+           "PartSpec", "PositionEncoding", "ResidualStream", "Runtime", "SplitSum", "StateView", "StepContext",
+           "WeightDecl", "Workspace", "build_part", "dense_delta", "register_part", "registered"]

@@ -43,7 +43,7 @@ class GQAAttention(Mixer):
         self.qkv_width = self.q_size + 2 * self.kv_size
         self.position = build_part("position", position, runtime)
         self.w_qkv = runtime.empty(self.qkv_width, hidden)
-        self.b_qkv = torch.empty(self.qkv_width, dtype=torch.float32, device=runtime.device) if qkv_bias else None
+        self.b_qkv = runtime.empty(self.qkv_width, dtype=torch.float32) if qkv_bias else None
         self.w_o = runtime.empty(hidden, self.q_size)
 
     def weights(self) -> list[WeightDecl]:
@@ -74,7 +74,7 @@ class GQAAttention(Mixer):
         if fused_decode:
             # decode-only step: the attention kernel adds the bias, rotates, writes the new key and value and attends
             self._decode(ctx, out, None, cache, fused=(source if source is not None else qkv, table, write_cache))
-            return linear(ctx, "mixer.delta", out, self.w_o, allow_split=ctx.split_ok, small_consumer=True)
+            return linear(ctx, "mixer.delta", out, self.w_o, allow_split=True, small_consumer=True)
         if table is None:
             # generic path: bias, then the position part's own transformation, then the cache write
             if self.b_qkv is not None:
@@ -88,7 +88,7 @@ class GQAAttention(Mixer):
                           cache.k_pages, cache.v_pages, n, self.n_heads, self.n_kv_heads, self.head_dim,
                           write_cache, ctx.status, source=source)
         self._attend(ctx, out, qkv, cache)
-        return linear(ctx, "mixer.delta", out, self.w_o, allow_split=ctx.split_ok, small_consumer=True)
+        return linear(ctx, "mixer.delta", out, self.w_o, allow_split=True, small_consumer=True)
 
     def _attend_tensor_cores(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, cache: PagedView) -> None:
         """bfloat16: flash attention for requests with several tokens, split-KV attention for

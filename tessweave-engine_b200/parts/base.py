@@ -1,20 +1,31 @@
 """Interfaces of the parts a model is put together from, and their registries.
 
-A model is a list of blocks; a block arranges a mixer, a feed-forward and their
-norms; a mixer may use a position encoding.  Every part gets its sizes and
-constants as parameters, declares the weights it wants by name, says what cache it
-needs, and runs on the rows of a step.  No part knows which model it is in.
+A model is an embedding, a list of blocks, a final norm and an output head; a block
+arranges a mixer, a feed-forward and their norms; a mixer may use a position
+encoding.  Every part gets its sizes and constants as parameters, declares the
+weights it wants by name, says what cache it needs, and runs on the rows of a step.
+No part knows which model it is in.
 
 A part kind is registered under a name in its category; a model description
-(``ModelSpec``) names kinds and parameters only, so a new mixer, feed-forward,
-norm or position encoding is added by registering it: no framework file changes.
+(``ModelSpec``) names kinds and parameters only, so a new embedding, mixer,
+feed-forward, norm, position encoding or head is added by registering it: no
+framework file changes.
+
+What a sub-layer hands to the residual stream is a *delta*: a tensor ``[rows, width]``
+of the activation type, or a ``SplitSum`` -- the fp32 slices of a matrix product that
+was split over k, whose sum is the delta.  A producer may return either; a consumer
+that cannot add slices itself calls ``dense_delta`` first.  Nobody has to know who
+comes next.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Any, Callable
 
 import torch
+
+from ..csrc.ops import SplitSum
 
 
 # ---------------------------------------------------------------------------
@@ -76,7 +87,22 @@ class Runtime:
     dtype: torch.dtype
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
-        return torch.empty(*shape, dtype=dtype or self.dtype, device=self.device)
+        return poisoned(torch.empty(*shape, dtype=dtype or self.dtype, device=self.device))
+
+
+def poison_new_buffers() -> bool:
+    """TESSWEAVE_POISON_BUFFERS=1 (the tests set it): every buffer that is allocated without a value --
+    workspace, weight storage before loading -- is filled with NaN (integers with a large negative
+    number), so that a kernel that reads what nobody wrote gives NaN instead of whatever the memory held.
+    Fresh device memory is often zero, or holds the same values an earlier run left there, and hides
+    such a read."""
+    return os.environ.get("TESSWEAVE_POISON_BUFFERS", "0") == "1"
+
+
+def poisoned(t: torch.Tensor) -> torch.Tensor:
+    if poison_new_buffers():
+        t.fill_(float("nan") if t.is_floating_point() else -(2 ** 30))
+    return t
 
 
 class Workspace:
@@ -101,8 +127,10 @@ class Workspace:
         if buf is None or buf.dtype != dtype or buf.numel() < numel:
             if self.frozen:
                 raise RuntimeError(f"workspace buffer {name!r} would have to grow while a CUDA graph holds its address")
-            make = torch.zeros if zero else torch.empty
-            buf = make(max(numel, 1), dtype=dtype, device=self.device)
+            if zero:
+                buf = torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
+            else:
+                buf = poisoned(torch.empty(max(numel, 1), dtype=dtype, device=self.device))
             self._buffers[name] = buf
         return buf[:numel].view(*shape)
 
@@ -159,7 +187,6 @@ class StepContext:
     decode_only: bool = False      # every sequence brings exactly one token
     fixed_shape: bool = False      # the launch is being captured: sizes must not depend on host values of this step
     device_tokens: torch.Tensor | None = None   # int32: token ids the previous step left on the device (id -(i+1) -> [i])
-    split_ok: bool = False         # the consumer of the running sub-layer's output adds split-product slices itself
 
 
 # ---------------------------------------------------------------------------
@@ -173,6 +200,11 @@ class Part:
         self.runtime = runtime
 
     def weights(self) -> list[WeightDecl]:
+        return []
+
+    def redundant_names(self) -> list[str]:
+        """Tensors a checkpoint may carry for this part that are not loaded because the part gets them
+        another way (a tied head's copy of the embedding matrix).  Relative to the part's prefix."""
         return []
 
     def finalize(self) -> None:
@@ -189,24 +221,61 @@ class Part:
         return total
 
 
+def dense_delta(ctx: "StepContext", delta, dtype: torch.dtype, name: str = "delta.dense"):
+    """``delta`` as a tensor: a ``SplitSum`` is added up (in slice order) into a workspace buffer."""
+    if isinstance(delta, SplitSum):
+        _, rows, width = delta.slices.shape
+        return delta.dense(dtype, ctx.workspace.get(name, (rows, width), dtype))
+    return delta
+
+
+class Embedding(Part):
+    """Turns the token ids of a step into the rows of the residual stream."""
+
+    def forward(self, ctx: "StepContext") -> "ResidualStream":
+        raise NotImplementedError
+
+    def shared_matrix(self) -> torch.Tensor | None:
+        """The [vocab, hidden] matrix an output head may share when the model ties the two, or None."""
+        return None
+
+
+class Head(Part):
+    """Turns normalised rows into fp32 logits."""
+
+    def forward(self, ctx: "StepContext", logits: torch.Tensor, y: torch.Tensor, n_rows: int) -> None:
+        """logits[:n_rows] = head(y[:n_rows]); logits is fp32 [>= n_rows, vocab]."""
+        raise NotImplementedError
+
+
 class Norm(Part):
     """out = norm(resid [+ delta]); updates the fp32 residual stream in place.
 
-    ``delta`` is a tensor of the activation type or, if the norm sets ``accepts_split_sum``,
-    possibly a ``SplitSum`` (fp32 slices of a matrix product split over k)."""
+    ``delta`` is None, a tensor of the activation type, or a ``SplitSum``.  A norm whose kernel adds
+    the slices itself sets ``accepts_split_sum``; callers go through ``apply``, which adds them up
+    first for a norm that does not."""
     accepts_split_sum = False
 
-    def forward(self, ctx: StepContext, out: torch.Tensor, resid: torch.Tensor, delta: torch.Tensor | None,
-                n_rows: int, rows: torch.Tensor | None = None) -> None:
+    def apply(self, ctx: "StepContext", out: torch.Tensor, resid: torch.Tensor, delta, n_rows: int,
+              rows: torch.Tensor | None = None) -> None:
+        if not self.accepts_split_sum:
+            delta = dense_delta(ctx, delta, out.dtype)
+        self.forward(ctx, out, resid, delta, n_rows, rows)
+
+    def forward(self, ctx: "StepContext", out: torch.Tensor, resid: torch.Tensor, delta, n_rows: int,
+                rows: torch.Tensor | None = None) -> None:
         raise NotImplementedError
 
 
 class PositionEncoding(Part):
     """Encodes positions into queries and keys.
 
-    ``apply`` rewrites the q and k heads of the packed rows in place.  A mixer that
-    can fuse the encoding into another kernel asks ``fused_rotary_table()``; ``None``
-    means "call apply()".
+    ``apply`` rewrites the first ``n_heads`` heads of the packed rows (q heads, then k heads) in
+    place; every encoding implements it, and a mixer needs to know nothing else.  An encoding that
+    is a rotation by ``position * inv_freq[i]`` of the pairs ``(i, i + head_dim / 2)`` may also give
+    that table through ``fused_rotary_table()``: a mixer that has a kernel which rotates while it
+    does something else (writes the cache, attends) can then skip ``apply``.  ``None`` means
+    "call apply()".
     """
 
     def apply(self, ctx: StepContext, qk: torch.Tensor, n_heads: int, head_dim: int) -> None:
@@ -223,15 +292,17 @@ class Mixer(Part):
         return None
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: PagedView | StateView | None,
-                write_cache: bool) -> torch.Tensor:
-        """h: [n_tokens, hidden] normalised rows.  Returns the delta for the residual stream."""
+                write_cache: bool):
+        """h: [n_tokens, hidden] normalised rows.  Returns the delta for the residual stream
+        (a tensor or a ``SplitSum``)."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
     """Token-wise transformation (dense or routed)."""
 
-    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx: StepContext, h: torch.Tensor):
+        """Returns the delta for the residual stream (a tensor or a ``SplitSum``)."""
         raise NotImplementedError
 
 
@@ -247,15 +318,15 @@ class Block(Part):
 
 @dataclass
 class ResidualStream:
-    """The fp32 residual rows plus a delta the next norm still has to add."""
+    """The fp32 residual rows plus a delta (tensor or ``SplitSum``) the next norm still has to add."""
     resid: torch.Tensor
-    pending: torch.Tensor | None = None
+    pending: object = None
 
 
 # ---------------------------------------------------------------------------
 # registries
 # ---------------------------------------------------------------------------
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+CATEGORIES = ("embedding", "norm", "position", "mixer", "feed_forward", "block", "head")
 _REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {c: {} for c in CATEGORIES}
 
 

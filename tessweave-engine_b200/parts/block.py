@@ -25,7 +25,6 @@ class PreNormBlock(Block):
         self.norm2 = build_part("norm", norm2, runtime)
         self.feed_forward = build_part("feed_forward", feed_forward, runtime)
         self.graph_safe = all(p.graph_safe for p in self.parts().values())
-        self.next_norm_accepts_split_sum = False     # set by the model: the norm that consumes this block's output
 
     def parts(self):
         return {"norm1": self.norm1, "mixer": self.mixer, "norm2": self.norm2, "feed_forward": self.feed_forward}
@@ -38,6 +37,10 @@ class PreNormBlock(Block):
                 decls.append(WeightDecl(f"{prefix}.{w.name}" if prefix else w.name, w.shape, w.role, w.init, w.dest))
         return decls
 
+    def redundant_names(self) -> list[str]:
+        return [f"{self.names[role]}.{name}" if self.names[role] else name
+                for role, part in self.parts().items() for name in part.redundant_names()]
+
     def finalize(self) -> None:
         for part in self.parts().values():
             part.finalize()
@@ -48,12 +51,7 @@ class PreNormBlock(Block):
     def forward(self, ctx: StepContext, stream: ResidualStream, cache, write_cache: bool) -> None:
         n = ctx.n_tokens
         h = ctx.workspace.get("block.h", (n, self.hidden), self.runtime.dtype)
-        self.norm1.forward(ctx, h, stream.resid, stream.pending, n)
-        # a sub-layer may hand its output over as the slices of a split product if the norm
-        # that consumes it can add them
-        ctx.split_ok = self.norm2.accepts_split_sum
+        self.norm1.apply(ctx, h, stream.resid, stream.pending, n)
         delta = self.mixer.forward(ctx, h, cache, write_cache)
-        self.norm2.forward(ctx, h, stream.resid, delta, n)
-        ctx.split_ok = self.next_norm_accepts_split_sum
-        stream.pending = self.feed_forward.forward(ctx, h)
-        ctx.split_ok = False
+        self.norm2.apply(ctx, h, stream.resid, delta, n)
+        stream.pending = self.feed_forward.forward(ctx, h)      # whoever normalises next adds it

@@ -64,4 +64,4 @@ class SwiGLU(FeedForward):
         else:
             gate_up = linear(ctx, "ffn.gate_up", h, self.w_gate_up)
             ops.silu_mul(act, gate_up, n, self.interleaved)
-        return linear(ctx, "ffn.delta", act, self.w_down, allow_split=ctx.split_ok, small_consumer=True)
+        return linear(ctx, "ffn.delta", act, self.w_down, allow_split=True, small_consumer=True)

@@ -26,6 +26,23 @@ def configure_matmul_precision() -> None:
     _configured = True
 
 
+def verify_true_fp32(device) -> None:
+    """Raise unless the library's float32 product is a true 32-bit one on ``device``.
+
+    Every element is 1 + 2**-12: exact in float32, rounded to 1 by any mode that shortens the
+    operands (TF32 keeps 10 bits, bfloat16 7).  The sum of 256 squares is 256.125 in 32 bits and
+    256 otherwise.  Run once per float32 runner, after the switches above: a reduced mode left on by
+    an environment variable or by an earlier user of the process would put errors of 1e-3 into every
+    logit, which no later test could tell from a fault of the model."""
+    configure_matmul_precision()
+    a = torch.full((48, 256), 1.0 + 2.0 ** -12, dtype=torch.float32, device=device)
+    got = torch.mm(a, a.t())
+    worst = float((got - 256.125).abs().max())
+    if not worst < 1e-3:
+        raise RuntimeError(f"float32 matrix products are not computed in 32 bits on {device} "
+                           f"(256 x (1 + 2**-12)**2 came out {float(got[0, 0])!r}); a reduced-precision matrix mode is on")
+
+
 def matmul_nt(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """out[n, o] = sum_i x[n, i] * w[o, i].  x and w are of one element type; out is of the
     same type, or fp32 for a bf16 product whose result must not be rounded (the logits)."""
@@ -46,8 +63,7 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
 
     Steps with up to 8 rows (decode) in bfloat16 go through the weight-streaming kernel of
     csrc/gemm_smallm.cu; products of 9 to 64 rows with a large matrix (down, logits) through the persistent
-    tcgen05 kernel of csrc/gemm_tcgen05_stream.cu.  (The tcgen05/TMA kernel of csrc/gemm_tcgen05.cu with the weights as the
-    128-row operand takes 9 to 32 rows when TESSWEAVE_SWAP_AB=1; the library measured faster there.)
+    tcgen05 kernel of csrc/gemm_tcgen05_stream.cu.
     When the matrix has too few rows to fill the GPU these kernels split k and, if the caller can take it
     (``allow_split``), the fp32 slices are returned as a ``SplitSum`` for the consuming kernel
     to add.  Everything else is a library product.  ``small_consumer`` says that the kernel that follows is
@@ -56,18 +72,6 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
     """
     m, n = x.shape[0], w.shape[0]
     dtype = out_dtype or x.dtype
-    if x.is_cuda and ops.tcgen05_supported(x, w, m):
-        # 9..32 rows: tcgen05 tensor cores with the weights as the 128-row operand, fed by TMA
-        split, kper = ops.tcgen05_split(n, w.shape[1])
-        if split > 1:
-            slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
-            ops.gemm_tcgen05(slices, x, w, m, ctx.status, kper=kper, swap=True)
-            if allow_split:
-                return SplitSum(slices)
-            return SplitSum(slices).dense(dtype, ctx.workspace.get(name, (m, n), dtype))
-        out = ctx.workspace.get(name, (m, n), dtype)
-        ops.gemm_tcgen05(out, x, w, m, ctx.status, swap=True)
-        return out
     if ops.stream_product_preferred(x, w, m):
         # decode steps of 9 to 64 requests, large matrices: the weights stream once through the persistent
         # tcgen05 kernel (csrc/gemm_tcgen05_stream.cu); slices only where the consumer adds them itself

@@ -21,7 +21,7 @@ class RMSNorm(Norm):
         if size <= 0 or not eps > 0:
             raise ValueError("rmsnorm needs a positive size and eps")
         self.size, self.eps, self.weight_name = int(size), float(eps), weight_name
-        self.weight = torch.empty(self.size, dtype=torch.float32, device=runtime.device)
+        self.weight = runtime.empty(self.size, dtype=torch.float32)
 
     def weights(self) -> list[WeightDecl]:
         return [WeightDecl(self.weight_name, (self.size,), role="vector", init="one_plus_normal", dest=self.weight)]

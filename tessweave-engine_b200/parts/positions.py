@@ -35,8 +35,10 @@ class RotaryEmbedding(PositionEncoding):
         return table
 
     def apply(self, ctx: StepContext, qk: torch.Tensor, n_heads: int, head_dim: int) -> None:
-        """Rotate ``n_heads`` heads at the start of each packed row in place (no cache write)."""
-        raise NotImplementedError("rope is applied by the mixer's fused kernel; see fused_rotary_table()")
+        """Rotate ``n_heads`` heads at the start of each packed row in place (nothing else is touched).
+        A mixer with a kernel that rotates on the way (``fused_rotary_table``) gets the same numbers."""
+        ops.rotate_heads(qk, None, ctx.positions, ctx.seq_of_token, self.fused_rotary_table(head_dim), ctx.n_tokens,
+                         n_heads, head_dim)
 
 
 @register_part("position", "none")

@@ -45,12 +45,13 @@ def fill_weights(model: Model, folder) -> None:
     folder = Path(folder).resolve(strict=True)
     decls = model.weight_decls()
     spec = model.spec
+    redundant = model.redundant_names()
     seen: set[str] = set()
     unexpected, duplicate, wrong_shape = [], [], []
     for shard in shard_names(folder):
         with safe_open(str(folder / shard), framework="pt", device="cpu") as f:
             for key in f.keys():
-                if key == spec.head_name and spec.tie_word_embeddings:
+                if key in redundant:
                     continue
                 if any(key.endswith(sfx) for sfx in spec.ignored_suffixes):
                     continue

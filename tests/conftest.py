@@ -3,11 +3,16 @@
 ``-m "not gpu"`` tests run anywhere; ``-m gpu`` tests need a B200 and are skipped (not
 failed) where no CUDA device is visible.  Model folders are written into temporary folders.
 """
+import os
 import sys
 from pathlib import Path
 
 import pytest
 import torch
+
+# every buffer the engine allocates without a value starts as NaN in the tests: a kernel that reads memory
+# nobody wrote then shows as NaN instead of depending on what the memory held before
+os.environ.setdefault("TESSWEAVE_POISON_BUFFERS", "1")
 
 ROOT = Path(__file__).resolve().parent.parent
 for p in (str(ROOT), str(ROOT / "tests")):

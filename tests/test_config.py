@@ -18,7 +18,6 @@ def test_fields_and_defaults():
     # defaults of flow_engine/config.py:38-48
     assert d.num_key_value_heads == 4 and d.head_dim == 8 and d.rms_norm_eps == 1e-6 and d.rope_theta == 10000.0
     assert d.tie_word_embeddings is False and d.eos_token_ids == ()
-    assert d.kv_bytes_per_token(2) == 2 * 1 * 4 * 8 * 2
 
 
 @pytest.mark.parametrize("change", [

@@ -530,37 +530,6 @@ def test_gemm_small_m_fused_silu(m, inter, k):
     assert torch.allclose(out.float().cpu(), g * torch.sigmoid(g) * u, **TOL["bfloat16"])
 
 
-# ---------------------------------------------------------------------------
-# tcgen05 + TMA matrix product
-# ---------------------------------------------------------------------------
-@pytest.mark.parametrize("m,n,k,swap", [(9, 100, 64, True), (16, 37, 200, True), (32, 4608, 3584, True),
-                                        (64, 1000, 18944, True), (128, 256, 64, False), (300, 1000, 200, False),
-                                        (2048, 4608, 3584, False), (130, 130, 96, False)])
-def test_gemm_tcgen05(m, n, k, swap):
-    """tcgen05.mma fed by TMA against fp32 torch: both orientations, ragged tails in every size
-    (rows that fill no tile, k that is no multiple of 64), whole and split over k."""
-    torch.manual_seed(m + n)
-    x = dev(torch.randn(m, k) * 0.5, torch.bfloat16)
-    w = dev(torch.randn(n, k) * 0.05, torch.bfloat16)
-    want = x.float() @ w.float().t()
-    tol = dict(atol=2e-3 * max(1.0, float(want.abs().max())), rtol=0)
-    st = status()
-    out32 = torch.full((m, n), float("nan"), device="cuda")
-    ops().gemm_tcgen05(out32, x, w, m, st, swap=swap)
-    assert int(st) == 0
-    assert torch.allclose(out32, want, **tol)
-    out16 = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
-    ops().gemm_tcgen05(out16, x, w, m, st, swap=swap)
-    assert torch.allclose(out16.float(), want, atol=tol["atol"] + 8e-3 * float(want.abs().max()), rtol=0)
-    for kper in (64, 256, 1024):
-        if kper >= k:
-            continue
-        slices = torch.full((-(-k // kper), m, n), float("nan"), device="cuda")
-        ops().gemm_tcgen05(slices, x, w, m, st, kper=kper, swap=swap)
-        assert torch.allclose(slices.sum(0), want, **tol)
-    assert int(st) == 0
-
-
 def test_decode_attention_many_pages_per_block():
     """Pages of 4 tokens and one slice: a block walks 375 block-table entries, more than it keeps
     in shared memory, so the entries beyond come straight from the table."""

@@ -108,11 +108,13 @@ def block(mixer, ffn=SWIGLU):
                                  "names": NAMES})
 
 
-def spec_of(blocks, schedule):
+def spec_of(blocks, schedule, embedding=None, head=None, tie=False):
     return ModelSpec(architecture="ToyForTests", vocab_size=VOCAB, hidden_size=H,
                      layers=tuple(LayerSpec(b, f"layers.{i}") for i, b in enumerate(blocks)),
-                     schedule=tuple(schedule), final_norm=NORM, final_norm_prefix="norm",
-                     embedding_name="embed.weight", head_name="head.weight", tie_word_embeddings=False,
+                     schedule=tuple(schedule), embedding=embedding or PartSpec("token_embedding", {"vocab": VOCAB, "hidden": H}),
+                     embedding_prefix="embed", final_norm=NORM, final_norm_prefix="norm",
+                     head=head or PartSpec("linear_head", {"vocab": VOCAB, "hidden": H}), head_prefix="head",
+                     tie_word_embeddings=tie,
                      max_position_embeddings=512, init_std=0.08)
 
 
@@ -296,7 +298,7 @@ def test_builtin_parts_alone(dtype):
         d.dest.copy_((torch.randn(d.shape) * 0.1).view(d.dest.shape))
     x = (torch.randn(n, 200, device="cuda") * 0.5).to(dtype)
     ws = Workspace(torch.device("cuda"))
-    ctx = type("Ctx", (), {"n_tokens": n, "workspace": ws, "split_ok": False,
+    ctx = type("Ctx", (), {"n_tokens": n, "workspace": ws,
                            "status": torch.zeros(1, dtype=torch.int32, device="cuda")})()
     got = ffn.forward(ctx, x).float().cpu()
     w = {f"m.{d.name}": d.dest.float().cpu().reshape(d.shape) for d in ffn.weights()}

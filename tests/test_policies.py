@@ -26,7 +26,7 @@ def test_small_m_split_covers_k(n, k):
 
 def test_products_route_by_rows():
     assert ops.SMALL_M_LIMIT == 8 and ops.PAIR_MIN_M >= 256
-    assert ops.TCGEN05_MIN_M == ops.SMALL_M_LIMIT + 1
+    assert ops.STREAM_MIN_M == ops.SMALL_M_LIMIT + 1
 
 
 def test_split_policy_respects_the_consumers_limit():

@@ -213,7 +213,8 @@ class ResolvingRunner(FakeRunner):
         self.count = 0
         self.max_in_flight = 0
 
-    def launch(self, entries, temperature, seed, counter):
+    def launch(self, entries, temperature, seed, counter, device_refs=False):
+        assert device_refs or all(t >= 0 for e in entries for t in e.tokens)
         if self.fail_next:
             raise RuntimeError("injected failure")
         self.count += 1

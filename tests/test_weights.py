@@ -53,7 +53,7 @@ def test_load_keeps_matrices_in_run_type_and_vectors_in_fp32(tmp_path):
         assert torch.equal(packed[:8], gate[:8]) and torch.equal(packed[8:16], up[:8])
         assert torch.equal(packed[-8:], up[-8:]) and torch.equal(packed[-16:-8], gate[-8:])
     tied = tw.load_model(make_folder(tmp_path, "A"), "float32", "cpu")
-    assert tied.head.data_ptr() == tied.embedding.data_ptr()
+    assert tied.head.weight.data_ptr() == tied.embedding.weight.data_ptr()
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
@@ -93,7 +93,7 @@ def test_sharded_checkpoint_and_unsafe_shard_names(tmp_path):
     index = {"weight_map": {k: ("part-1.safetensors" if i < half else "part-2.safetensors") for i, k in enumerate(names)}}
     (folder / "model.safetensors.index.json").write_text(json.dumps(index))
     model = tw.load_model(folder, "float32", "cpu")
-    assert torch.equal(model.embedding, tensors["model.embed_tokens.weight"])
+    assert torch.equal(model.embedding.weight, tensors["model.embed_tokens.weight"])
     index["weight_map"][names[0]] = "../evil.safetensors"
     (folder / "model.safetensors.index.json").write_text(json.dumps(index))
     with pytest.raises(WeightError, match="unsafe"):

@@ -91,3 +91,37 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
     message = lib.tw_attn_decode_static_last_error().decode()
     assert "static array holds" in message and "128 slices" in message
     assert torch.isnan(out.float()).all()                               # nothing ran
+
+
+def test_entry_points_refuse_what_the_kernel_cannot_take():
+    """More slices than the merge has shared memory for, and a query the kernel's 16-byte loads cannot read,
+    are refused by the C entry points themselves before anything is launched: the return code says so and
+    the output is untouched.  (Nothing oversized is ever run.)"""
+    from tessweave_engine_b200.csrc import ops
+    from tessweave_engine_b200.csrc.build import load_library
+    lib = load_library("attention_bf16", {"TW_HEAD_DIM": D})
+    lib.tw_attn_decode_max_splits.restype = c_int
+    limit = lib.tw_attn_decode_max_splits()
+    assert limit == ops.DECODE_MAX_SPLITS
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    case = make_case(4, [1000])
+    code, out = call_static(lib, case, limit + 1, status)        # 3.7 MB of partial results would fit the array
+    torch.cuda.synchronize()
+    assert code == 1 and torch.isnan(out.float()).all()           # cudaErrorInvalidValue, nothing ran
+    code, out = call_static(lib, case, 1000, status)
+    assert code == 1 and torch.isnan(out.float()).all()
+    # a query that starts 2 bytes into a row
+    shifted = dict(case, q=case["q"].view(-1)[1:].clone().new_zeros(HQ * D + 8)[1:HQ * D + 1].view(1, HQ * D))
+    assert shifted["q"].data_ptr() % 16 != 0
+    code, out = call_static(lib, shifted, 4, status)
+    torch.cuda.synchronize()
+    assert code == 74 and torch.isnan(out.float()).all()          # cudaErrorMisalignedAddress
+    # the Python wrappers say the same in words
+    scratch = torch.empty(ops.decode_scratch_floats(HQ, D), device="cuda")
+    counters = torch.zeros(ops.decode_counter_ints(1, HKV, HQ // HKV), dtype=torch.int32, device="cuda")
+    out = torch.zeros(1, HQ * D, device="cuda", dtype=torch.bfloat16)
+    for q, nsplit, word in ((case["q"], limit + 1, "slices"), (shifted["q"], 4, "16-byte")):
+        with pytest.raises(ops.KernelError, match=word):
+            ops.attention_decode(out, q, case["q_start"], case["q_len"], case["kv_len"], case["slot"], case["table"],
+                                 case["k"], case["v"], 1, HQ, HKV, D, 0, D ** -0.5, nsplit, scratch, counters, status)
+    assert int(status) == 0
