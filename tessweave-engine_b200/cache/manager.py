@@ -287,6 +287,26 @@ class CacheManager:
                 g.host_table[lease.slot, b] = p
             g.dirty.add(lease.slot)
 
+    def check_writable(self, slot: int, start: int, end: int) -> None:
+        """A step is about to write the keys and values of positions ``start .. end - 1`` of the request
+        in ``slot``: every page it touches must be held by that request alone.  Shared pages are immutable
+        (flow_engine/cache.py:3-5): only full blocks are ever shared and a hit never covers a position that
+        is still to be computed, so a page with another holder here means the bookkeeping went wrong, and
+        the step must not run."""
+        lease = self.leases.get(slot)
+        if lease is None:
+            raise RuntimeError(f"request slot {slot} holds no lease")
+        ps = self.page_size
+        for gi, g in enumerate(self.groups):
+            table = lease.tables[gi]
+            for b in range(max(start // ps, lease.first_live_block[gi]), -(-end // ps)):
+                page = table[b] if b < len(table) else -1
+                if page < 0:
+                    raise RuntimeError(f"slot {slot}: block {b} of group {gi} has no page for positions {start}..{end - 1}")
+                if g.refs[page] != 1:
+                    raise RuntimeError(f"slot {slot}: page {page} of group {gi} (block {b}) has {g.refs[page]} holders "
+                                       f"and would be written at positions {start}..{end - 1}; shared pages are immutable")
+
     def advance(self, lease: Lease, tokens, computed: int) -> None:
         """Tell the manager that ``computed`` tokens of the request are now in the cache:
         full blocks become shareable, and pages that every later token's window has left

@@ -21,6 +21,7 @@
 //   score = (q . k) * scale,  visible iff  position - window < p <= position
 // Reference: flow_engine/model.py:193-200 and flow_engine/kernels/paged_decode.py:13-43.
 #include "common.cuh"
+#include "attention_common.cuh"
 #include <cooperative_groups.h>
 
 namespace cg = cooperative_groups;
@@ -39,39 +40,7 @@ constexpr int NT_O = D / 8;      // n-tiles of P.V
 constexpr int CHUNKS = D / 8;    // 16-byte chunks of a row
 constexpr float NEG_INF = -INFINITY;
 
-typedef __nv_bfloat16 bf16;
-
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
-    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
-}
-
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
-    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
-}
-
-// 16-byte asynchronous copy; src_bytes == 0 writes zeros and reads nothing.
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
-    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(a), "l"(gmem), "r"(src_bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
+using namespace tw_attn;
 
 // Element offset of key p's row in the cache, or -1 if p is outside [0, limit) or has no page.
 __device__ __forceinline__ long long key_offset(int p, int limit, const int* table, int table_stride, int page_size,
@@ -113,73 +82,10 @@ constexpr int DEC_MAX_CLUSTER = 16;                           // slices that can
 // after the last tile the stage buffers hold the warps' partial results and this block's merged slice
 static_assert((DEC_WARPS + 1) * DEC_HEADS * (D + 2) * 4 <= DEC_SMEM_STAGES, "merge area must fit the stage buffers");
 
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
-    uint32_t r;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
-    return r;
-}
-__device__ __forceinline__ void mma_bf16_regs(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 struct KFrag {                    // the d values of one key row this thread feeds to the MMAs
     uint4 blk[DB32 > 0 ? DB32 : 1];
     uint2 tail;
 };
-
-// Where a decode step's query, key and value come from when the kernel makes them itself: the rows of the
-// q/k/v product (fp32 slices of a product split over k, or one bf16 row), its bias, the rotation table.
-struct FusedQkv {
-    const float* partial;        // [slices][rows][width] fp32, or null
-    int nslices;
-    long long slice_stride;      // elements between slices
-    const bf16* dense;           // [rows][dense_stride] bf16, used when partial is null
-    int dense_stride;
-    const float* bias;           // [width] or null
-    const float* inv_freq;       // [D / 2]; null: no rotation
-    bf16* k_cache;               // where the new key and value go; null: the cache is not written
-    bf16* v_cache;
-    const void* next_weights;    // what the kernel after this one streams (or null): prefetched into L2 after the keys
-    long long next_bytes;
-};
-
-// fp32 values of NC columns of one row of the q/k/v product, bias included.  The slices of a split product are
-// summed (0 + 4 + 8 ..), (1 + 5 + ..), .. first and then ((.) + (.)) + ((.) + (.)), as the kernel that otherwise
-// does this work sums them; the loads of all columns and of four slices are independent of one another.
-template <int NC>
-__device__ __forceinline__ void product_cols(const FusedQkv& fq, size_t row, int width, const int (&cols)[NC], float (&out)[NC]) {
-    if (fq.partial) {
-        const float* prow = fq.partial + row * width;
-        float acc[NC][4];
-#pragma unroll
-        for (int j = 0; j < NC; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
-        int k = 0;
-        for (; k + 4 <= fq.nslices; k += 4) {
-#pragma unroll
-            for (int j = 0; j < NC; ++j) {
-#pragma unroll
-                for (int u = 0; u < 4; ++u) acc[j][u] += prow[(size_t)(k + u) * fq.slice_stride + cols[j]];
-            }
-        }
-        for (; k < fq.nslices; ++k) {
-#pragma unroll
-            for (int j = 0; j < NC; ++j) acc[j][0] += prow[(size_t)k * fq.slice_stride + cols[j]];
-        }
-#pragma unroll
-        for (int j = 0; j < NC; ++j) out[j] = (acc[j][0] + acc[j][1]) + (acc[j][2] + acc[j][3]);
-    } else {
-#pragma unroll
-        for (int j = 0; j < NC; ++j) out[j] = __bfloat162float(fq.dense[row * fq.dense_stride + cols[j]]);
-    }
-    if (fq.bias) {
-#pragma unroll
-        for (int j = 0; j < NC; ++j) out[j] += fq.bias[cols[j]];
-    }
-}
 
 // -DTW_TRACE: every block of the decode kernel records clock64() at its phase boundaries and the global
 // timer (ns) at its start and end, for a timeline of one launch (tw_attn_decode_trace_ptr gives the
@@ -213,7 +119,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
                    int* __restrict__ counters, int* status, const FusedQkv fq) {
     // k_cache and v_cache carry no __restrict__: with FUSED the block that holds the newest position writes that
     // position's key and value through fq.k_cache / fq.v_cache, which are the same memory, and reads them back
-    // below.  The keys are read with ld.global.cg (L2, coherent) and the values with cp.async.cg, never through
+    // below: that one key row with ld.global.cg (L2, coherent) and the values with cp.async.cg, never through
     // the non-coherent path, which may hold a line from before the write.
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_is_last;
@@ -341,17 +247,25 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         }
         cp_async_commit();      // one group per tile slot, empty past the end, so the wait count is constant
     };
-    // K of tile t (rows g and g + 8 of the warp's 16 keys), straight into registers; zero where there is no key
+    // K of tile t (rows g and g + 8 of the warp's 16 keys), straight into registers; zero where there is no key.
+    // Keys that earlier steps wrote come through the read-only path (ld.global.nc).  With FUSED the row of the
+    // newest position was written by this very block a moment ago: it alone is read with ld.global.cg, because
+    // the read-only path may still hold its line from before the write.
+    auto load_row = [&](long long off, bool fresh, KFrag& k) {
+#pragma unroll
+        for (int jb = 0; jb < DB32; ++jb) {
+            const uint4* p = reinterpret_cast<const uint4*>(k_cache + off + 32 * jb + 8 * c);
+            k.blk[jb] = off < 0 ? make_uint4(0u, 0u, 0u, 0u) : (fresh ? __ldcg(p) : __ldg(p));
+        }
+        const uint2* pt = reinterpret_cast<const uint2*>(k_cache + off + 32 * DB32 + 4 * c);
+        k.tail = (!DTAIL16 || off < 0) ? make_uint2(0u, 0u) : (fresh ? __ldcg(pt) : __ldg(pt));
+    };
     auto load_k = [&](int t, int st, KFrag& ka, KFrag& kb_) {
         const long long* offs = offs_base + st * 16;
         const long long oa = t < ntiles ? offs[g] : -1, ob = t < ntiles ? offs[g + 8] : -1;
-#pragma unroll
-        for (int jb = 0; jb < DB32; ++jb) {
-            ka.blk[jb] = oa >= 0 ? __ldcg(reinterpret_cast<const uint4*>(k_cache + oa + 32 * jb + 8 * c)) : make_uint4(0u, 0u, 0u, 0u);
-            kb_.blk[jb] = ob >= 0 ? __ldcg(reinterpret_cast<const uint4*>(k_cache + ob + 32 * jb + 8 * c)) : make_uint4(0u, 0u, 0u, 0u);
-        }
-        ka.tail = (DTAIL16 && oa >= 0) ? __ldcg(reinterpret_cast<const uint2*>(k_cache + oa + 32 * DB32 + 4 * c)) : make_uint2(0u, 0u);
-        kb_.tail = (DTAIL16 && ob >= 0) ? __ldcg(reinterpret_cast<const uint2*>(k_cache + ob + 32 * DB32 + 4 * c)) : make_uint2(0u, 0u);
+        const int pa = k_begin + t * DEC_TILE + warp * 16 + g;
+        load_row(oa, FUSED && pa == pos, ka);
+        load_row(ob, FUSED && pa + 8 == pos, kb_);
     };
 
     KFrag ka_next, kb_next;

@@ -17,6 +17,11 @@ fp32 ``[wanted, vocab]``, in the order of the entries and of ``want``.  After ev
 step ``done <step>`` is printed and flushed.  ``end`` names requests whose pages are
 given back after the step.  ``--max-tokens`` sizes the page pool, so pages are used
 again.
+
+With ``--prefix-cache`` full pages are shared between requests as in generation: a request's
+first entry is looked up in the prefix index, and the tokens its hit covers (whole pages,
+never the entry's last token) are not run again: the request starts at ``computed = shared``
+and only places behind the hit may be wanted.  The hit is reported on standard error.
 """
 from __future__ import annotations
 
@@ -40,6 +45,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-active", type=int, default=8, help="request slots")
     p.add_argument("--poison-freed-pages", action="store_true",
                    help="fill pages with NaN when they are given back, so a stale read shows")
+    p.add_argument("--prefix-cache", action="store_true",
+                   help="share full pages between requests with a common prefix, as generation does")
     return p
 
 
@@ -62,11 +69,12 @@ def run(args, stdin=None, stdout=None) -> int:
     model = load_model(args.model, args.dtype, "cuda")
     num_pages = math.ceil(args.max_tokens / page)
     cache = CacheManager(model.cache_needs(), page, num_pages, args.max_active, args.max_tokens,
-                         model.runtime.dtype, model.runtime.device, prefix_cache=False,
+                         model.runtime.dtype, model.runtime.device, prefix_cache=bool(getattr(args, "prefix_cache", False)),
                          poison_freed=args.poison_freed_pages)
     runner = ModelRunner(model, cache, max_step_tokens=args.max_tokens, max_step_seqs=args.max_active,
                          cuda_graphs=False)
-    live: dict[str, tuple] = {}     # id -> (lease, tokens so far)
+    vocab = model.spec.vocab_size
+    live: dict[str, list] = {}      # id -> [lease, tokens held, all tokens so far]
     for line in stdin:
         line = line.strip()
         if not line:
@@ -80,11 +88,24 @@ def run(args, stdin=None, stdout=None) -> int:
                 raise ValueError(f"step {step}: request {rid!r} appears twice")
             seen.add(rid)
             tokens = [int(t) for t in item["tokens"]]
+            if not tokens or min(tokens) < 0 or max(tokens) >= vocab:
+                raise ValueError(f"step {step}: request {rid!r} brings no tokens or a token id outside 0..{vocab - 1}")
+            want = [int(w) for w in item.get("want", [])]
             if rid not in live:
-                live[rid] = [cache.admit(None), 0]
-            lease, held = live[rid]
+                lease = cache.admit(tokens if cache.prefix_cache else None)
+                live[rid] = [lease, lease.cached_tokens, []]
+                if lease.cached_tokens:
+                    print(f"trace_run: request {rid} reuses {lease.cached_tokens} cached tokens", file=sys.stderr, flush=True)
+                    if want and min(want) < lease.cached_tokens:
+                        raise ValueError(f"step {step}: request {rid!r} wants place {min(want)}, which lies inside "
+                                         f"the {lease.cached_tokens} tokens taken from shared pages")
+                    want = [w - lease.cached_tokens for w in want]
+                    live[rid][2].extend(tokens[:lease.cached_tokens])
+                    tokens = tokens[lease.cached_tokens:]
+            lease, held, history = live[rid]
             cache.ensure(lease, held + len(tokens))
-            entries.append(StepEntry(lease.slot, tokens, held, [int(w) for w in item.get("want", [])]))
+            entries.append(StepEntry(lease.slot, tokens, held, want))
+            history.extend(tokens)
             live[rid][1] = held + len(tokens)
         if entries:
             logits = runner.step(entries)
@@ -95,8 +116,8 @@ def run(args, stdin=None, stdout=None) -> int:
             else:
                 runner.check_status()
             for item in record.get("entries", []):
-                lease, held = live[str(item["id"])]
-                cache.advance(lease, None, held)
+                lease, held, history = live[str(item["id"])]
+                cache.advance(lease, history, held)
         for rid in record.get("end", []):
             rid = str(rid)
             if rid in live:

@@ -119,6 +119,7 @@ class ModelRunner:
             ids.extend(e.tokens)
             pos.extend(range(e.start, e.start + t))
             sot.extend([si] * t)
+            self.cache.check_writable(e.slot, e.start, e.start + t)
             slot.append(e.slot); qs.append(cursor); ql.append(t); kl.append(e.start + t)
             for w in e.want:
                 if not 0 <= w < t:

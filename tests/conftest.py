@@ -38,4 +38,4 @@ def model_folders(tmp_path_factory):
     """name -> folder of the tiny model with weights stored in bf16 (exact in both run types)."""
     from helpers import make_folder
     tmp = tmp_path_factory.mktemp("models")
-    return {name: make_folder(tmp, name) for name in ("A", "B")}
+    return {name: make_folder(tmp, name) for name in ("A", "B", "C")}

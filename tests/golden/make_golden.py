@@ -29,7 +29,7 @@ import plain_qwen2  # noqa: E402
 from tiny_configs import CONFIGS, SEEDS  # noqa: E402
 from tessweave_engine_b200 import write_random_model  # noqa: E402
 
-LENGTHS = {"A": 33, "B": 40}
+LENGTHS = {"A": 33, "B": 40, "C": 29}
 
 
 def main(reference_root: str) -> None:

@@ -20,6 +20,17 @@ import plain_qwen2  # noqa: E402
 from tiny_configs import CONFIGS, PAGE_SIZE, SEEDS  # noqa: E402
 
 
+def note_error(test: str, case: str, error: float, scale: float) -> None:
+    """With TESSWEAVE_ERROR_LOG=<file> every comparison appends what it saw (worst difference, and the
+    size of the logits it was measured against): the bounds in the tests are set from such a record."""
+    import os
+    path = os.environ.get("TESSWEAVE_ERROR_LOG")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps({"test": test, "case": case, "error": error, "scale": scale,
+                                "relative": error / max(scale, 1e-30)}) + "\n")
+
+
 def make_folder(tmp, name: str, store_dtype: str = "bfloat16", **overrides) -> Path:
     """Write the tiny model ``name`` ("A" or "B") into ``tmp`` with random weights."""
     from tessweave_engine_b200 import write_random_model
@@ -142,12 +153,13 @@ def collect(steps: list[dict], out_dir: Path, vocab: int) -> dict[tuple[str, int
 
 
 def replay_in_process(folder, dtype: str, steps: list[dict], out_dir, max_tokens: int | None = None,
-                      block_size: int = 16, poison: bool = True) -> dict:
+                      block_size: int = 16, poison: bool = True, prefix_cache: bool = False) -> dict:
     """Run ``steps`` through the engine's replay program inside this process."""
     from tessweave_engine_b200.engine import replay
     out_dir = Path(out_dir)
     args = Namespace(model=str(folder), dtype=dtype, out=str(out_dir), block_size=block_size, max_active=8,
-                     max_tokens=max_tokens or max_live_tokens(steps), poison_freed_pages=poison)
+                     max_tokens=max_tokens or max_live_tokens(steps), poison_freed_pages=poison,
+                     prefix_cache=prefix_cache)
     stdin = io.StringIO("".join(json.dumps(s) + "\n" for s in steps))
     stdout = io.StringIO()
     code = replay.run(args, stdin=stdin, stdout=stdout)

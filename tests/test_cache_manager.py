@@ -192,3 +192,52 @@ def test_random_orders_keep_every_invariant(seed):
     m.check_invariants()
     assert all(len(g.free) == g.num_pages and g.promised == 0 for g in m.groups)
     assert len(m.free_slots) == 5
+
+
+def test_a_step_may_only_write_pages_its_request_holds_alone():
+    """Shared pages are immutable: a write into a page with a second holder, or into a block without
+    a page, is refused before the step runs (flow_engine/cache.py:3-5)."""
+    m = manager()
+    prompt = list(range(1, 10))
+    a = m.admit(prompt, reserve_tokens=12)
+    m.ensure(a, 9)
+    m.check_writable(a.slot, 0, 9)                    # private pages: fine
+    m.advance(a, prompt, 9)                           # blocks 0 and 1 are now in the prefix index too
+    m.check_writable(a.slot, 8, 9)                    # the partial tail stays private
+    with pytest.raises(RuntimeError, match="shared pages are immutable"):
+        m.check_writable(a.slot, 7, 9)                # position 7 lies in a published block
+    b = m.admit(prompt, reserve_tokens=12)            # hits both full blocks; computes from position 8
+    m.ensure(b, 9)
+    m.check_writable(b.slot, b.cached_tokens, 9)
+    with pytest.raises(RuntimeError, match="shared pages are immutable"):
+        m.check_writable(b.slot, 0, 9)
+    with pytest.raises(RuntimeError, match="has no page"):
+        m.check_writable(b.slot, 8, 13)               # block 3 was never ensured
+    with pytest.raises(RuntimeError, match="holds no lease"):
+        m.check_writable(3, 0, 1)
+    m.release(a); m.release(b); m.clear_prefixes()
+    m.check_invariants()
+
+
+def test_windowed_group_with_two_steps_under_way():
+    """With the next step launched before the current one has been accounted for, a windowed request holds
+    the pages of its window plus those of BOTH steps: the promise made at admission covers them, so a pool
+    that is promised to the last page never runs dry in the middle of a request."""
+    needs = [(WINDOW, None)]                                       # window 20, pages of 4
+    chunk = 8
+    m = CacheManager(needs, 4, 12, 1, 256, torch.float32, "cpu", prefix_cache=False)
+    need = m.pages_needed(200, 2 * chunk)[0]
+    assert need == -(-(20 + 2 * chunk) // 4) + 1
+    lease = m.admit(None, reserve_tokens=200, step_tokens=2 * chunk)
+    assert m.groups[0].promised == need
+    m.groups[0].promised += len(m.groups[0].free) - need           # everything else is promised to someone else
+    done = 0
+    m.ensure(lease, chunk)                                         # step A is launched
+    for _ in range(20):
+        m.ensure(lease, done + 2 * chunk)                          # step B is launched while A runs
+        done += chunk
+        m.advance(lease, None, done)                               # A is accounted for
+        assert sum(p >= 0 for p in lease.tables[0]) <= need
+    m.groups[0].promised -= len(m.groups[0].free) - lease.promised[0]
+    m.release(lease)
+    m.check_invariants()

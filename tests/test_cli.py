@@ -83,7 +83,7 @@ def test_generate_as_a_user_starts_it(name, tmp_path):
     prompt = [5, 17, 3, 200, 41, 7, 99, 100, 23]
     log = tmp_path / "runs" / "engine.jsonl"
     proc = run_cli("generate", folder, "--prompt-ids", ",".join(map(str, prompt)), "--dtype", "float32", "--max-tokens", 8,
-                   "--ignore-eos", "--log", log, "--block-size", 8, "--kv-blocks", 32, "--prefill-chunk", 4)
+                   "--ignore-eos", "--log", log, "--block-size", 8, "--kv-blocks", 32, "--prefill-chunk", 4, "--max-context", 256)
     assert proc.returncode == 0, proc.stderr[-3000:]
     got = [int(t) for t in proc.stdout.strip().split(",")]
     cfg, weights = plain_qwen2.read_folder(folder)

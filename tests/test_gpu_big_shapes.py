@@ -5,10 +5,15 @@ like these reach code that the tiny models do not: split matrix products, cluste
 import numpy as np
 import pytest
 
-from helpers import plain_logits, random_tokens, replay_in_process, schedule_tail, schedule_whole
+from helpers import (note_error, plain_logits, random_tokens, replay_in_process, schedule_portions, schedule_tail,
+                     schedule_whole)
 import tessweave_engine_b200 as tw
 
 pytestmark = pytest.mark.gpu
+
+# bfloat16 bound relative to the largest logit: twice the worst difference observed on a B200 at these sizes
+# (TESSWEAVE_ERROR_LOG=<file> records what every comparison saw)
+BF16_RELATIVE = 0.03
 
 BIG = {
     "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
@@ -19,26 +24,42 @@ BIG = {
 }
 
 
-@pytest.fixture(scope="module")
-def big(tmp_path_factory):
-    folder = tw.write_random_model(tmp_path_factory.mktemp("big") / "m", BIG, seed=5)
-    tokens = random_tokens(BIG["vocab_size"], 150, 21)
-    return folder, tokens, plain_logits(folder, tokens)
+# The layer sizes of the two larger benchmark configurations (Qwen2.5-14B and 32B: hidden 5120, 40 query and
+# 8 key/value heads, i.e. groups of five; intermediate 13,824 and 27,648), two layers each.  They take other routes
+# than the 7B sizes: the 128-row tiles of the gate/up matrix do not balance over the SMs, so decode portions of 9 to
+# 64 rows take the library's product and a separate SiLU.mul; the block-pair product is refused where its tiles
+# do not fill whole rounds; the small-batch product gives a row tile to two warps.
+def larger(intermediate):
+    return {**BIG, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 8,
+            "intermediate_size": intermediate}
+
+
+SIZES = {"7b": (BIG, 150), "14b": (larger(13824), 800), "32b": (larger(27648), 800)}
+
+
+@pytest.fixture(scope="module", params=list(SIZES))
+def big(request, tmp_path_factory):
+    config, length = SIZES[request.param]
+    folder = tw.write_random_model(tmp_path_factory.mktemp("big") / request.param, config, seed=5)
+    tokens = random_tokens(config["vocab_size"], length, 21)
+    return request.param, folder, tokens, plain_logits(folder, tokens)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_benchmark_layer_sizes_against_plain(dtype, big, tmp_path):
-    folder, tokens, want = big
-    tol = 1e-4 if dtype == "float32" else 0.03 * max(1.0, float(np.abs(want).max()))
-    # portions of 9 to 64 rows: in bfloat16 their large products (gate/up, down, logits) run on the persistent
-    # tcgen05 weight-streaming kernel
-    from helpers import schedule_portions
+    """Whole (for the larger sizes one portion of 800 rows: the prompt-sized products), most of it at once and the
+    last ten tokens one by one (the small-batch products), and portions of 9 to 64 rows (the streaming products and
+    the library's)."""
+    size, folder, tokens, want = big
+    scale = max(1.0, float(np.abs(want).max()))
+    tol = 1e-4 if dtype == "float32" else BF16_RELATIVE * scale
     for name, steps in (("whole", schedule_whole({"r": tokens})), ("tail", schedule_tail({"r": tokens}, tail=10)),
                         ("portions", schedule_portions({"r": tokens}, sizes=(12, 40, 64, 9, 25)))):
         rows = replay_in_process(folder, dtype, steps, tmp_path / name)
         errs = np.array([float(np.abs(rows[("r", p)] - want[p]).max()) for p in range(len(tokens))])
         worst = float(errs.max())
-        assert worst <= tol, (f"{dtype} {name}: off by {worst:.3e} at position {int(errs.argmax())} "
+        note_error("big_shapes", f"{size}/{dtype}/{name}", worst, scale)
+        assert worst <= tol, (f"{size} {dtype} {name}: off by {worst:.3e} at position {int(errs.argmax())} "
                               f"({int((errs > tol).sum())} of {len(errs)} positions beyond {tol:.1e}, median {np.median(errs):.3e}; "
                               f"logits up to {np.abs(want).max():.2f})")
 
@@ -82,8 +103,9 @@ def test_long_portions_against_plain(dtype, how, medium, tmp_path, monkeypatch):
     rows = replay_in_process(folder, dtype, steps, tmp_path / how)
     for rid, toks in requests.items():
         scale = max(1.0, float(np.abs(want[rid]).max()))
-        tol = 1e-4 if dtype == "float32" else 0.03 * scale
+        tol = 1e-4 if dtype == "float32" else BF16_RELATIVE * scale
         got = [p for p in range(len(toks)) if (rid, p) in rows]
         assert got, f"no logits for request {rid}"
         worst = max(float(np.abs(rows[(rid, p)] - want[rid][p]).max()) for p in got)
+        note_error("long_portions", f"{dtype}/{how}/{rid}", worst, scale)
         assert worst <= tol, f"{dtype} {how} request {rid}: off by {worst:.3e}"

@@ -15,16 +15,24 @@ def plain_generate(folder, prompt, n, temperature=0.0, seed=0):
     return plain_qwen2.generate(config, weights, prompt, n, temperature, seed)
 
 
-def assert_plausible(folder, prompt, output, margin):
+def assert_plausible(folder, prompt, output, margin, note=None):
     """Every generated token is the plain implementation's best one, or within ``margin`` of it
     (reduced precision may flip a near-tie; the reference says the same, docs/BENCHMARKS.md:7)."""
+    from helpers import note_error
     logits = plain_logits(folder, prompt + output)
-    for i, tok in enumerate(output):
-        row = logits[len(prompt) + i - 1]
-        assert row.max() - row[tok] <= margin, f"token {i} ({tok}) is {row.max() - row[tok]:.3f} below the best"
+    gaps = [float(logits[len(prompt) + i - 1].max() - logits[len(prompt) + i - 1][tok]) for i, tok in enumerate(output)]
+    if note:
+        note_error("plausible", note, max(gaps), float(np.abs(logits).max()))
+    for i, gap in enumerate(gaps):
+        assert gap <= margin, f"token {i} ({output[i]}) is {gap:.3f} below the best"
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+# How far below the plain implementation's best logit a token chosen in bfloat16 may lie: twice the worst
+# gap observed on a B200 (TESSWEAVE_ERROR_LOG=<file> records it).
+BF16_MARGIN = {"A": 0.012, "B": 0.06, "C": 0.064}       # twice the bound on a bfloat16 logit; observed gap: 0
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_greedy_generation_equals_plain(name, model_folders):
     vocab = CONFIGS[name]["vocab_size"]
     prompts = [random_tokens(vocab, n, 40 + n) for n in (5, 17, 33)]
@@ -36,7 +44,7 @@ def test_greedy_generation_equals_plain(name, model_folders):
     out16 = tw.generate(model16, prompts, max_tokens=8, ignore_eos=True, engine_config=cfg)
     for p, o in zip(prompts, out16):
         assert len(o) == 8
-        assert_plausible(model_folders[name], p, o, margin=0.08)
+        assert_plausible(model_folders[name], p, o, margin=BF16_MARGIN[name], note=f"greedy/{name}")
 
 
 def test_graphs_and_eager_steps_agree(model_folders):
@@ -133,7 +141,80 @@ def test_bad_token_is_reported_by_the_kernel(model_folders):
     runner.step([StepEntry(lease.slot, [1, 999, 2], 0, [2])])
     with pytest.raises(StepError, match="vocabulary"):
         runner.check_status()
-    other = cache.admit(None)                                   # no pages taken for it
-    runner.step([StepEntry(other.slot, [1, 2], 0, [1])])
-    with pytest.raises(StepError, match="page"):
-        runner.check_status()
+    # an id below zero names a token of the step before only where the caller says that there is such a step
+    with pytest.raises(ValueError, match="negative"):
+        runner.step([StepEntry(lease.slot, [-1], 3, [0])])
+    other = cache.admit(None)                                   # no pages taken for it: refused on the host,
+    with pytest.raises(RuntimeError, match="has no page"):      # before a kernel could meet the empty block table
+        runner.step([StepEntry(other.slot, [1, 2], 0, [1])])
+    runner.check_status()
+
+
+def test_cancel_while_the_step_ahead_is_on_the_gpu(model_folders):
+    """Look-ahead on the real runner: a request is cancelled between two ``step()`` calls, while the step that
+    was launched ahead (and that still writes the request's pages) is running.  Its pages are held until that
+    step has finished; the neighbours' tokens are the plain implementation's; nothing is lost."""
+    vocab = CONFIGS["B"]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 300 + n) for n in (9, 21, 14)]
+    model = tw.load_model(model_folders["B"], "float32", "cuda")
+    engine = tw.Engine(model, tw.EngineConfig(min_prefill_chunk=1, block_size=8, kv_blocks=30, max_context=64, max_active=3,
+                                              prefill_chunk=8, prefix_cache=False, lookahead=True))
+    assert engine.lookahead
+    reqs = [engine.submit(p, max_tokens=16, ignore_eos=True) for p in prompts]
+    for _ in range(6):
+        engine.step()
+    victim = reqs[1]
+    assert engine.inflight is not None and victim.id in engine.inflight.rows      # a step with its rows is under way
+    held = len(engine.cache.leases)
+    engine.cancel(victim.id)
+    assert victim.status == "cancelled" and len(engine.cache.leases) == held          # not given back yet
+    assert engine.inflight.deferred
+    engine.step()
+    assert len(engine.cache.leases) == held - 1
+    engine.cache.check_invariants()
+    late = engine.submit(prompts[1], max_tokens=5, ignore_eos=True)                  # takes the freed slot and pages
+    engine.run_until_done()
+    assert reqs[0].output == plain_generate(model_folders["B"], prompts[0], 16)
+    assert reqs[2].output == plain_generate(model_folders["B"], prompts[2], 16)
+    assert late.output == plain_generate(model_folders["B"], prompts[1], 5)
+    assert victim.output == plain_generate(model_folders["B"], prompts[1], 16)[:len(victim.output)]
+    engine.close()
+    engine.cache.check_invariants()
+    assert engine.stats()["free_blocks"] == 30 and engine.stats()["cancelled"] == 1
+
+
+@pytest.mark.parametrize("live", [3, 5])
+def test_padded_graph_steps_with_temperature(live, model_folders):
+    """Three (five) requests decode in a captured batch of four (eight): the padding rows must not disturb the
+    seeded draws of the live rows, which equal the plain implementation's, request by request."""
+    vocab = CONFIGS["A"]["vocab_size"]
+    prompts = [random_tokens(vocab, 4 + 3 * i, 500 + i) for i in range(live)]
+    model = tw.load_model(model_folders["A"], "float32", "cuda")
+    engine = tw.Engine(model, tw.EngineConfig(min_prefill_chunk=1, block_size=16, kv_blocks=40, max_context=64, max_active=8,
+                                              prefill_chunk=32, cuda_graphs=True))
+    temps = [0.7, 0.0, 1.2, 0.9, 0.0][:live]
+    reqs = [engine.submit(p, max_tokens=10 + i, temperature=t, seed=40 + i, ignore_eos=True)
+            for i, (p, t) in enumerate(zip(prompts, temps))]
+    engine.run_until_done()
+    assert engine.runner.graph_kernels, "no decode step ran from a captured graph"
+    for i, r in enumerate(reqs):
+        assert r.output == plain_generate(model_folders["A"], prompts[i], 10 + i, temps[i], 40 + i), f"request {i}"
+    engine.close()
+
+
+def test_adaptive_portions_do_not_change_the_tokens(model_folders):
+    """The feedback controller that steers the size of prompt portions towards a step time moves the cuts,
+    never the tokens."""
+    vocab = CONFIGS["B"]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 700 + n) for n in (60, 33, 47)]
+    model = tw.load_model(model_folders["B"], "float32", "cuda")
+    engine = tw.Engine(model, tw.EngineConfig(block_size=8, kv_blocks=40, max_context=96, max_active=3, prefill_chunk=24,
+                                              min_prefill_chunk=2, adaptive_chunk=True, target_step_ms=0.05))
+    reqs = [engine.submit(p, max_tokens=6, ignore_eos=True) for p in prompts]
+    seen = set()
+    while engine.step():
+        seen.add(engine.chunk)
+        engine.book.drain_events()
+    assert min(seen) < 24, "the controller never shortened a portion although no step can take 0.05 ms"
+    assert [r.output for r in reqs] == [plain_generate(model_folders["B"], p, 6) for p in prompts]
+    engine.close()

@@ -12,8 +12,9 @@ import torch
 import plain_qwen2
 import tessweave_engine_b200 as tw
 from tessweave_engine_b200.models import LayerSpec, Model, ModelSpec, ScheduleEntry
-from tessweave_engine_b200.parts import (FeedForward, FixedState, Mixer, PartSpec, PositionEncoding, Runtime,
-                                         StateView, WeightDecl, register_part)
+from tessweave_engine_b200.parts import (Embedding, FeedForward, FixedState, Head, Mixer, PartSpec, PositionEncoding,
+                                         ResidualStream, Runtime, StateView, StepContext, WeightDecl, Workspace,
+                                         build_part, dense_delta, register_part)
 from tessweave_engine_b200.engine.runner import ModelRunner, StepEntry
 
 pytestmark = pytest.mark.gpu
@@ -86,6 +87,55 @@ class ToyScalePositions(PositionEncoding):
         scale = 1.0 / (1.0 + ctx.positions.float() / 64.0)
         cols = n_heads * head_dim
         qk[:, :cols] = (qk[:, :cols].float() * scale[:, None]).to(qk.dtype)
+
+
+@register_part("embedding", "toy_scaled_embedding")
+class ToyScaledEmbedding(Embedding):
+    """resid = weight[token] * scale + learned_position[position]: an embedding scale and absolute positions
+    added to the stream, neither of which the built-in embedding has."""
+    graph_safe = False
+
+    def __init__(self, runtime, vocab, hidden, scale, max_positions):
+        super().__init__(runtime)
+        self.vocab, self.hidden, self.scale, self.max_positions = vocab, hidden, scale, max_positions
+        self.weight = runtime.empty(vocab, hidden)
+        self.positions = runtime.empty(max_positions, hidden)
+
+    def weights(self):
+        return [WeightDecl("weight", (self.vocab, self.hidden), dest=self.weight),
+                WeightDecl("positions.weight", (self.max_positions, self.hidden), dest=self.positions)]
+
+    def shared_matrix(self):
+        return self.weight
+
+    def forward(self, ctx):
+        resid = ctx.workspace.get("toy.resid", (ctx.n_tokens, self.hidden), torch.float32)
+        resid.copy_(self.weight[ctx.token_ids.long()].float() * self.scale + self.positions[ctx.positions.long()].float())
+        return ResidualStream(resid)
+
+
+@register_part("head", "toy_capped_head")
+class ToyCappedHead(Head):
+    """logits = cap * tanh((y @ W.T + bias) / cap): a bias and a cap, neither of which the built-in head has."""
+    graph_safe = False
+
+    def __init__(self, runtime, vocab, hidden, cap, tied=None):
+        super().__init__(runtime)
+        self.vocab, self.hidden, self.cap = vocab, hidden, cap
+        self.tied = tied is not None
+        self.weight = tied if tied is not None else runtime.empty(vocab, hidden)
+        self.bias = runtime.empty(vocab, dtype=torch.float32)
+
+    def weights(self):
+        own = [] if self.tied else [WeightDecl("weight", (self.vocab, self.hidden), dest=self.weight)]
+        return own + [WeightDecl("bias", (self.vocab,), role="vector", dest=self.bias)]
+
+    def redundant_names(self):
+        return ["weight"] if self.tied else []
+
+    def forward(self, ctx, logits, y, n_rows):
+        z = y[:n_rows].float() @ self.weight.float().t() + self.bias
+        logits[:n_rows] = self.cap * torch.tanh(z / self.cap)
 
 
 # ---------------------------------------------------------------------------
@@ -300,6 +350,156 @@ def test_builtin_parts_alone(dtype):
     ws = Workspace(torch.device("cuda"))
     ctx = type("Ctx", (), {"n_tokens": n, "workspace": ws,
                            "status": torch.zeros(1, dtype=torch.int32, device="cuda")})()
-    got = ffn.forward(ctx, x).float().cpu()
+    got = dense_delta(ctx, ffn.forward(ctx, x), dtype).float().cpu()
     w = {f"m.{d.name}": d.dest.float().cpu().reshape(d.shape) for d in ffn.weights()}
     assert torch.allclose(got, plain_qwen2.swiglu(w, "m", x.float().cpu()), **tol)
+
+
+@pytest.mark.parametrize("tie", [True, False])
+def test_toy_embedding_and_head_need_no_framework_change(tie):
+    """A scaled embedding with learned positions and a biased, capped head -- registered here -- make a model
+    whose first and last stage are not the built-in ones: ``Model`` only walks the parts its spec names.  Tied,
+    the head shares the toy embedding's matrix and the checkpoint brings no tensor for it."""
+    spec = spec_of([block(attention(position=PartSpec("none", {})))], [ScheduleEntry(0)],
+                   embedding=PartSpec("toy_scaled_embedding", {"vocab": VOCAB, "hidden": H, "scale": 3.0, "max_positions": 128}),
+                   head=PartSpec("toy_capped_head", {"vocab": VOCAB, "hidden": H, "cap": 2.5}), tie=tie)
+    model, cache, runner, w = build(spec)
+    assert ("head.weight" in w) == (not tie) and "head.bias" in w and "embed.positions.weight" in w
+    assert not model.graph_safe
+    if tie:
+        assert model.head.weight.data_ptr() == model.embedding.weight.data_ptr() and model.redundant_names() == {"head.weight"}
+    t = len(TOKENS)
+    pos = list(range(t))
+    x = w["embed.weight"][TOKENS] * 3.0 + w["embed.positions.weight"][:t]
+    h = plain_qwen2.rms_norm(x, w["layers.0.n1.weight"], 1e-5)
+    p = "layers.0.mix"
+    q = plain_qwen2.linear(h, w[f"{p}.q_proj.weight"], w[f"{p}.q_proj.bias"]).reshape(t, HEADS, D)
+    k = plain_qwen2.linear(h, w[f"{p}.k_proj.weight"], w[f"{p}.k_proj.bias"]).reshape(t, KV, D)
+    v = plain_qwen2.linear(h, w[f"{p}.v_proj.weight"], w[f"{p}.v_proj.bias"]).reshape(t, KV, D)
+    x = x + plain_qwen2.linear(plain_qwen2.attention(q, k, v).reshape(t, HEADS * D), w[f"{p}.o_proj.weight"])
+    x = plain_swiglu(w, "layers.0", x)
+    z = plain_qwen2.rms_norm(x, w["norm.weight"], 1e-5) @ w["embed.weight" if tie else "head.weight"].t() + w["head.bias"]
+    want = 2.5 * torch.tanh(z / 2.5)
+    for cuts in CUTS[:2]:
+        assert float((run_cut(cache, runner, TOKENS, cuts) - want).abs().max()) <= 1e-4, cuts[:3]
+
+
+def hand_made_context(rt, positions, seq_of_token, slots, q_start, q_len, kv_len):
+    """A StepContext as the runner would stage it, for running one part outside a model."""
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    n = len(positions)
+    return StepContext(runtime=rt, workspace=Workspace(torch.device("cuda")), n_tokens=n, n_seqs=len(slots),
+                       token_ids=i32([0] * n), positions=i32(positions), seq_of_token=i32(seq_of_token),
+                       seq_slot=i32(slots), seq_q_start=i32(q_start), seq_q_len=i32(q_len), seq_kv_len=i32(kv_len),
+                       status=torch.zeros(1, dtype=torch.int32, device="cuda"), host_slot=slots, host_q_start=q_start,
+                       host_q_len=q_len, host_kv_len=kv_len, max_q_len=max(q_len), max_kv_len=max(kv_len),
+                       decode_only=all(c == 1 for c in q_len))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("head_dim,theta", [(16, 1e4), (64, 1e6), (24, 5e4)])
+def test_position_encoding_alone(dtype, head_dim, theta):
+    """``RotaryEmbedding.apply`` -- the interface every position encoding has -- against the plain rotation,
+    for rows of several requests at scattered positions; the heads behind the first ``n_heads`` stay as they were."""
+    rt = Runtime(torch.device("cuda"), dtype)
+    rope = build_part("position", PartSpec("rope", {"theta": theta}), rt)
+    positions = [0, 1, 2, 700, 3, 15, 16, 4095]
+    ctx = hand_made_context(rt, positions, [0, 0, 0, 1, 2, 2, 2, 3], [0, 1, 2, 3], [0, 3, 4, 7], [3, 1, 3, 1], [3, 701, 17, 4096])
+    heads, extra = 5, 2
+    torch.manual_seed(4)
+    x = torch.randn(len(positions), (heads + extra) * head_dim).to(dtype)
+    qk = x.cuda().clone()
+    rope.apply(ctx, qk, heads, head_dim)
+    want = plain_qwen2.rope(x.float().reshape(len(positions), heads + extra, head_dim)[:, :heads], positions, theta)
+    got = qk.float().cpu().reshape(len(positions), heads + extra, head_dim)
+    tol = dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    assert torch.allclose(got[:, :heads], want, **tol)
+    assert torch.equal(got[:, heads:], x.float().reshape(len(positions), heads + extra, head_dim)[:, heads:])
+    table = rope.fused_rotary_table(head_dim).cpu()
+    assert torch.equal(table, theta ** (-torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+
+
+class TableHidden(PositionEncoding):
+    """The rotary encoding behind the plain interface only: no table for a mixer to fuse."""
+
+    def __init__(self, inner):
+        super().__init__(inner.runtime)
+        self.inner = inner
+
+    def apply(self, ctx, qk, n_heads, head_dim):
+        self.inner.apply(ctx, qk, n_heads, head_dim)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_part_alone(dtype):
+    """The attention part built from its PartSpec and run on hand-made rows: a prompt portion of one request
+    beside a single token of another whose keys are already in the cache (written by an earlier call of the
+    same part).  With the position encoding's table hidden, the part must take ``apply`` and give the same."""
+    rt = Runtime(torch.device("cuda"), dtype)
+    hidden, heads, kv, d, page = 80, 4, 2, 32, 8
+    spec = PartSpec("gqa_attention", {"hidden": hidden, "n_heads": heads, "n_kv_heads": kv, "head_dim": d, "qkv_bias": True,
+                                      "position": PartSpec("rope", {"theta": 1e4})})
+    results = []
+    for hide_table in (False, True):
+        mixer = build_part("mixer", spec, rt)
+        torch.manual_seed(6)
+        for decl in mixer.weights():
+            decl.dest.copy_((torch.randn(decl.shape) * 0.15).view(decl.dest.shape))
+        if hide_table:
+            mixer.position = TableHidden(mixer.position)
+        cache = tw.CacheManager([(mixer.cache_need(), None)], page, 12, 2, 64, dtype, rt.device, prefix_cache=False)
+        a, b = cache.admit(None), cache.admit(None)
+        torch.manual_seed(7)
+        ha, hb = torch.randn(13, hidden) * 0.7, torch.randn(20, hidden) * 0.7
+        # first call: b's first 19 rows (fills its cache); second call: 13 rows of a beside row 19 of b
+        cache.ensure(b, 19); cache.sync_tables()
+        ctx = hand_made_context(rt, list(range(19)), [0] * 19, [b.slot], [0], [19], [19])
+        mixer.forward(ctx, hb[:19].to(dtype).cuda(), cache.view(0), True)
+        cache.ensure(a, 13); cache.ensure(b, 20); cache.sync_tables()
+        ctx = hand_made_context(rt, list(range(13)) + [19], [0] * 13 + [1], [a.slot, b.slot], [0, 13], [13, 1], [13, 20])
+        h = torch.cat([ha, hb[19:]]).to(dtype).cuda()
+        got = dense_delta(ctx, mixer.forward(ctx, h, cache.view(0), True), dtype).float().cpu()
+        assert int(ctx.status) == 0
+        results.append(got)
+        w = {f"m.{decl.name}": decl.dest.float().cpu().reshape(decl.shape) for decl in mixer.weights()}
+        sz = {"heads": heads, "kv_heads": kv, "head_dim": d, "theta": 1e4}
+        for hs, rows in ((ha.to(dtype).float(), slice(0, 13)), (hb.to(dtype).float(), slice(13, 14))):
+            t = hs.shape[0]
+            q = plain_qwen2.rope(plain_qwen2.linear(hs, w["m.q_proj.weight"], w["m.q_proj.bias"]).reshape(t, heads, d), list(range(t)), 1e4)
+            k = plain_qwen2.rope(plain_qwen2.linear(hs, w["m.k_proj.weight"], w["m.k_proj.bias"]).reshape(t, kv, d), list(range(t)), 1e4)
+            v = plain_qwen2.linear(hs, w["m.v_proj.weight"], w["m.v_proj.bias"]).reshape(t, kv, d)
+            want = plain_qwen2.linear(plain_qwen2.attention(q, k, v).reshape(t, heads * d), w["m.o_proj.weight"])
+            want = want if rows.stop - rows.start == t else want[-1:]
+            tol = dict(atol=5e-5, rtol=5e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+            assert torch.allclose(got[rows], want, **tol), (hide_table, rows)
+    same = dict(atol=1e-6, rtol=0) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    assert torch.allclose(results[0], results[1], **same)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_head_parts_alone(dtype):
+    rt = Runtime(torch.device("cuda"), dtype)
+    vocab, hidden = 211, 72
+    emb = build_part("embedding", PartSpec("token_embedding", {"vocab": vocab, "hidden": hidden}), rt)
+    torch.manual_seed(8)
+    emb.weight.copy_(torch.randn(vocab, hidden))
+    ids = [0, 210, 5, 5, 99]
+    ctx = hand_made_context(rt, [0, 1, 2, 3, 4], [0] * 5, [0], [0], [5], [5])
+    ctx.token_ids = torch.tensor(ids, dtype=torch.int32, device="cuda")
+    stream = emb.forward(ctx)
+    assert stream.pending is None and stream.resid.dtype == torch.float32
+    assert torch.equal(stream.resid, emb.weight[ids].float())
+    for tied in (None, emb.shared_matrix()):
+        head = build_part("head", PartSpec("linear_head", {"vocab": vocab, "hidden": hidden}), rt,
+                          **({"tied": tied} if tied is not None else {}))
+        assert (head.weights() == []) == (tied is not None) and head.redundant_names() == (["weight"] if tied is not None else [])
+        if tied is None:
+            head.weight.copy_(torch.randn(vocab, hidden) * 0.1)
+        y = (torch.randn(7, hidden) * 0.5).to(dtype).cuda()
+        logits = torch.full((9, vocab), float("nan"), device="cuda")
+        head.forward(ctx, logits, y, 7)
+        want = y.float() @ head.weight.float().t()
+        assert logits.dtype == torch.float32 and torch.isnan(logits[7:]).all()
+        assert torch.allclose(logits[:7], want, atol=2e-5 if dtype == torch.float32 else 2e-3, rtol=0)
+    with pytest.raises(ValueError, match="tied head"):
+        build_part("head", PartSpec("linear_head", {"vocab": vocab + 1, "hidden": hidden}), rt, tied=emb.shared_matrix())

@@ -11,8 +11,8 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from helpers import (CONFIGS, PAGE_SIZE, ROOT, max_live_tokens, plain_logits, random_tokens, replay_in_process,
-                     schedule_mixed, schedule_portions, schedule_tail, schedule_whole)
+from helpers import (CONFIGS, PAGE_SIZE, ROOT, max_live_tokens, note_error, plain_logits, random_tokens,
+                     replay_in_process, schedule_mixed, schedule_portions, schedule_tail, schedule_whole)
 
 pytestmark = pytest.mark.gpu
 
@@ -24,12 +24,19 @@ def requests_for(name):
     return {f"r{i}": random_tokens(vocab, n, 10 + i) for i, n in enumerate(LENGTHS)}
 
 
-def tolerance(dtype, reference):
-    """float32: 1e-4 absolute.  bfloat16: 3% of the largest logit magnitude (at least 0.03):
-    activations carry 8 bits, and a few roundings per layer add up."""
-    if dtype == "float32":
-        return 1e-4
-    return 0.03 * max(1.0, float(np.abs(reference).max()))
+# Largest logit magnitude of each tiny model over these requests (plain implementation), and the bounds on a
+# logit.  The bounds are twice the worst difference observed on a B200 over all four cuttings
+# (TESSWEAVE_ERROR_LOG=<file> makes every comparison record what it saw), i.e. about 1 % of the logit scale:
+# activations carry 8 bits and a few roundings per layer add up, but a key left out or a stale page shifts a
+# logit by far more than that.
+SCALE = {"A": 1.33, "B": 2.3, "C": 2.0}
+BF16_BOUND = {"A": 0.006, "B": 0.03, "C": 0.032}       # observed 0.0028, 0.0145, 0.0160
+F32_BOUND = 1e-5                                        # observed 4.8e-7, 1.4e-6, 1.4e-6 (the limit asked for is 1e-4)
+
+
+def tolerance(dtype, name):
+    """float32: 1e-5 absolute for these tiny models.  bfloat16: the model's measured bound (see BF16_BOUND)."""
+    return F32_BOUND if dtype == "float32" else BF16_BOUND[name]
 
 
 SCHEDULES = {
@@ -43,11 +50,11 @@ SCHEDULES = {
 @pytest.fixture(scope="module")
 def plain(model_folders):
     return {name: {rid: plain_logits(model_folders[name], t) for rid, t in requests_for(name).items()}
-            for name in ("A", "B")}
+            for name in ("A", "B", "C")}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_every_cutting_gives_the_plain_logits(name, dtype, model_folders, plain, tmp_path):
     reqs = requests_for(name)
     results = {}
@@ -55,17 +62,20 @@ def test_every_cutting_gives_the_plain_logits(name, dtype, model_folders, plain,
         steps = make(reqs)
         rows = replay_in_process(model_folders[name], dtype, steps, tmp_path / sname, block_size=PAGE_SIZE[name])
         assert len(rows) == sum(LENGTHS), f"{sname}: not every position came back"
+        worst = 0.0
         for (rid, pos), row in rows.items():
             want = plain[name][rid][pos]
             err = float(np.abs(row - want).max())
+            worst = max(worst, err)
             assert np.isfinite(row).all(), f"{sname}: non-finite logits at {rid}[{pos}] (a stale page was read?)"
-            assert err <= tolerance(dtype, want), f"{sname}: {rid}[{pos}] is off by {err:.3e}"
+            assert err <= tolerance(dtype, name), f"{sname}: {rid}[{pos}] is off by {err:.3e}"
+        note_error("replay", f"{name}/{dtype}/{sname}", worst, SCALE[name])
         results[sname] = rows
     # the same position under different cuttings: equal beyond rounding
     for sname in ("tail", "portions", "mixed"):
         for key, row in results[sname].items():
             err = float(np.abs(row - results["whole"][key]).max())
-            bound = 2e-5 if dtype == "float32" else tolerance(dtype, row)
+            bound = 2e-5 if dtype == "float32" else tolerance(dtype, name)
             assert err <= bound, f"{sname} vs whole: {key} differs by {err:.3e}"
 
 
@@ -88,7 +98,8 @@ def test_long_decoding(dtype, model_folders, plain, tmp_path):
     rows = replay_in_process(model_folders["B"], dtype, steps, tmp_path, block_size=PAGE_SIZE["B"])
     want = plain_logits(model_folders["B"], tokens)
     worst = max(float(np.abs(rows[("long", p)] - want[p]).max()) for p in range(308))
-    assert worst <= tolerance(dtype, want), f"off by {worst:.3e}"
+    note_error("long_decoding", f"B/{dtype}", worst, SCALE["B"])
+    assert worst <= tolerance(dtype, "B"), f"off by {worst:.3e}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -101,7 +112,7 @@ def test_first_tokens_of_a_sequence(dtype, model_folders, tmp_path):
     rows = replay_in_process(model_folders["A"], dtype, steps, tmp_path)
     want = plain_logits(model_folders["A"], tokens)
     for p in range(4):
-        assert float(np.abs(rows[("s", p)] - want[p]).max()) <= tolerance(dtype, want)
+        assert float(np.abs(rows[("s", p)] - want[p]).max()) <= tolerance(dtype, "A")
 
 
 def test_trace_run_program(model_folders, tmp_path):
@@ -128,3 +139,46 @@ def test_trace_run_program(model_folders, tmp_path):
     assert np.abs(np.fromfile(out / "1.f32", dtype="<f4") - wb[7]).max() <= 1e-4
     assert np.abs(np.fromfile(out / "2.f32", dtype="<f4") - wb[8]).max() <= 1e-4
     assert np.abs(np.fromfile(out / "3.f32", dtype="<f4") - wa[19]).max() <= 1e-4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_prefix_hit_gives_the_same_logits_as_alone(name, dtype, model_folders, tmp_path, capfd):
+    """Two requests share a page-aligned prefix.  The second starts at ``computed = shared``: the shared pages are
+    not computed again, and its logits behind the hit equal those of the request alone (and the plain
+    implementation's).  Reference: tests/test_engine.py:113-126 (test_shared_prefix_logits_identical)."""
+    vocab, page = CONFIGS[name]["vocab_size"], PAGE_SIZE[name]
+    shared = random_tokens(vocab, 3 * page, 61)
+    first = shared + random_tokens(vocab, 11, 62)
+    second = shared + random_tokens(vocab, page + 5, 63)          # diverges exactly at a page's edge
+    third = shared[:2 * page] + random_tokens(vocab, 9, 64)       # shares two pages only
+    alone = replay_in_process(model_folders[name], dtype, schedule_whole({"b": second, "c": third}), tmp_path / "alone",
+                              block_size=page)
+    cut = 2 * page + 3
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": first[:cut], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": first[cut:], "want": [len(first) - cut - 1]}], "end": []},
+        # b arrives while a is alive: three pages hit; in the same step a decodes nothing, c starts beside b
+        {"step": 2, "entries": [{"id": "b", "tokens": second[:-4], "want": list(range(3 * page, len(second) - 4))},
+                                {"id": "c", "tokens": third, "want": list(range(2 * page, len(third)))}], "end": ["a", "c"]},
+        {"step": 3, "entries": [{"id": "b", "tokens": second[-4:], "want": [0, 1, 2, 3]}], "end": ["b"]},
+    ]
+    capfd.readouterr()
+    rows = replay_in_process(model_folders[name], dtype, steps, tmp_path / "shared", block_size=page, prefix_cache=True,
+                             max_tokens=max_live_tokens(steps) + 64)
+    err = capfd.readouterr().err
+    assert f"request b reuses {3 * page} cached tokens" in err and f"request c reuses {2 * page} cached tokens" in err
+    want_b, want_c = plain_logits(model_folders[name], second), plain_logits(model_folders[name], third)
+    for rid, toks, want, first_place in (("b", second, want_b, 3 * page), ("c", third, want_c, 2 * page)):
+        for p in range(first_place, len(toks)):
+            row = rows[(rid, p)]
+            assert np.isfinite(row).all()
+            assert float(np.abs(row - want[p]).max()) <= tolerance(dtype, name), f"{rid}[{p}] against plain"
+            same = float(np.abs(row - alone[(rid, p)]).max())
+            assert same <= (2e-5 if dtype == "float32" else tolerance(dtype, name)), f"{rid}[{p}] differs from the request alone by {same:.3e}"
+    assert ("b", 0) not in rows
+    # wanting a place inside the hit is refused, not answered from nowhere
+    bad = [steps[0], steps[1], {"step": 2, "entries": [{"id": "b", "tokens": second, "want": [0]}], "end": []}]
+    with pytest.raises(ValueError, match="inside"):
+        replay_in_process(model_folders[name], dtype, bad, tmp_path / "bad", block_size=page, prefix_cache=True,
+                          max_tokens=max_live_tokens(steps) + 64)

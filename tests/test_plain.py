@@ -12,7 +12,7 @@ import tessweave_engine_b200 as tw
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_plain_equals_reference_logits(name, tmp_path):
     """Golden logits come from flow_engine.model.CausalLM (tests/golden/make_golden.py)."""
     meta = json.loads((GOLDEN / f"qwen2_tiny_{name}.json").read_text())

@@ -296,3 +296,51 @@ def test_lookahead_cancel_and_failure_leave_nothing_behind(model):
     assert b.status == "error" and e.inflight is None
     e.cache.check_invariants()
     assert not e.cache.leases and e.stats()["free_blocks"] + e.stats()["cached_prefix_blocks"] == 64
+
+
+def test_small_budget_leaves_nobody_out(model):
+    """A token budget below the number of active requests: the decode pass starts at a moving place, so
+    every request advances within a few steps, and a prompt still being read always gets a token."""
+    e, runner = engine_for(model, max_active=4, max_step_tokens=2, prefill_chunk=4)
+    reqs = [e.submit([10 + i, 20 + i], max_tokens=6, ignore_eos=True) for i in range(4)]
+    for _ in range(8):
+        e.step()                                        # prompts go in two tokens at a time
+    before = [len(r.output) for r in reqs]
+    late = e.submit([1, 2, 3, 4, 5], max_tokens=2, ignore_eos=True)    # waits for a slot; nothing to check yet
+    for _ in range(4):
+        e.step()
+    after = [len(r.output) for r in reqs]
+    assert all(b > a for a, b in zip(before, after) if a < 6), (before, after)
+    drain(e)
+    assert all(len(r.output) == 6 for r in reqs) and len(late.output) == 2
+    # decode rows never crowd out a prompt: with three decoding requests and budget 2, the reader still moves
+    e2, runner2 = engine_for(model, max_active=4, max_step_tokens=2, prefill_chunk=4)
+    for i in range(3):
+        e2.submit([5 + i], max_tokens=30, ignore_eos=True)
+    for _ in range(4):
+        e2.step()
+    reader = e2.submit(list(range(40, 52)), max_tokens=1, ignore_eos=True)
+    for _ in range(14):
+        e2.step()
+    assert reader.computed >= 12 or reader.status == "length"
+    e.close(); e2.close()
+
+
+def test_failed_launch_of_the_step_ahead_waits_for_the_running_step(model):
+    """The step launched ahead fails (here: the runner refuses it) while the step before it is still running:
+    that step is waited for before any page is given back."""
+    e, runner = lookahead_engine(model, True)
+    a = e.submit([1, 2, 3], max_tokens=20, ignore_eos=True)
+    e.step()
+    assert len(runner.queue) == 1                       # one step under way, launched ahead
+    launches = runner.count
+
+    def failing_launch(entries, temperature, seed, counter, device_refs=False):
+        assert runner.queue, "the step before is still running when the next launch fails"
+        raise RuntimeError("injected launch failure")
+    runner.launch = failing_launch
+    with pytest.raises(RuntimeError, match="injected launch failure"):
+        e.step()
+    assert runner.count == launches and not runner.queue      # the running step was finished (waited for), not abandoned
+    assert a.status == "error" and not e.cache.leases and not e.flights
+    e.cache.check_invariants()

@@ -111,16 +111,16 @@ def test_entry_points_refuse_what_the_kernel_cannot_take():
     code, out = call_static(lib, case, 1000, status)
     assert code == 1 and torch.isnan(out.float()).all()
     # a query that starts 2 bytes into a row
-    shifted = dict(case, q=case["q"].view(-1)[1:].clone().new_zeros(HQ * D + 8)[1:HQ * D + 1].view(1, HQ * D))
+    shifted = dict(case, q=torch.zeros(HQ * D + 8, device="cuda", dtype=torch.bfloat16)[1:HQ * D + 1].view(1, HQ * D))
     assert shifted["q"].data_ptr() % 16 != 0
     code, out = call_static(lib, shifted, 4, status)
     torch.cuda.synchronize()
-    assert code == 74 and torch.isnan(out.float()).all()          # cudaErrorMisalignedAddress
+    assert code == 716 and torch.isnan(out.float()).all()         # cudaErrorMisalignedAddress
     # the Python wrappers say the same in words
     scratch = torch.empty(ops.decode_scratch_floats(HQ, D), device="cuda")
     counters = torch.zeros(ops.decode_counter_ints(1, HKV, HQ // HKV), dtype=torch.int32, device="cuda")
     out = torch.zeros(1, HQ * D, device="cuda", dtype=torch.bfloat16)
-    for q, nsplit, word in ((case["q"], limit + 1, "slices"), (shifted["q"], 4, "16-byte")):
+    for q, nsplit, word in ((case["q"], limit + 1, "slices"), (shifted["q"], 4, "aligned")):
         with pytest.raises(ops.KernelError, match=word):
             ops.attention_decode(out, q, case["q_start"], case["q_len"], case["kv_len"], case["slot"], case["table"],
                                  case["k"], case["v"], 1, HQ, HKV, D, 0, D ** -0.5, nsplit, scratch, counters, status)

@@ -21,6 +21,18 @@ TINY_B = {
     "initializer_range": 0.05,
 }
 
-PAGE_SIZE = {"A": 16, "B": 8}
-CONFIGS = {"A": TINY_A, "B": TINY_B}
-SEEDS = {"A": 1234, "B": 4321}
+# Sizes the kernels' fast paths do not take: a head size that is no multiple of 16 (bfloat16 attention falls to the
+# exact kernel, the rotation to the two-values-at-a-time kernel), an intermediate size that is no multiple of 8
+# (gate and up rows are not interleaved), a hidden size that is no multiple of 16, pages of 4 tokens.
+TINY_C = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 131, "hidden_size": 72, "intermediate_size": 100, "num_hidden_layers": 2,
+    "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 24,
+    "rope_theta": 50000.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 512,
+    "tie_word_embeddings": True, "use_sliding_window": False, "hidden_act": "silu",
+    "initializer_range": 0.06,
+}
+
+PAGE_SIZE = {"A": 16, "B": 8, "C": 4}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+SEEDS = {"A": 1234, "B": 4321, "C": 77}
