@@ -34,6 +34,8 @@ BENCH_CONFIG = {
 }
 PAGE_SIZE = 16
 PREFILL_TOKENS = 2048
+SHORT_CONTEXT = 512            # the benchmark configuration's prompts: generation starts here and runs to the context length
+LONG_PREFILL_TOKENS = 8192
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -113,16 +115,18 @@ def build_model(layers: int):
     return model, cfg
 
 
-def decode_run(model, cfg, batch: int, context: int, steps: int, warmup: int, graphs: bool = True):
+def decode_run(model, cfg, batch: int, context: int, steps: int, warmup: int, graphs: bool = True, max_context: int = 0):
     """Device-timed decode: ``batch`` requests that already hold ``context - steps - warmup``
-    tokens each (cache filled with random keys and values) decode one token per step."""
+    tokens each (cache filled with random keys and values) decode one token per step.  ``max_context``: the
+    longest request the engine is configured for (block tables and the choices frozen into the captured graphs
+    are made for it); by default the context itself."""
     import torch
     import tessweave_engine_b200 as tw
     from tessweave_engine_b200.engine.runner import ModelRunner, StepEntry
     total = warmup + steps
     start = max(1, context - total)
     pages = batch * (-(-(start + total) // PAGE_SIZE))
-    cache = tw.CacheManager(model.cache_needs(), PAGE_SIZE, pages, batch, start + total, model.runtime.dtype,
+    cache = tw.CacheManager(model.cache_needs(), PAGE_SIZE, pages, batch, max(start + total, max_context), model.runtime.dtype,
                             model.runtime.device, prefix_cache=False)
     for g in cache.groups:
         g.k.normal_(0, 0.5)
@@ -242,6 +246,36 @@ def e2e_run(model, cfg, batch: int, context: int, steps: int, warmup: int):
             "generated": generated}
 
 
+def generation_run(model, cfg, batch: int, prompt_len: int, context: int):
+    """The workload the benchmark configuration names, end to end through ``Engine.submit`` / ``Engine.step``:
+    ``batch`` random prompts of ``prompt_len`` tokens, each generating up to ``context`` tokens in all.  Decode
+    tokens per second averaged over the whole run (the prompts' steps are left out of the time)."""
+    import torch
+    import tessweave_engine_b200 as tw
+    pages = batch * (-(-context // PAGE_SIZE)) + 1
+    engine = tw.Engine(model, tw.EngineConfig(block_size=PAGE_SIZE, kv_blocks=pages, max_context=context, max_active=batch,
+                                              max_queue=batch, prefill_chunk=2048, max_step_tokens=2048 + batch,
+                                              prefix_cache=False))
+    gen = torch.Generator().manual_seed(5)
+    reqs = [engine.submit(torch.randint(0, cfg.vocab_size, (prompt_len,), generator=gen).tolist(),
+                          max_tokens=context - prompt_len, ignore_eos=True) for _ in range(batch)]
+    while any(r.computed < len(r.prompt) for r in reqs) or engine.waiting:
+        engine.step()
+    for _ in range(4):
+        engine.step()
+    torch.cuda.synchronize()
+    before = sum(len(r.output) for r in reqs)
+    t0 = time.perf_counter()
+    engine.run_until_done()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    generated = sum(len(r.output) for r in reqs) - before
+    engine.close()
+    del engine
+    torch.cuda.empty_cache()
+    return {"tok_s": generated / seconds, "seconds": seconds, "generated": generated}
+
+
 WORKLOAD_SIZES = {
     # layer sizes of the Qwen2.5-14B-sized and -32B-sized configurations
     "continuous14b": dict(num_hidden_layers=48, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
@@ -315,6 +349,16 @@ def workload_run(name: str, layers: int | None) -> dict:
             "finished": stats["finished"], "weights_gb": round(model.weight_bytes() / 1e9, 2)}
 
 
+def config_record(args, peaks_source: str) -> dict:
+    """What both arms measure on (flat, every size named): the same record in the line of either arm."""
+    c = BENCH_CONFIG
+    return {"model": "Qwen2.5-7B-sized (random weights)", "layers": args.layers, "layers_full": c["num_hidden_layers"],
+            "hidden": c["hidden_size"], "heads": c["num_attention_heads"], "kv_heads": c["num_key_value_heads"],
+            "head_dim": c["head_dim"], "intermediate": c["intermediate_size"], "vocab": c["vocab_size"],
+            "global_batch": args.batch, "seq_len": args.context, "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (weights >> 126 MB)", "peaks": peaks_source}
+
+
 def reference_arm(args) -> int:
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "flow_engine").exists():
@@ -323,7 +367,7 @@ def reference_arm(args) -> int:
         return 0
     try:
         from baseline.run_reference import run
-        print(json.dumps(run(args, BENCH_CONFIG)))
+        print(json.dumps(run(args, BENCH_CONFIG, config_record(args, peaks()[1]))))
     except Exception as exc:    # noqa: BLE001
         print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}))
     return 0
@@ -410,8 +454,8 @@ def main() -> int:
     if args.kernels:
         import tessweave_engine_b200 as tw
         from tessweave_engine_b200.engine.kernel_bench import format_table, kernel_table
-        cfg = tw.Qwen2Config.from_dict(BENCH_CONFIG)
-        rows = kernel_table(cfg, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE)
+        _, spec = tw.resolve(BENCH_CONFIG)
+        rows = kernel_table(spec, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE)
         print(format_table(rows), file=sys.stderr)
         print(json.dumps({"kernels": rows, "peaks": pk, "peaks_source": pk_source, "batch": args.batch,
                           "context": args.context, "prefill_tokens": PREFILL_TOKENS}))
@@ -439,13 +483,7 @@ def main() -> int:
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids",
         "impl": "ours",
-        "config": {"model": "Qwen2.5-7B-sized (random weights)", "layers": args.layers,
-                   "layers_full": BENCH_CONFIG["num_hidden_layers"], "hidden": cfg.hidden_size,
-                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
-                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
-                   "seq_len": args.context, "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS,
-                   "parallelism": "single GPU", "l2": "inputs larger than L2 (weights >> 126 MB)",
-                   "peaks": pk_source},
+        "config": config_record(args, pk_source),
     }
     nbytes = decode_bytes(model, cfg, args.batch, main_run["context"])
     achieved = nbytes / (main_run["ms_per_step"] / 1e3) / 1e9
@@ -462,13 +500,23 @@ def main() -> int:
         for b in (1, 64):
             r = decode_run(model, cfg, b, args.context, max(8, args.steps // 2), 3)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
+        # the other end of the workload: requests of about 512 tokens inside an engine set up for 4,096
+        for b in (1, 8, 64):
+            r = decode_run(model, cfg, b, SHORT_CONTEXT, max(8, args.steps // 2), 3, max_context=args.context)
+            points[f"decode_b{b}_ctx{SHORT_CONTEXT}"] = round(r["tok_s"], 1)
+        # and the whole of it: prompts of 512 tokens generating to 4,096, end to end, averaged over the run
+        run = generation_run(model, cfg, args.batch, SHORT_CONTEXT, args.context)
+        points[f"decode_b{args.batch}_avg_{SHORT_CONTEXT}_to_{args.context}_e2e"] = round(run["tok_s"], 1)
+        long_pre = prefill_run(model, cfg, LONG_PREFILL_TOKENS, reps=3, warmup=2)
+        points[f"prefill_{LONG_PREFILL_TOKENS}"] = round(long_pre["tok_s"], 1)
+        points[f"prefill_{LONG_PREFILL_TOKENS}_frac"] = round(long_pre["flops"] / (long_pre["ms"] / 1e3) / peak_flops, 4)
         record["points"] = points
         e2e = e2e_run(model, cfg, args.batch, args.context, args.steps, args.warmup)
         record["e2e"] = {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms_per_step"], 4),
                          "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]}
         # the dominant kernel of both regimes (the gate/up product) alone, against its own roofline
         from tessweave_engine_b200.engine.kernel_bench import kernel_table
-        rows = kernel_table(cfg, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE,
+        rows = kernel_table(model.spec, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE,
                             only=("gate/up",))
         record["dominant_kernel"] = {r["op"]: {"kernel": r["kernel"], "us": r["us"], "frac": r["frac"], "bound": r["bound"]}
                                      for r in rows}

@@ -76,10 +76,17 @@ def _check(code: int, what: str) -> None:
 
 _sigs_done: set[str] = set()
 LAUNCHES = [0]      # kernel launchers called so far (each call launches at least one kernel)
+CALL_LOG: list[str] | None = None     # when a list: the launchers called, by name (who measures asks which kernel ran)
+
+
+def note_call(name: str) -> None:
+    if CALL_LOG is not None:
+        CALL_LOG.append(name)
 
 
 def _fn(lib_name: str, fn_name: str, defines=None):
     LAUNCHES[0] += 1
+    note_call(fn_name)
     lib = load_library(lib_name, defines)
     fn = getattr(lib, fn_name)
     key = f"{lib_name}:{fn_name}:{defines}"
@@ -444,6 +451,113 @@ def attention_decode_fused(out, source, bias, inv_freq, write_cache, seq_q_start
         _ptr(status), _ptr(prefetch), ctypes.c_longlong(prefetch.numel() * prefetch.element_size() if prefetch is not None else 0),
         _stream())
     _check(code, "attention_decode_fused")
+
+
+# ---------------------------------------------------------------------------
+# decode attention fed by TMA (head sizes that are multiples of 64)
+# ---------------------------------------------------------------------------
+def decode_tma_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    """Whether single-token requests attend through ``attention_decode_tma``: bfloat16, a head size of 64, 128,
+    192 or 256, and pages that are a whole fraction (at least 4 keys) or a whole multiple of a 64-key tile.
+    TESSWEAVE_DECODE_TMA=0 keeps the kernel that loads keys through registers."""
+    import os
+    if os.environ.get("TESSWEAVE_DECODE_TMA", "1") == "0":
+        return False
+    return (dtype == torch.bfloat16 and head_dim % 64 == 0 and 64 <= head_dim <= 256 and page_size >= 4
+            and (64 % page_size == 0 or page_size % 64 == 0))
+
+
+def decode_tma_splits(n_seqs: int, n_kv_heads: int, group: int, max_kv_len: int) -> int:
+    """How many slices the TMA decode attention cuts a request's keys into.  Two blocks share an SM (a ring of
+    three 64-key tiles each), and a block alone does not pull its share of the bandwidth, so the launch is filled
+    to about 256 blocks -- not to the last of the 296 places: clusters that do not all find room at once start a
+    second round (measured on B200 at 4,096 keys, whole decode steps of the 7B-sized model: batch 8 with 8 slices
+    3.33 ms, with 4 slices 3.53, with 9 (288 blocks) 3.75; batch 12 with 5 slices 3.61 ms, with 6 (288 blocks)
+    4.07, with 3 (144 blocks) 4.71; batch 4 with 13 slices 3.15 ms, with 14 or 16 3.5; batch 2 with 8 slices 3.18
+    ms, with 12 or 16 3.4 to 3.5).  Few requests with long contexts take more slices and merge through scratch
+    memory (16,384 keys, batch 2, 12 layers: 1.56 ms with 32 slices, 1.89 with 16).
+    TESSWEAVE_DECODE_SPLITS forces a number."""
+    import os
+    forced = os.environ.get("TESSWEAVE_DECODE_SPLITS")
+    tiles = max(1, -(-max_kv_len // 64))
+    most = min(tiles, DECODE_MAX_SPLITS, DECODE_SCRATCH_UNITS // max(1, n_seqs))
+    if forced:
+        return max(1, min(int(forced), most))
+    groups = max(1, n_seqs * n_kv_heads * ((group + 7) // 8))
+    if groups <= 8 and max_kv_len > 8192:
+        want = min(32, 256 // groups)
+    elif groups <= 4:
+        want = 16
+    elif groups <= 8:
+        want = 8
+    elif groups <= 16:
+        want = 13
+    else:
+        want = max(1, 256 // groups)
+    nsplit = max(1, min(want, most))
+    per = -(-(-(-max_kv_len // nsplit)) // 64) * 64          # slices are whole tiles: no slice without keys
+    return max(1, -(-max_kv_len // per))
+
+
+def attention_decode_tma(out, q, source, bias, inv_freq, write_cache, seq_q_start, seq_q_len, seq_kv_len, seq_slot,
+                         block_table, k_pages, v_pages, n_seqs, n_q_heads, n_kv_heads, head_dim, window, scale, nsplit,
+                         scratch, counters, status, merge_in_scratch: bool = False, prefetch: torch.Tensor | None = None,
+                         stages: int = 0) -> None:
+    """Split-KV attention for the requests of the batch that bring one token, keys and values brought in by TMA.
+    Either ``q`` (bf16 [rows, Hq D], 16-byte aligned rows) or ``source`` -- the step's untouched q/k/v product, a
+    ``SplitSum`` or a bf16 [rows, (Hq + 2 Hkv) D] tensor, which the kernel biases, rotates and (``write_cache``)
+    stores itself -- is given.  The other arguments are those of ``attention_decode`` / ``attention_decode_fused``;
+    ``stages`` is the depth of a block's ring of 64-key tiles (0: chosen from the size of the launch)."""
+    import os
+    width = (n_q_heads + 2 * n_kv_heads) * head_dim
+    partial = dense = None
+    nslices = slice_stride = dense_stride = 0
+    if isinstance(source, SplitSum):
+        partial = source.slices
+        _need(partial.is_cuda and partial.dtype == torch.float32 and partial.dim() == 3 and partial.shape[2] == width
+              and partial[0].is_contiguous(), "attention_decode_tma: bad split source")
+        nslices, slice_stride = partial.shape[0], partial.stride(0)
+    elif source is not None:
+        dense = source
+        _need(dense.is_cuda and dense.dtype == torch.bfloat16 and dense.dim() == 2 and dense.shape[1] == width
+              and dense.stride(1) == 1, "attention_decode_tma: the product must be bf16 [rows, (Hq + 2 Hkv) D]")
+        dense_stride = dense.stride(0)
+    else:
+        _need(q is not None and q.is_cuda and q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.data_ptr() % 16 == 0
+              and q.stride(0) % 8 == 0, "attention_decode_tma: q must be bf16 with 16-byte aligned rows")
+    _cuda(out, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, scratch, counters, status,
+          bias, inv_freq, prefetch)
+    _need(decode_tma_supported(out.dtype, head_dim, k_pages.shape[2]) or os.environ.get("TESSWEAVE_DECODE_TMA") == "0",
+          f"attention_decode_tma does not take head size {head_dim} with pages of {k_pages.shape[2]} keys in {out.dtype}")
+    _need(out.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16, "attention_decode_tma: bfloat16 only")
+    _need(n_q_heads % n_kv_heads == 0, "attention: query heads must be a multiple of key/value heads")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape[3] == head_dim
+          and k_pages.shape[1] == n_kv_heads and v_pages.shape == k_pages.shape
+          and k_pages.data_ptr() % 16 == 0 and v_pages.data_ptr() % 16 == 0,
+          "attention: cache pages must be contiguous, 16-byte aligned [pages, kv_heads, page, head_dim]")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: bad block table")
+    _need(out.stride(1) == 1 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0,
+          "attention_decode_tma: output rows must be 8-byte aligned")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == width), "attention_decode_tma: bias must be fp32")
+    _need(inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2),
+          "attention_decode_tma: inv_freq must be fp32 [D/2]")
+    _need(1 <= nsplit <= DECODE_MAX_SPLITS, f"attention_decode_tma: 1 to {DECODE_MAX_SPLITS} slices, not {nsplit}")
+    if nsplit > 1:
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.data_ptr() % 16 == 0
+              and scratch.numel() >= n_seqs * n_q_heads * nsplit * (head_dim + 2), "attention_decode: scratch too small")
+        _need(counters is not None and counters.dtype == torch.int32
+              and counters.numel() >= n_seqs * n_kv_heads * ((n_q_heads // n_kv_heads + 7) // 8),
+              "attention_decode: too few counters")
+    stages = stages or int(os.environ.get("TESSWEAVE_DECODE_STAGES", "0"))
+    code = _fn("attention_decode_tma", "tw_attn_decode_tma", {"TW_HEAD_DIM": head_dim})(
+        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0) if q is not None else 0), _ptr(partial), c_int(nslices),
+        ctypes.c_longlong(slice_stride), _ptr(dense), c_int(dense_stride), _ptr(bias), _ptr(inv_freq),
+        c_int(1 if write_cache else 0), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(seq_slot),
+        _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(n_seqs), c_int(n_q_heads),
+        c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), c_int(window), c_float(scale), c_int(nsplit),
+        c_int(stages), c_int(1 if merge_in_scratch else 0), _ptr(scratch), _ptr(counters), _ptr(status), _ptr(prefetch),
+        ctypes.c_longlong(prefetch.numel() * prefetch.element_size() if prefetch is not None else 0), _stream())
+    _check(code, "attention_decode_tma")
 
 
 def attention_prefill_tcgen05(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, n_seqs,

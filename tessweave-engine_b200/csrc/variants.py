@@ -11,6 +11,7 @@ COMMON_HEAD_DIMS = (16, 32, 64, 128)
 _SPECIALISED: dict[str, list[dict]] = {
     "attention_bf16": [{"TW_HEAD_DIM": d} for d in COMMON_HEAD_DIMS],
     "attention_tcgen05": [{"TW_HEAD_DIM": d} for d in (64, 128)],
+    "attention_decode_tma": [{"TW_HEAD_DIM": d} for d in (64, 128)],
 }
 
 

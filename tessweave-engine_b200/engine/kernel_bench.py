@@ -1,10 +1,13 @@
-"""Per-kernel timings of one decoder layer and the output head, each with its roofline.
+"""Per-operation timings of one decoder layer and the output head, each with its roofline.
 
-Every operation of a decode step (few rows) and of a prompt step (many rows) is run alone, the
-way the engine runs it (the same wrappers, the same routing between hand-written kernels and the
-library), inside a CUDA graph and with its large operands rotated through more copies than the
-L2 cache holds, so that a timing is neither launch-bound nor cache-resident.  A row gives the
-bytes the operation has to move, its FLOPs, the time, and
+Every operation of a decode step (few rows) and of a prompt step (many rows) is run alone by calling the
+engine's own parts -- the attention part's ``project_qkv / attend / project_out``, the feed-forward's
+``gate_up / down``, the norm, the head, the sampler -- built from the model's own spec, so whatever routing
+between hand-written kernels and the library a part does, the table follows it; the name of the kernel that ran
+is read from the launch log, not restated here.  Each call sits inside a CUDA graph, and the large operands
+(weights, cache pages, activations of prompt steps) exist in more copies than the L2 cache holds and are used
+in turn, so that a timing is neither launch-bound nor cache-resident.  A row gives the bytes the operation has
+to move, its FLOPs, the time, and
 
     fraction = max(bytes / HBM peak, FLOPs / tensor peak) / time.
 
@@ -12,14 +15,11 @@ bytes the operation has to move, its FLOPs, the time, and
 """
 from __future__ import annotations
 
-from types import SimpleNamespace
-
 import torch
 
+from ..cache.manager import CacheManager
 from ..csrc import ops
-from ..csrc.ops import SplitSum
-from ..parts.base import Workspace
-from ..parts.linear import linear
+from ..parts.base import Runtime, StepContext, Workspace, build_part
 
 L2_BYTES = 126 * 1024 * 1024
 
@@ -51,17 +51,53 @@ def _copies(nbytes: int) -> int:
     return max(2, min(16, -(-3 * L2_BYTES // max(1, nbytes))))
 
 
-def kernel_table(cfg, batch: int, context: int, prefill_tokens: int, hbm_gbs: float, tflops: float,
+def _kernels_of(thunk) -> str:
+    """Run ``thunk`` once and name the launchers it called."""
+    ops.CALL_LOG = []
+    try:
+        thunk()
+        names = []
+        for name in ops.CALL_LOG:
+            name = name.removeprefix("tw_")
+            if name not in names:
+                names.append(name)
+    finally:
+        ops.CALL_LOG = None
+    return " + ".join(names) or "none"
+
+
+def _context(rt: Runtime, ws: Workspace, status, positions, seq_of_token, slots, q_start, q_len, kv_len) -> StepContext:
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=rt.device)   # noqa: E731
+    return StepContext(runtime=rt, workspace=ws, n_tokens=len(positions), n_seqs=len(slots), token_ids=i32([0] * len(positions)),
+                       positions=i32(positions), seq_of_token=i32(seq_of_token), seq_slot=i32(slots), seq_q_start=i32(q_start),
+                       seq_q_len=i32(q_len), seq_kv_len=i32(kv_len), status=status, host_slot=list(slots),
+                       host_q_start=list(q_start), host_q_len=list(q_len), host_kv_len=list(kv_len), max_q_len=max(q_len),
+                       max_kv_len=max(kv_len), decode_only=all(c == 1 for c in q_len), fixed_shape=True)
+
+
+def _fill(part, std: float = 0.02) -> None:
+    for decl in part.weights():
+        if decl.role == "matrix":
+            decl.dest.normal_(0, std)
+        elif decl.init == "one_plus_normal":
+            decl.dest.fill_(1.0)
+        else:
+            decl.dest.normal_(0, std)
+    part.finalize()
+
+
+def kernel_table(spec, batch: int, context: int, prefill_tokens: int, hbm_gbs: float, tflops: float,
                  page_size: int = 16, only: tuple[str, ...] | None = None) -> list[dict]:
-    """All rows, or with ``only`` the rows whose operation name contains one of the given words."""
+    """All rows for the first layer of ``spec`` (a ``ModelSpec``) and its head, or with ``only`` the rows whose
+    operation name contains one of the given words."""
     dev = torch.device("cuda")
     bf = torch.bfloat16
-    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
-    Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-    qkv_w = (Hq + 2 * Hkv) * D
+    rt = Runtime(dev, bf)
+    block_spec = spec.layers[0].block
+    mixer_spec, ffn_spec, norm_spec = block_spec.params["mixer"], block_spec.params["feed_forward"], block_spec.params["norm1"]
+    H, V = spec.hidden_size, spec.vocab_size
     rows: list[dict] = []
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)   # noqa: E731
 
     def want(name: str) -> bool:
         return only is None or any(word in name for word in only)
@@ -72,137 +108,122 @@ def kernel_table(cfg, batch: int, context: int, prefill_tokens: int, hbm_gbs: fl
                      "gflop": round(flops / 1e9, 2), "floor_us": round(floor, 2), "frac": round(floor / us, 3),
                      "bound": "hbm" if nbytes / (hbm_gbs * 1e9) >= flops / (tflops * 1e12) else "tensor"})
 
-    def product(name, m, n, k, fused_silu=False, out_dtype=None):
-        """x[m, k] @ w[n, k].T the way the engine runs it; weights rotated beyond L2.  With ``fused_silu`` the
-        weights are gate/up rows and the step's SiLU.mul is part of the row where a kernel fuses it."""
-        fused = None
-        x = torch.randn(m, k, device=dev, dtype=bf)
-        probe = torch.empty(n, k, device=dev, dtype=bf)
-        if fused_silu and m <= ops.SMALL_M_LIMIT:
-            fused = "small"
-        elif fused_silu and ops.stream_product_preferred(x, probe, m) and ops.stream_whole_k_balanced(n):
-            fused = "stream"
-        elif fused_silu and ops.pair_product_preferred(x, probe, m):
-            fused = "pair"
-        del probe
-        if fused:
-            name += " + SiLU.mul"
-        if not want(name):
-            return
-        copies = _copies(n * k * 2)
-        ws = [torch.randn(n, k, device=dev, dtype=bf) * 0.02 for _ in range(copies)]
-        ctx = SimpleNamespace(workspace=Workspace(dev), status=status)
-        out_cols = n
-        if fused == "small":
-            out_cols = n // 2
-            out = torch.empty(m, out_cols, device=dev, dtype=bf)
-            calls = [(lambda w=w: ops.gemm_small_m(out, x, w, m, silu_mul_pairs=True)) for w in ws]
-            kernel = "gemm_smallm"
-        elif fused == "stream":
-            out_cols = n // 2
-            out = torch.empty(m, out_cols, device=dev, dtype=bf)
-            calls = [(lambda w=w: ops.gemm_tcgen05_stream(out, x, w, m, status, silu_mul_pairs=True)) for w in ws]
-            kernel = "gemm_tcgen05_stream"
-        elif fused == "pair":
-            out_cols = n // 2
-            out = torch.empty(m, out_cols, device=dev, dtype=bf)
-            calls = [(lambda w=w: ops.gemm_tcgen05_pair(out, x, w, m, status, silu_mul_pairs=True)) for w in ws]
-            kernel = "gemm_tcgen05_pair (2-CTA)"
-        else:
-            calls = [(lambda w=w: linear(ctx, "p", x, w, out_dtype=out_dtype, allow_split=True)) for w in ws]
-            kernel = ("gemm_smallm" if m <= ops.SMALL_M_LIMIT else
-                      "gemm_tcgen05_stream" if ops.stream_product_preferred(x, ws[0], m) else
-                      "gemm_tcgen05 (swap-AB)" if ops.tcgen05_supported(x, ws[0], m) else "library (cuBLAS)")
-        us = _graph_us(calls)
-        out_bytes = m * out_cols * (4 if out_dtype == torch.float32 else 2)
-        add(name, m, us, n * k * 2 + m * k * 2 + out_bytes, 2.0 * m * n * k, kernel)
-        del ws
-        if fused_silu and not fused and want(name.split(":")[0] + ": SiLU.mul"):
-            gu = torch.randn(m, n, device=dev, dtype=bf)
-            act = torch.empty(m, n // 2, device=dev, dtype=bf)
-            us = _graph_us([lambda: ops.silu_mul(act, gu, m, True)], reps=4)
-            add(name.split(":")[0] + ": SiLU.mul", m, us, m * (n // 2) * 2 * 3, 0.0, "silu_mul")
+    def measure(name, m, thunks, nbytes, flops, reps=4):
+        kernel = _kernels_of(thunks[0])
+        add(name, m, _graph_us(thunks, reps), nbytes, flops, kernel)
 
+    wants_mixer = any(want(f"{ph}: {t}") for ph in ("decode", "prefill") for t in ("qkv product", "attention", "o_proj product"))
+    wants_ffn = any(want(f"{ph}: {t}") for ph in ("decode", "prefill") for t in ("gate/up product", "down product"))
     for m, phase in ((batch, "decode"), (prefill_tokens, "prefill")):
-        elementwise = only is None or any(want(f"{phase}: {t}") for t in ("residual add + RMSNorm", "bias + RoPE + cache write",
-                                                                          "attention"))
-        if elementwise:
-            resid = torch.randn(m, H, device=dev)
-            delta = torch.randn(m, H, device=dev, dtype=bf)
-            weight = torch.ones(H, device=dev)
-            out = torch.empty(m, H, device=dev, dtype=bf)
-            us = _graph_us([lambda: ops.add_rmsnorm(out, resid, delta, weight, cfg.rms_norm_eps, m)], reps=8)
-            add(f"{phase}: residual add + RMSNorm", m, us, m * H * (4 + 4 + 2 + 2), 0.0, "add_rmsnorm")
-        product(f"{phase}: qkv product", m, qkv_w, H)
-        if elementwise:
-            # bias + RoPE + cache write, and attention
-            pages = -(-context // page_size) * batch if phase == "decode" else -(-m // page_size)
-            kp = torch.zeros(pages, Hkv, page_size, D, device=dev, dtype=bf)
-            vp = torch.zeros_like(kp)
-            qkv = torch.randn(m, qkv_w, device=dev, dtype=bf)
-            bias = torch.randn(qkv_w, device=dev)
-            inv = (cfg.rope_theta ** (-torch.arange(0, D, 2, dtype=torch.float32) / D)).to(dev)
-            if phase == "decode":
-                blocks = -(-context // page_size)
-                table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(batch, blocks)
-                positions, seq_of = i32([context - 1] * m), i32(list(range(m)))
-                slots = i32(list(range(batch)))
-            else:
-                table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, pages)
-                positions = torch.arange(m, dtype=torch.int32, device=dev)
-                seq_of = torch.zeros(m, dtype=torch.int32, device=dev)
-                slots = i32([0])
-            if phase == "prefill":
-                us = _graph_us([lambda: ops.rope_kv_write(qkv, bias, positions, seq_of, slots, table, inv, kp, vp, m, Hq, Hkv, D,
-                                                          True, status)], reps=8)
-                add(f"{phase}: bias + RoPE + cache write", m, us, m * qkv_w * 2 * 2, 0.0, "rope_kv_write")
-                q = torch.randn(m, Hq * D, device=dev, dtype=bf)
-                ao = torch.empty_like(q)
-                kp.normal_(); vp.normal_()
-                args = (i32([0]), i32([m]), i32([m]), slots, table, kp, vp, 1, m, Hq, Hkv, D, 0, D ** -0.5, False, status)
-                tc5 = ops.prefer_tcgen05_attention(bf, D, page_size, m)
-                fn = ops.attention_prefill_tcgen05 if tc5 else ops.attention_prefill
-                us = _graph_us([lambda: fn(ao, q, *args)], reps=4)
-                add(f"prefill: causal attention, {m} tokens", m, us, m * (Hq + 2 * Hkv) * D * 2 + m * Hq * D * 2,
-                    4.0 * Hq * D * m * (m + 1) / 2, "attn_prefill_tc5 (tcgen05)" if tc5 else "attn_prefill (mma.sync)")
-            else:
-                # decode-only steps: one kernel adds the bias, rotates, writes the new key and value and attends
-                nset = _copies(kp.numel() * 2 * 2)
-                sets = [(torch.randn_like(kp), torch.randn_like(vp)) for _ in range(nset)]
-                ao = torch.empty(m, Hq * D, device=dev, dtype=bf)
-                qs, ql, kl = i32(list(range(m))), i32([1] * m), i32([context] * m)
-                ns = ops.decode_splits(m, Hkv, Hq // Hkv, context)
-                scratch = torch.empty(ops.decode_scratch_floats(Hq, D), device=dev)
-                counters = torch.zeros(ops.decode_counter_ints(m, Hkv, Hq // Hkv), dtype=torch.int32, device=dev)
-                nsl, _ = ops.small_m_split(qkv_w, H)
-                source = SplitSum(torch.randn(nsl, m, qkv_w, device=dev)) if nsl > 1 else qkv
-                calls = [(lambda k=k, v=v: ops.attention_decode_fused(ao, source, bias, inv, True, qs, ql, kl, slots, table, k, v, m,
-                                                                      Hq, Hkv, D, 0, D ** -0.5, ns, scratch, counters, status))
-                         for k, v in sets]
-                us = _graph_us(calls)
-                add(f"decode: bias + RoPE + cache write + attention over {context} keys", m, us,
-                    m * context * Hkv * D * 2 * 2 + nsl * m * qkv_w * 4, 4.0 * m * Hq * D * context,
-                    f"attn_decode fused ({ns} slices)")
-                del sets
-            del kp, vp
-        product(f"{phase}: o_proj product", m, H, Hq * D)
-        product(f"{phase}: gate/up product", m, 2 * I, H, fused_silu=True)
-        product(f"{phase}: down product", m, H, I)
-    product("decode: output matrix (logits, fp32)", batch, V, H, out_dtype=torch.float32)
+        ws = Workspace(dev)
+        if phase == "decode":
+            ctx = _context(rt, ws, status, [context - 1] * m, list(range(m)), list(range(m)), list(range(m)), [1] * m, [context] * m)
+        else:
+            ctx = _context(rt, ws, status, list(range(m)), [0] * m, [0], [0], [m], [m])
+        act_copies = _copies(m * H * 2) if phase == "prefill" else 1
+        hs = [torch.randn(m, H, device=dev, dtype=bf) for _ in range(act_copies)]
+        # ---- residual add + norm
+        if want(f"{phase}: residual add + RMSNorm"):
+            norm = build_part("norm", norm_spec, rt)
+            _fill(norm)
+            n_sets = _copies(m * H * 12)
+            sets = [(torch.randn(m, H, device=dev), torch.randn(m, H, device=dev, dtype=bf), torch.empty(m, H, device=dev, dtype=bf))
+                    for _ in range(n_sets)]
+            measure(f"{phase}: residual add + RMSNorm", m,
+                    [(lambda r=r, d=d, o=o: norm.apply(ctx, o, r, d, m)) for r, d, o in sets], m * H * (4 + 4 + 2 + 2), 0.0, reps=8)
+            del sets
+        # ---- the mixer in its three stages
+        if wants_mixer:
+            first = build_part("mixer", mixer_spec, rt)
+            weight_bytes = first.w_qkv.numel() * 2
+            mixers = [first] + [build_part("mixer", mixer_spec, rt) for _ in range(_copies(weight_bytes) - 1)]
+            for mx in mixers:
+                _fill(mx)
+            Hq, Hkv, D = first.n_heads, first.n_kv_heads, first.head_dim
+            qkv_w = first.qkv_width
+            if want(f"{phase}: qkv product"):
+                measure(f"{phase}: qkv product", m, [(lambda mx=mx, i=i: mx.project_qkv(ctx, hs[i % len(hs)])) for i, mx in enumerate(mixers)],
+                        qkv_w * H * 2 + m * H * 2 + m * qkv_w * 2, 2.0 * m * qkv_w * H)
+            if want(f"{phase}: attention"):
+                requests = batch if phase == "decode" else 1
+                kv_tokens = context if phase == "decode" else m
+                blocks = -(-kv_tokens // page_size)
+                page_bytes = 2 * requests * blocks * page_size * Hkv * D * 2
+                caches = []
+                for _ in range(_copies(page_bytes)):
+                    cache = CacheManager([(first.cache_need(), None)], page_size, requests * blocks, requests, kv_tokens, bf, dev,
+                                         prefix_cache=False)
+                    for g in cache.groups:
+                        g.k.normal_(0, 0.5)
+                        g.v.normal_(0, 0.5)
+                    for _r in range(requests):
+                        cache.ensure(cache.admit(None), kv_tokens)
+                    cache.sync_tables()
+                    caches.append(cache)
+                products = [mixers[0].project_qkv(ctx, hs[0])]
+                if isinstance(products[0], ops.SplitSum):
+                    products = [ops.SplitSum(products[0].slices.clone())]
+                else:
+                    products = [products[0].clone() for _ in range(len(hs))]
+                views = [c.view(0) for c in caches]
+                thunks = [(lambda v=v, i=i: first.attend(ctx, products[i % len(products)], v, True)) for i, v in enumerate(views)]
+                if phase == "decode":
+                    slices = products[0].slices.shape[0] if isinstance(products[0], ops.SplitSum) else 0
+                    measure(f"decode: bias + RoPE + cache write + attention over {context} keys", m, thunks,
+                            m * context * Hkv * D * 2 * 2 + max(slices, 1) * m * qkv_w * (4 if slices else 2), 4.0 * m * Hq * D * context)
+                else:
+                    measure(f"prefill: bias + RoPE + cache write + causal attention, {m} tokens", m, thunks,
+                            m * qkv_w * 2 * 2 + m * Hq * D * 2, 4.0 * Hq * D * m * (m + 1) / 2)
+                del caches, views, thunks
+            if want(f"{phase}: o_proj product"):
+                outs = [torch.randn(m, first.q_size, device=dev, dtype=bf) for _ in range(act_copies)]
+                measure(f"{phase}: o_proj product", m, [(lambda mx=mx, i=i: mx.project_out(ctx, outs[i % len(outs)])) for i, mx in enumerate(mixers)],
+                        H * first.q_size * 2 + m * first.q_size * 2 + m * H * 2, 2.0 * m * H * first.q_size)
+            del mixers, first
+        # ---- the feed-forward in its two stages
+        if wants_ffn:
+            one = build_part("feed_forward", ffn_spec, rt)
+            ffns = [one] + [build_part("feed_forward", ffn_spec, rt) for _ in range(_copies(one.w_gate_up.numel() * 2) - 1)]
+            for f in ffns:
+                _fill(f)
+            inter = one.intermediate
+            if want(f"{phase}: gate/up product"):
+                measure(f"{phase}: gate/up product + SiLU.mul", m, [(lambda f=f, i=i: f.gate_up(ctx, hs[i % len(hs)])) for i, f in enumerate(ffns)],
+                        2 * inter * H * 2 + m * H * 2 + m * inter * 2, 2.0 * m * 2 * inter * H)
+            if want(f"{phase}: down product"):
+                acts = [torch.randn(m, inter, device=dev, dtype=bf) * 0.1 for _ in range(_copies(m * inter * 2) if phase == "prefill" else 1)]
+                measure(f"{phase}: down product", m, [(lambda f=f, i=i: f.down(ctx, acts[i % len(acts)])) for i, f in enumerate(ffns)],
+                        H * inter * 2 + m * inter * 2 + m * H * 2, 2.0 * m * H * inter)
+            del ffns, one
+        del hs
+        torch.cuda.empty_cache()
+    # ---- the head and the sampler of a decode step
+    ws = Workspace(dev)
+    ctx = _context(rt, ws, status, [context - 1] * batch, list(range(batch)), list(range(batch)), list(range(batch)), [1] * batch,
+                   [context] * batch)
+    if want("decode: output matrix"):
+        heads = [build_part("head", spec.head, rt) for _ in range(_copies(V * H * 2))]
+        for hd in heads:
+            _fill(hd)
+        y = torch.randn(batch, H, device=dev, dtype=bf)
+        logits = torch.empty(batch, V, device=dev)
+        measure("decode: output matrix (logits, fp32)", batch, [(lambda hd=hd: hd.forward(ctx, logits, y, batch)) for hd in heads],
+                V * H * 2 + batch * H * 2 + batch * V * 4, 2.0 * batch * V * H)
+        del heads
     if want("decode: greedy sampling"):
-        logits = torch.randn(batch, V, device=dev)
+        sets = [torch.randn(batch, V, device=dev) for _ in range(_copies(batch * V * 4))]
         ids = torch.zeros(batch, dtype=torch.int32, device=dev)
-        us = _graph_us([lambda: ops.sample(ids, logits, batch)], reps=8)
-        add("decode: greedy sampling", batch, us, batch * V * 4, 0.0, "sample")
+        measure("decode: greedy sampling", batch, [(lambda lg=lg: ops.sample(ids, lg, batch)) for lg in sets], batch * V * 4, 0.0, reps=8)
     if int(status) != 0:
         raise RuntimeError(f"a kernel reported status {int(status)} during the kernel table")
     return rows
 
 
 def format_table(rows: list[dict]) -> str:
-    head = f"{'operation':62s} {'rows':>5s} {'kernel':28s} {'us':>9s} {'MB':>9s} {'GFLOP':>9s} {'floor us':>9s} {'frac':>6s}"
+    width = max(28, max(len(r["kernel"]) for r in rows))
+    head = f"{'operation':66s} {'rows':>5s} {'kernel':{width}s} {'us':>9s} {'MB':>9s} {'GFLOP':>9s} {'floor us':>9s} {'frac':>6s}"
     lines = [head, "-" * len(head)]
     for r in rows:
-        lines.append(f"{r['op']:62s} {r['rows']:5d} {r['kernel']:28s} {r['us']:9.2f} {r['mbytes']:9.2f} {r['gflop']:9.2f} "
+        lines.append(f"{r['op']:66s} {r['rows']:5d} {r['kernel']:{width}s} {r['us']:9.2f} {r['mbytes']:9.2f} {r['gflop']:9.2f} "
                      f"{r['floor_us']:9.2f} {r['frac']:6.3f}")
     return "\n".join(lines)

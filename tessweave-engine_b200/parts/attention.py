@@ -58,23 +58,43 @@ class GQAAttention(Mixer):
     def cache_need(self) -> PagedKV:
         return PagedKV(self.n_kv_heads, self.head_dim, self.window)
 
-    def forward(self, ctx: StepContext, h: torch.Tensor, cache, write_cache: bool) -> torch.Tensor:
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache, write_cache: bool):
         if not isinstance(cache, PagedView):
             raise TypeError("gqa_attention needs a paged key/value cache")
+        return self.project_out(ctx, self.attend(ctx, self.project_qkv(ctx, h), cache, write_cache))
+
+    def _fused_decode(self, ctx: StepContext):
+        """The rotation table, if this step's attention kernel adds the bias, rotates, writes the new key and value
+        and attends all by itself (decode-only steps in bfloat16 with a rotary encoding); else None."""
+        table = self.position.fused_rotary_table(self.head_dim)
+        if (table is not None and ctx.decode_only and ops.fused_decode_enabled()
+                and ops.tensor_core_attention_supported(self.runtime.dtype, self.head_dim)):
+            return table
+        return None
+
+    def project_qkv(self, ctx: StepContext, h: torch.Tensor):
+        """h @ [Wq; Wk; Wv].T without the bias: a tensor, or the slices of a split product where the kernel
+        that follows adds them itself (both rotary kernels do)."""
+        rotary = self.position.fused_rotary_table(self.head_dim) is not None
+        # the decode kernel reads the product once per block: up to four slices are one round trip to L2 for it
+        return linear(ctx, "attn.qkv", h, self.w_qkv, allow_split=rotary,
+                      max_slices=4 if self._fused_decode(ctx) is not None else 12)
+
+    def project_out(self, ctx: StepContext, out: torch.Tensor):
+        return linear(ctx, "mixer.delta", out, self.w_o, allow_split=True, small_consumer=True)
+
+    def attend(self, ctx: StepContext, qkv, cache: PagedView, write_cache: bool) -> torch.Tensor:
+        """Bias, position encoding, cache write and attention for the step's rows; [rows, Hq * D]."""
         n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
         table = self.position.fused_rotary_table(self.head_dim)
-        fused_decode = (table is not None and ctx.decode_only and ops.fused_decode_enabled()
-                        and ops.tensor_core_attention_supported(dt, self.head_dim))
-        # the decode kernel reads the product once per block: up to four slices are one round trip to L2 for it
-        qkv = linear(ctx, "attn.qkv", h, self.w_qkv, allow_split=table is not None, max_slices=4 if fused_decode else 12)
         source = None
-        if isinstance(qkv, SplitSum):       # the fused kernel below adds the slices itself
+        if isinstance(qkv, SplitSum):       # the kernels below add the slices themselves
             source, qkv = qkv, ws.get("attn.qkv", (n, self.qkv_width), dt)
         out = ws.get("attn.out", (n, self.q_size), dt)
-        if fused_decode:
+        if self._fused_decode(ctx) is not None:
             # decode-only step: the attention kernel adds the bias, rotates, writes the new key and value and attends
             self._decode(ctx, out, None, cache, fused=(source if source is not None else qkv, table, write_cache))
-            return linear(ctx, "mixer.delta", out, self.w_o, allow_split=True, small_consumer=True)
+            return out
         if table is None:
             # generic path: bias, then the position part's own transformation, then the cache write
             if self.b_qkv is not None:
@@ -88,7 +108,7 @@ class GQAAttention(Mixer):
                           cache.k_pages, cache.v_pages, n, self.n_heads, self.n_kv_heads, self.head_dim,
                           write_cache, ctx.status, source=source)
         self._attend(ctx, out, qkv, cache)
-        return linear(ctx, "mixer.delta", out, self.w_o, allow_split=True, small_consumer=True)
+        return out
 
     def _attend_tensor_cores(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, cache: PagedView) -> None:
         """bfloat16: flash attention for requests with several tokens, split-KV attention for
@@ -109,26 +129,34 @@ class GQAAttention(Mixer):
 
     def _decode(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor | None, cache: PagedView, fused=None) -> None:
         """Split-KV attention for the requests that bring one token; with ``fused`` = (product, rotation table,
-        write_cache) the kernel makes q, k and v of the new token from the product itself."""
-        nsplit = ops.decode_splits(ctx.n_seqs, self.n_kv_heads, self.n_heads // self.n_kv_heads, ctx.max_kv_len)
+        write_cache) the kernel makes q, k and v of the new token from the product itself.  Head sizes that are
+        multiples of 64 take the kernel that is fed by TMA, the others the one that loads keys through registers."""
+        group = self.n_heads // self.n_kv_heads
+        tma = ops.decode_tma_supported(self.runtime.dtype, self.head_dim, cache.page_size)
+        splits = ops.decode_tma_splits if tma else ops.decode_splits
+        nsplit = splits(ctx.n_seqs, self.n_kv_heads, group, ctx.max_kv_len)
         scratch = ctx.workspace.get("attn.decode_scratch", (ops.decode_scratch_floats(self.n_heads, self.head_dim),),
                                     torch.float32)
         counters = ctx.workspace.get(
-            "attn.decode_counters", (ops.decode_counter_ints(ctx.n_seqs, self.n_kv_heads, self.n_heads // self.n_kv_heads),),
-            torch.int32, zero=True)
+            "attn.decode_counters", (ops.decode_counter_ints(ctx.n_seqs, self.n_kv_heads, group),), torch.int32, zero=True)
         window = self.window or 0
-        if fused is not None:
-            product, table, write_cache = fused
+        product, table, write_cache = fused if fused is not None else (None, None, False)
+        prefetch = self.w_o if (fused is not None and ops.weight_prefetch_enabled()) else None
+        if tma:
+            ops.attention_decode_tma(out, q, product, self.b_qkv if fused is not None else None, table, write_cache,
+                                     ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot, cache.block_table,
+                                     cache.k_pages, cache.v_pages, ctx.n_seqs, self.n_heads, self.n_kv_heads, self.head_dim,
+                                     window, self.scale, nsplit, scratch, counters, ctx.status, prefetch=prefetch)
+        elif fused is not None:
             ops.attention_decode_fused(out, product, self.b_qkv, table, write_cache, ctx.seq_q_start, ctx.seq_q_len,
                                        ctx.seq_kv_len, ctx.seq_slot, cache.block_table, cache.k_pages, cache.v_pages,
                                        ctx.n_seqs, self.n_heads, self.n_kv_heads, self.head_dim, window, self.scale,
-                                       nsplit, scratch, counters, ctx.status,
-                                       prefetch=self.w_o if ops.weight_prefetch_enabled() else None)
-            return
-        ops.attention_decode(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
-                             cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, self.n_heads,
-                             self.n_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, counters,
-                             ctx.status)
+                                       nsplit, scratch, counters, ctx.status, prefetch=prefetch)
+        else:
+            ops.attention_decode(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
+                                 cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, self.n_heads,
+                                 self.n_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, counters,
+                                 ctx.status)
 
     def _attend(self, ctx: StepContext, out: torch.Tensor, qkv: torch.Tensor, cache: PagedView) -> None:
         q = qkv[:, : self.q_size]

@@ -40,7 +40,15 @@ class SwiGLU(FeedForward):
                 WeightDecl("up_proj.weight", (i, self.hidden), dest=up),
                 WeightDecl("down_proj.weight", (self.hidden, i), dest=self.w_down)]
 
-    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx: StepContext, h: torch.Tensor):
+        return self.down(ctx, self.gate_up(ctx, h))
+
+    def down(self, ctx: StepContext, act: torch.Tensor):
+        """delta = act @ Wd.T (a tensor, or the slices of the product for the next norm to add)."""
+        return linear(ctx, "ffn.delta", act, self.w_down, allow_split=True, small_consumer=True)
+
+    def gate_up(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        """act = silu(h @ Wg.T) * (h @ Wu.T), by whichever kernel takes the step's number of rows."""
         n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
         act = ws.get("ffn.act", (n, self.intermediate), dt)
         if self.interleaved and ops.small_m_supported(h, self.w_gate_up, n):
@@ -64,4 +72,4 @@ class SwiGLU(FeedForward):
         else:
             gate_up = linear(ctx, "ffn.gate_up", h, self.w_gate_up)
             ops.silu_mul(act, gate_up, n, self.interleaved)
-        return linear(ctx, "ffn.delta", act, self.w_down, allow_split=True, small_consumer=True)
+        return act

@@ -50,6 +50,7 @@ def matmul_nt(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tens
         configure_matmul_precision()
     if not x.is_cuda:
         raise RuntimeError("matrix products run on the GPU only; this engine has no CPU path")
+    ops.note_call("library product (cuBLAS)")
     if out.dtype != x.dtype:
         torch.mm(x, w.t(), out_dtype=out.dtype, out=out)
     else:

@@ -290,9 +290,10 @@ def test_sample_greedy_and_temperature():
 TC_CASES = [(8, 8, 16), (8, 2, 32), (8, 1, 64), (6, 3, 48), (28, 4, 128), (4, 2, 256), (3, 1, 80), (40, 2, 64)]
 
 
-def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None, merge_in_scratch=False, tcgen05=False):
+def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None, merge_in_scratch=False, tcgen05=False,
+                              tma=False, stages=0):
     """rows_of: request -> the consecutive positions it brings; the request holds exactly
-    positions 0..last.  Requests with one row go through the decode kernel."""
+    positions 0..last.  Requests with one row go through the decode kernel (with ``tma`` the one fed by TMA)."""
     o = ops()
     n = sum(len(r) for r in rows_of)
     qd = dev(q.reshape(n, hq * d), torch.bfloat16)
@@ -315,9 +316,14 @@ def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None
         counters = torch.zeros(o.decode_counter_ints(len(rows_of), hkv, hq // hkv), dtype=torch.int32, device="cuda")
         for _ in range(2):      # twice: the counters must come back to zero
             out.fill_(float("nan")) if not any(len(r) > 1 for r in rows_of) else None
-            o.attention_decode(out, qd, q_start, q_len, kv_len, slot, setup["table"], setup["k_pages"], setup["v_pages"],
-                               len(rows_of), hq, hkv, d, window, d ** -0.5, ns, scratch, counters, st,
-                               merge_in_scratch=merge_in_scratch)
+            if tma:
+                o.attention_decode_tma(out, qd, None, None, None, False, q_start, q_len, kv_len, slot, setup["table"],
+                                       setup["k_pages"], setup["v_pages"], len(rows_of), hq, hkv, d, window, d ** -0.5, ns,
+                                       scratch, counters, st, merge_in_scratch=merge_in_scratch, stages=stages)
+            else:
+                o.attention_decode(out, qd, q_start, q_len, kv_len, slot, setup["table"], setup["k_pages"], setup["v_pages"],
+                                   len(rows_of), hq, hkv, d, window, d ** -0.5, ns, scratch, counters, st,
+                                   merge_in_scratch=merge_in_scratch)
         assert int(counters.abs().sum()) == 0
     assert int(st) == 0
     return out.float().cpu().reshape(n, hq, d), qd.float().cpu().reshape(n, hq, d)
@@ -344,9 +350,10 @@ def test_tensor_core_attention_mixed_rows(hq, hkv, d, window):
         cursor += len(r)
 
 
+@pytest.mark.parametrize("tma", [False, True])
 @pytest.mark.parametrize("merge_in_scratch", [False, True])
 @pytest.mark.parametrize("nsplit", [1, 2, 7, 16, 17, 64])
-def test_decode_attention_any_split(nsplit, merge_in_scratch):
+def test_decode_attention_any_split(nsplit, merge_in_scratch, tma):
     """The split count must not matter, also when most slices are empty; neither may the way the
     slices are merged (inside a cluster up to 16 slices, through scratch memory beyond)."""
     hq, hkv, d = 14, 2, 64
@@ -354,21 +361,22 @@ def test_decode_attention_any_split(nsplit, merge_in_scratch):
     setup = paged_setup(lengths, 16, hkv, d, torch.bfloat16, seed=9)
     rows_of = [[n - 1] for n in lengths]
     q = torch.randn(4, hq, d, generator=torch.Generator().manual_seed(1))
-    got, qr = run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, 0, nsplit=nsplit, merge_in_scratch=merge_in_scratch)
+    got, qr = run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, 0, nsplit=nsplit, merge_in_scratch=merge_in_scratch,
+                                        tma=tma)
     for i, r in enumerate(rows_of):
         k = setup["k"][i].to(torch.bfloat16).float(); v = setup["v"][i].to(torch.bfloat16).float()
         assert torch.allclose(got[i:i + 1], dense_attention(qr[i:i + 1], k, v, r), **TOL["bfloat16"]), f"request {i}"
 
 
-@pytest.mark.parametrize("kind", ["decode", "prefill"])
+@pytest.mark.parametrize("kind", ["decode", "decode_tma", "prefill"])
 @pytest.mark.parametrize("where", ["first_of_page", "last_of_page", "position_zero", "tile_edge", "window_edge_inside",
                                    "window_edge_outside"])
 def test_tensor_core_attention_finds_one_far_key(kind, where):
     """As above for the fp32 kernel: one dominating key at a page's first or last slot, at a
     64-key tile's edge, at position 0 and at both sides of a window's edge."""
-    hq, hkv, d, page, n = 4, 2, 32, 16, 400
+    hq, hkv, d, page, n = 4, 2, (64 if kind == "decode_tma" else 32), 16, 400
     window = 0
-    rows = [n - 1] if kind == "decode" else list(range(n - 5, n))
+    rows = [n - 1] if kind.startswith("decode") else list(range(n - 5, n))
     pos = rows[0]
     target = {"first_of_page": 16 * 7, "last_of_page": 16 * 9 + 15, "position_zero": 0, "tile_edge": 63}.get(where)
     if where.startswith("window_edge"):
@@ -383,7 +391,7 @@ def test_tensor_core_attention_finds_one_far_key(kind, where):
     kp[pid, :, target % page] = (direction * 12.0).to(torch.bfloat16).cuda()
     marker = torch.arange(d, dtype=torch.float32) / d + 2.0
     vp[pid, :, target % page] = marker.to(torch.bfloat16).cuda()
-    got, qr = run_tensor_core_attention(setup, [rows], q, hq, hkv, d, window)
+    got, qr = run_tensor_core_attention(setup, [rows], q, hq, hkv, d, window, tma=kind == "decode_tma")
     k = setup["k"][0].clone(); v = setup["v"][0].clone()
     k[target] = direction * 12.0; v[target] = marker
     want = dense_attention(qr, k.to(torch.bfloat16).float(), v.to(torch.bfloat16).float(), rows, window or None)
@@ -722,3 +730,131 @@ def test_decode_attention_fused_with_rotation_and_cache_write(hq, hkv, d, split_
         assert torch.equal(v_a.view(torch.int16), v_b.view(torch.int16)), "values written differ"
         assert not torch.isnan(out_b.float()).any()
         assert torch.equal(out_a.view(torch.int16), out_b.view(torch.int16)), "attention output differs"
+
+
+# ---------------------------------------------------------------------------
+# decode attention fed by TMA
+# ---------------------------------------------------------------------------
+TMA_CASES = [
+    # hq, hkv, d, page
+    (28, 4, 128, 16),       # the benchmark's layer
+    (40, 8, 128, 16),       # groups of five
+    (14, 2, 64, 8),
+    (9, 1, 64, 32),         # nine heads in a group: two head tiles
+    (20, 2, 64, 4),         # sixteen boxes to a tile
+    (4, 2, 256, 16),
+    (6, 1, 128, 64),        # a page is a tile
+    (16, 2, 128, 128),      # a page is two tiles
+]
+
+
+@pytest.mark.parametrize("hq,hkv,d,page", TMA_CASES)
+@pytest.mark.parametrize("window", [0, 40, 100])
+@pytest.mark.parametrize("nsplit,stages", [(1, 2), (3, 0), (5, 3), (17, 2)])
+def test_decode_attention_tma(hq, hkv, d, page, window, nsplit, stages):
+    """Requests of 1 to 1,000 keys on permuted pages whose unused slots hold NaN, every one bringing its newest
+    token: whole, in slices merged inside a cluster and through scratch memory, with windows that start inside a
+    tile, and with rings of two stages (every stage is used many times) up to the deepest."""
+    lengths = [1, 17, 64, 65, 129, 300, 1000]
+    setup = paged_setup(lengths, page, hkv, d, torch.bfloat16, seed=hq + d + page)
+    rows_of = [[n - 1] for n in lengths]
+    q = torch.randn(len(lengths), hq, d, generator=torch.Generator().manual_seed(window + nsplit))
+    for merge_in_scratch in ((False, True) if 1 < nsplit <= 16 else (False,)):
+        got, qr = run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=nsplit, tma=True, stages=stages,
+                                            merge_in_scratch=merge_in_scratch)
+        for i, r in enumerate(rows_of):
+            k = setup["k"][i].to(torch.bfloat16).float(); v = setup["v"][i].to(torch.bfloat16).float()
+            want = dense_attention(qr[i:i + 1], k, v, r, window or None)
+            assert torch.isfinite(got[i]).all(), f"request {i}: a slot that holds no key was read"
+            assert torch.allclose(got[i:i + 1], want, **TOL["bfloat16"]), f"request {i} ({lengths[i]} keys)"
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (20, 2, 64), (4, 2, 256), (9, 1, 64)])
+@pytest.mark.parametrize("split_source", [0, 1, 3, 4, 9])
+@pytest.mark.parametrize("window", [0, 40])
+def test_decode_attention_tma_makes_q_k_v_itself(hq, hkv, d, split_source, window):
+    """The TMA kernel on a decode-only step's untouched q/k/v product: bias, rotation by position, the write of the
+    new key and value and the attention, against the plain formulas (rope and dense attention in fp32 on the CPU)
+    and, for what lands in the cache, bit for bit against the kernel that does only that.  Newest positions at a
+    page's first and last slot, at position 0 and in between; the new key's row reaches the products from the
+    block's own arithmetic, so a copy that read the page before the write cannot matter."""
+    o = ops()
+    lengths = [1, 16 * 9 + 1, 16 * 11, 300, 64]
+    page, theta = 16, 1e4
+    setup = paged_setup(lengths, page, hkv, d, torch.bfloat16, seed=hq + d)
+    n = len(lengths)
+    width = (hq + 2 * hkv) * d
+    g = torch.Generator().manual_seed(3)
+    bias = dev(torch.randn(width, generator=g))
+    inv = dev(theta ** (-torch.arange(0, d, 2, dtype=torch.float32) / d))
+    i32 = lambda v: dev(torch.tensor(v, dtype=torch.int32))
+    q_start, q_len, kv_len, slot = i32(list(range(n))), i32([1] * n), i32(lengths), i32(setup["slots"])
+    positions, seq_of = i32([m - 1 for m in lengths]), i32(list(range(n)))
+    if split_source:
+        slices = dev(torch.randn(split_source, n, width, generator=g))
+        source, dense = o.SplitSum(slices), torch.zeros(n, width, device="cuda", dtype=torch.bfloat16)
+        product = slices.sum(0).cpu()
+    else:
+        dense = dev(torch.randn(n, width, generator=g), torch.bfloat16)
+        source, product = None, dense.float().cpu()
+    scratch = torch.full((o.decode_scratch_floats(hq, d),), float("nan"), device="cuda")
+    counters = torch.zeros(o.decode_counter_ints(n, hkv, hq // hkv), dtype=torch.int32, device="cuda")
+    st = status()
+    # what the plain formulas give
+    x = product + bias.cpu()
+    pos = [m - 1 for m in lengths]
+    q_new = plain_qwen2.rope(x[:, : hq * d].reshape(n, hq, d), pos, theta)
+    k_new = plain_qwen2.rope(x[:, hq * d:(hq + hkv) * d].reshape(n, hkv, d), pos, theta)
+    v_new = x[:, (hq + hkv) * d:].reshape(n, hkv, d)
+    # the cache as the kernel that only writes leaves it
+    k_a, v_a = setup["k_pages"].clone(), setup["v_pages"].clone()
+    o.rope_kv_write(dense.clone(), bias, positions, seq_of, slot, setup["table"], inv, k_a, v_a, n, hq, hkv, d, True, st, source=source)
+    for ns, merge_in_scratch in ((1, False), (3, False), (3, True)):
+        k_b, v_b = setup["k_pages"].clone(), setup["v_pages"].clone()
+        out = torch.full((n, hq * d), float("nan"), device="cuda", dtype=torch.bfloat16)
+        o.attention_decode_tma(out, None, source if source is not None else dense, bias, inv, True, q_start, q_len, kv_len, slot,
+                               setup["table"], k_b, v_b, n, hq, hkv, d, window, d ** -0.5, ns, scratch, counters, st,
+                               merge_in_scratch=merge_in_scratch, prefetch=bias if ns == 1 else None)
+        assert int(st) == 0
+        assert torch.equal(k_a.view(torch.int16), k_b.view(torch.int16)) and torch.equal(v_a.view(torch.int16), v_b.view(torch.int16))
+        got = out.float().cpu().reshape(n, hq, d)
+        for i, m in enumerate(lengths):
+            k = setup["k"][i].clone(); v = setup["v"][i].clone()
+            k[m - 1], v[m - 1] = k_new[i], v_new[i]
+            want = dense_attention(q_new[i:i + 1].to(torch.bfloat16).float(), k.to(torch.bfloat16).float(),
+                                   v.to(torch.bfloat16).float(), [m - 1], window or None)
+            assert torch.allclose(got[i:i + 1], want, **TOL["bfloat16"]), f"request {i} ({m} keys), {ns} slices"
+    # a layer that reads another layer's cache: nothing is written, the newest key is already there
+    k_c, v_c = k_a.clone(), v_a.clone()
+    out_c = torch.full((n, hq * d), float("nan"), device="cuda", dtype=torch.bfloat16)
+    o.attention_decode_tma(out_c, None, source if source is not None else dense, bias, inv, False, q_start, q_len, kv_len, slot,
+                           setup["table"], k_c, v_c, n, hq, hkv, d, window, d ** -0.5, 3, scratch, counters, st)
+    assert torch.equal(k_c.view(torch.int16), k_a.view(torch.int16)) and torch.equal(out_c, out) and int(st) == 0
+
+
+def test_decode_attention_tma_refuses_and_reports():
+    """Shapes the kernel does not take are refused in words; a block table without a page sets the page bit of the
+    status word and the kernel returns (it reads nothing out of bounds)."""
+    o = ops()
+    hq, hkv, d = 4, 2, 64
+    assert not o.decode_tma_supported(torch.bfloat16, 32, 16) and not o.decode_tma_supported(torch.float32, 64, 16)
+    assert not o.decode_tma_supported(torch.bfloat16, 64, 24) and o.decode_tma_supported(torch.bfloat16, 64, 128)
+    setup = paged_setup([100], 16, hkv, d, torch.bfloat16, seed=1)
+    i32 = lambda v: dev(torch.tensor(v, dtype=torch.int32))
+    q = dev(torch.randn(1, hq * d), torch.bfloat16)
+    out = torch.zeros(1, hq * d, device="cuda", dtype=torch.bfloat16)
+    scratch = torch.zeros(o.decode_scratch_floats(hq, d), device="cuda")
+    counters = torch.zeros(o.decode_counter_ints(1, hkv, 2), dtype=torch.int32, device="cuda")
+    args = (i32([0]), i32([1]), i32([100]), i32(setup["slots"]), setup["table"], setup["k_pages"], setup["v_pages"], 1, hq, hkv, d,
+            0, d ** -0.5)
+    with pytest.raises(o.KernelError, match="slices"):
+        o.attention_decode_tma(out, q, None, None, None, False, *args, 129, scratch, counters, status())
+    with pytest.raises(o.KernelError, match="aligned"):
+        o.attention_decode_tma(out, dev(torch.zeros(hq * d + 8), torch.bfloat16)[1:hq * d + 1].view(1, -1), None, None, None, False,
+                               *args, 2, scratch, counters, status())
+    table = setup["table"].clone()
+    table[setup["slots"][0], 3] = -1                         # keys 48..63 have no page
+    st = status()
+    o.attention_decode_tma(out, q, None, None, None, False, args[0], args[1], args[2], args[3], table, *args[5:], 2, scratch,
+                           counters, st)
+    assert int(st) == 2

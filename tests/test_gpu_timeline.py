@@ -52,3 +52,26 @@ def test_timeline_needs_the_switch():
         pytest.skip("the switch is on in this process")
     with pytest.raises(RuntimeError, match="TESSWEAVE_TIMELINE"):
         Timeline()
+
+
+def test_kernel_table_runs_the_parts_own_routes():
+    """The per-operation table is made by calling the parts of a model's spec, and names the kernels from the
+    launch log: at four rows the products run on the small-batch kernel, the attention of a decode step on the
+    kernel fed by TMA (head size 64), and every row carries a positive time and a roofline fraction."""
+    import tessweave_engine_b200 as tw
+    from tessweave_engine_b200.engine.kernel_bench import format_table, kernel_table
+    config = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": 2048, "hidden_size": 512,
+              "intermediate_size": 1408, "num_hidden_layers": 1, "num_attention_heads": 8, "num_key_value_heads": 2,
+              "head_dim": 64, "rope_theta": 1e4, "rms_norm_eps": 1e-6, "max_position_embeddings": 4096,
+              "tie_word_embeddings": False, "use_sliding_window": False, "hidden_act": "silu"}
+    _, spec = tw.resolve(config)
+    rows = kernel_table(spec, 4, 320, 192, 6456.5, 1657.4, page_size=16)
+    by_op = {r["op"]: r for r in rows}
+    assert len(rows) == 2 * 6 + 2 and all(r["us"] > 0 and r["frac"] > 0 for r in rows)
+    assert by_op["decode: gate/up product + SiLU.mul"]["kernel"] == "gemm_smallm"
+    assert "attn_decode_tma" in by_op["decode: bias + RoPE + cache write + attention over 320 keys"]["kernel"]
+    assert "attn_prefill_tc5" in by_op["prefill: bias + RoPE + cache write + causal attention, 192 tokens"]["kernel"]
+    assert "library product" in by_op["prefill: down product"]["kernel"]
+    assert format_table(rows).count("\n") == len(rows) + 1
+    only = kernel_table(spec, 4, 320, 192, 6456.5, 1657.4, page_size=16, only=("gate/up",))
+    assert [r["op"] for r in only] == ["decode: gate/up product + SiLU.mul", "prefill: gate/up product + SiLU.mul"]

@@ -108,3 +108,21 @@ def test_pair_product_only_where_its_tiles_fill_the_pairs():
     assert eff(2048, 37888) == 1.0 and eff(768, 37888) == 1.0
     assert eff(544, 37888) < 0.75                       # padded to 768 rows
     assert eff(1280, 27648) < 0.93 <= eff(1536, 27648)  # 540 tiles: 7.3 rounds of 74 pairs; 648 tiles: 8.76
+
+
+def test_tma_decode_slices_fill_about_two_blocks_per_sm():
+    """The slice count of the TMA decode attention: about 256 blocks for many requests, whole tiles of 64 keys per
+    slice, no slice without keys, at most 128, and within the scratch buffer for any batch."""
+    from tessweave_engine_b200.csrc import ops
+    for batch in (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 200):
+        for keys in (1, 63, 64, 65, 512, 4096, 16384, 100000):
+            n = ops.decode_tma_splits(batch, 4, 7, keys)
+            assert 1 <= n <= min(ops.DECODE_MAX_SPLITS, -(-keys // 64))
+            assert batch * n <= max(batch, ops.DECODE_SCRATCH_UNITS)
+            per = -(-(-(-keys // n)) // 64) * 64
+            assert (n - 1) * per < keys                      # the last slice holds at least one key
+            if batch >= 8 and keys >= 4096:
+                assert n == 1 or batch * 4 * n <= 296        # never more blocks than two per SM, unless one per request is more
+    assert ops.decode_tma_splits(8, 4, 7, 4096) == 8 and ops.decode_tma_splits(64, 4, 7, 4096) == 1
+    assert ops.decode_tma_splits(8, 8, 5, 4096) == 4         # 14B sizes: twice the key/value heads, half the slices
+    assert ops.decode_tma_supported(__import__("torch").bfloat16, 128, 16)
