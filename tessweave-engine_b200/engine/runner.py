@@ -22,6 +22,7 @@ from ..csrc import ops
 from ..models.model import Model
 from ..parts.base import StepContext, Workspace
 from ..parts.linear import configure_matmul_precision, verify_true_fp32
+from ..sampling import select_tokens
 
 
 @dataclass
@@ -274,10 +275,10 @@ class ModelRunner:
         the kernels' status word to the host."""
         m = logits.shape[0]
         if greedy_only:
-            ops.sample(self.sampled, logits, m)
+            select_tokens(self.sampled, logits, m)
         else:
-            ops.sample(self.sampled, logits, m, self._d["temperature"].view(torch.float32),
-                       self._d["seed"].view(torch.int64), self._d["counter"].view(torch.int64))
+            select_tokens(self.sampled, logits, m, self._d["temperature"].view(torch.float32),
+                          self._d["seed"].view(torch.int64), self._d["counter"].view(torch.int64))
         self.sampled[m:m + 1].copy_(self.status)
         self._sampled_host[:m + 1].copy_(self.sampled[:m + 1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
@@ -300,10 +301,10 @@ class ModelRunner:
         self._launched += 1
         if m:
             if all(t == 0 for t in temperature):
-                ops.sample(self.sampled, logits, m)
+                select_tokens(self.sampled, logits, m)
             else:
-                ops.sample(self.sampled, logits, m, self._d["temperature"].view(torch.float32),
-                           self._d["seed"].view(torch.int64), self._d["counter"].view(torch.int64))
+                select_tokens(self.sampled, logits, m, self._d["temperature"].view(torch.float32),
+                              self._d["seed"].view(torch.int64), self._d["counter"].view(torch.int64))
         self.sampled[m:m + 1].copy_(self.status)
         host[:m + 1].copy_(self.sampled[:m + 1], non_blocking=True)
         done = torch.cuda.Event()

@@ -26,6 +26,18 @@ def uniform(seed: int, counter: int) -> float:
     return (z >> 40) / 16777216.0
 
 
+def select_tokens(out: torch.Tensor, logits: torch.Tensor, n_rows: int, temperature: torch.Tensor | None = None,
+                  seed: torch.Tensor | None = None, counter: torch.Tensor | None = None) -> None:
+    """out[r] = the token of row r of fp32 ``logits``, for the first ``n_rows`` rows; everything stays on the device and
+    nothing is allocated, so the call can be captured and can follow a step without a round trip to the host.  Rows
+    whose ``temperature`` is 0 -- all of them without the three tensors (fp32, int64, int64 per row) -- are greedy.
+    This is what the step function calls after every forward pass."""
+    if temperature is None:
+        ops.sample(out, logits, n_rows)
+    else:
+        ops.sample(out, logits, n_rows, temperature, seed, counter)
+
+
 @torch.inference_mode()
 def choose_tokens(logits: torch.Tensor, temperature=None, seed=None, counter=None) -> torch.Tensor:
     """One token id per row of fp32 ``logits`` (on the device).  ``temperature``, ``seed`` and
@@ -33,10 +45,10 @@ def choose_tokens(logits: torch.Tensor, temperature=None, seed=None, counter=Non
     m = logits.shape[0]
     out = torch.empty(m, dtype=torch.int32, device=logits.device)
     if temperature is None:
-        ops.sample(out, logits, m)
+        select_tokens(out, logits, m)
     else:
         t = torch.as_tensor(temperature, dtype=torch.float32).to(logits.device)
         s = torch.as_tensor(seed if seed is not None else [0] * m, dtype=torch.int64).to(logits.device)
         c = torch.as_tensor(counter if counter is not None else [0] * m, dtype=torch.int64).to(logits.device)
-        ops.sample(out, logits, m, t, s, c)
+        select_tokens(out, logits, m, t, s, c)
     return out

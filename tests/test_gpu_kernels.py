@@ -276,6 +276,10 @@ def test_sample_greedy_and_temperature():
     alone = torch.zeros(1, dtype=torch.int32, device="cuda")
     ops().sample(alone, dev(small[4:5]), 1, dev(torch.tensor([0.8])), dev(torch.tensor([11])), dev(torch.tensor([1])))
     assert int(alone) == want[4]
+    # the sampling package's entry point, which the step function uses: the same tokens from plain Python lists
+    from tessweave_engine_b200.sampling import choose_tokens
+    assert choose_tokens(dev(small), temps, seeds, counters).tolist() == want
+    assert choose_tokens(dev(logits)).tolist() == out.tolist()
     # many draws follow the distribution
     row = torch.tensor([[0.0, 1.0, 2.0, -30.0, 0.5]]).repeat(4000, 1)
     out3 = torch.zeros(4000, dtype=torch.int32, device="cuda")
@@ -683,8 +687,11 @@ def test_gemm_tcgen05_stream_refuses_what_it_cannot_do():
 @pytest.mark.parametrize("split_source", [0, 2, 3, 4, 5, 9])
 @pytest.mark.parametrize("window", [0, 40])
 def test_decode_attention_fused_with_rotation_and_cache_write(hq, hkv, d, split_source, window):
-    """The fused kernel against the two kernels it replaces (bias + rotation + cache write, then decode
-    attention): the same attention output and the same cache contents, bit for bit, for requests whose
+    """The fused kernel (the one that loads keys through registers) against the two kernels it replaces (bias +
+    rotation + cache write, then decode attention): strong against the two drifting apart, blind to a fault they
+    share -- that is what test_rope_kv_write (against the plain rotation) and, for the fused arithmetic as a whole,
+    test_decode_attention_tma_makes_q_k_v_itself and the replay tests (against the plain implementation) are for.
+    The same attention output and the same cache contents, bit for bit, for requests whose
     newest position is a page's first slot, its last slot, position 0 and somewhere in between.  The product
     comes as bf16 rows (0) or as that many fp32 slices: up to four are loaded ahead of the keys, more afterwards.
     One of the two runs also asks for a tensor to be prefetched into L2, which changes nothing."""
