@@ -72,7 +72,7 @@ def _context(rt: Runtime, ws: Workspace, status, positions, seq_of_token, slots,
                        positions=i32(positions), seq_of_token=i32(seq_of_token), seq_slot=i32(slots), seq_q_start=i32(q_start),
                        seq_q_len=i32(q_len), seq_kv_len=i32(kv_len), status=status, host_slot=list(slots),
                        host_q_start=list(q_start), host_q_len=list(q_len), host_kv_len=list(kv_len), max_q_len=max(q_len),
-                       max_kv_len=max(kv_len), decode_only=all(c == 1 for c in q_len), fixed_shape=True)
+                       max_kv_len=max(kv_len), decode_only=all(c == 1 for c in q_len), fixed_shape=all(c == 1 for c in q_len))
 
 
 def _fill(part, std: float = 0.02) -> None:
