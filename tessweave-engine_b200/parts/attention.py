@@ -141,7 +141,18 @@ class GQAAttention(Mixer):
             "attn.decode_counters", (ops.decode_counter_ints(ctx.n_seqs, self.n_kv_heads, group),), torch.int32, zero=True)
         window = self.window or 0
         product, table, write_cache = fused if fused is not None else (None, None, False)
-        prefetch = self.w_o if (fused is not None and ops.weight_prefetch_enabled()) else None
+        # While the slices merge, the memory system has little to do: the kernel asks it to bring weights of the
+        # kernels that follow into L2.  Not this part's own output matrix -- the product that reads it starts
+        # fetching it before this kernel has ended -- but the head of what the part after this one streams; and
+        # only where the keys take longer to read than the output matrix, else the two fetches collide.
+        prefetch = None
+        upcoming = ctx.upcoming_weights
+        keys = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
+        cache_bytes = ctx.n_seqs * keys * 2 * self.n_kv_heads * self.head_dim * cache.k_pages.element_size()
+        if (fused is not None and upcoming is not None and upcoming.is_contiguous()
+                and cache_bytes >= ops.weight_prefetch_min_cache_bytes()):
+            head = ops.weight_prefetch_bytes() // upcoming.element_size()
+            prefetch = upcoming.view(-1)[:head] if head else None
         if tma:
             ops.attention_decode_tma(out, q, product, self.b_qkv if fused is not None else None, table, write_cache,
                                      ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot, cache.block_table,

@@ -187,6 +187,7 @@ class StepContext:
     decode_only: bool = False      # every sequence brings exactly one token
     fixed_shape: bool = False      # the launch is being captured: sizes must not depend on host values of this step
     device_tokens: torch.Tensor | None = None   # int32: token ids the previous step left on the device (id -(i+1) -> [i])
+    upcoming_weights: torch.Tensor | None = None  # set by a block: what the part after the running one streams first
 
 
 # ---------------------------------------------------------------------------
@@ -209,6 +210,11 @@ class Part:
 
     def finalize(self) -> None:
         """Called once after every declared weight has been filled."""
+
+    def streamed_first(self) -> torch.Tensor | None:
+        """The contiguous weight this part's forward reads first and from end to end, or None.  A part that runs
+        before it may ask the memory system to bring its head into L2 while its own last blocks finish."""
+        return None
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

@@ -52,6 +52,8 @@ class PreNormBlock(Block):
         n = ctx.n_tokens
         h = ctx.workspace.get("block.h", (n, self.hidden), self.runtime.dtype)
         self.norm1.apply(ctx, h, stream.resid, stream.pending, n)
+        ctx.upcoming_weights = self.feed_forward.streamed_first()
         delta = self.mixer.forward(ctx, h, cache, write_cache)
+        ctx.upcoming_weights = None
         self.norm2.apply(ctx, h, stream.resid, delta, n)
         stream.pending = self.feed_forward.forward(ctx, h)      # whoever normalises next adds it

@@ -43,6 +43,9 @@ class SwiGLU(FeedForward):
     def forward(self, ctx: StepContext, h: torch.Tensor):
         return self.down(ctx, self.gate_up(ctx, h))
 
+    def streamed_first(self) -> torch.Tensor:
+        return self.w_gate_up
+
     def down(self, ctx: StepContext, act: torch.Tensor):
         """delta = act @ Wd.T (a tensor, or the slices of the product for the next norm to add)."""
         return linear(ctx, "ffn.delta", act, self.w_down, allow_split=True, small_consumer=True)
