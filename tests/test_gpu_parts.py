@@ -42,8 +42,11 @@ class ToyDecayMixer(Mixer):
     def cache_need(self):
         return FixedState(self.hidden, torch.float32)
 
+    seen_upcoming = []
+
     def forward(self, ctx, h, cache, write_cache):
         assert isinstance(cache, StateView)
+        self.seen_upcoming.append(ctx.upcoming_weights)     # what the block says the part after this one streams first
         out = ctx.workspace.get("toy.out", (ctx.n_tokens, self.hidden), self.runtime.dtype)
         for slot, start, count in zip(ctx.host_slot, ctx.host_q_start, ctx.host_q_len):
             state = cache.state[slot]
@@ -325,6 +328,11 @@ def test_toy_mixer_with_state_and_routed_feed_forward():
     l1 = runner.step([StepEntry(a.slot, TOKENS[:10], 0, [9]), StepEntry(b.slot, TOKENS[20:23], 0, [2])]).cpu().clone()
     l2 = runner.step([StepEntry(b.slot, TOKENS[23:30], 3, [6]), StepEntry(a.slot, TOKENS[10:11], 10, [0])]).cpu().clone()
     assert float((l1[0] - want[9]).abs().max()) <= 2e-4 and float((l2[1] - want[10]).abs().max()) <= 2e-4
+    # the toy feed-forward names no weight that it streams first, so the mixer before it was told of none;
+    # the SwiGLU of the second layer names its gate/up matrix
+    assert ToyDecayMixer.seen_upcoming and all(t is None for t in ToyDecayMixer.seen_upcoming)
+    swiglu = model.blocks[1].feed_forward
+    assert swiglu.streamed_first() is swiglu.w_gate_up and model.blocks[1].mixer.streamed_first() is None
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
