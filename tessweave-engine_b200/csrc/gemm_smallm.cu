@@ -14,6 +14,10 @@
 // writes fp32 partial sums to scratch memory [slice][token][n]; the kernels that consume the
 // result (residual add + norm, bias + rotary + cache write) add the slices in a fixed order.
 //
+// A caller may name the weights that the kernel after this one streams (`next_weights`): every block asks for
+// its share of them to be brought into L2 when its own stream is over, so that the memory system has work
+// while the last blocks finish and the next kernel starts (gate/up before down, 7B-size layer: 0.7 % of a step).
+//
 // The reference runs these products through a library (nn.Linear: flow_engine/model.py:54,
 // 76-80,201,204).
 #include "common.cuh"
@@ -58,7 +62,7 @@ struct Frag {          // 16 consecutive values of k of one row
 template <int NT, int KS>
 __global__ void __launch_bounds__(WARPS * 32, (NT == 1 ? 5 : 0))
 gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M, int N, int K, int kper,
-                   void* __restrict__ out, int out_mode, int out_stride) {
+                   void* __restrict__ out, int out_mode, int out_stride, const void* next_weights, long long next_bytes) {
     constexpr int TILES = WARPS / KS;                  // 16-row tiles of a block
     __shared__ float s_part[KS > 1 ? TILES * 32 * NT * 4 : 1];
     TW_TIMELINE_SCOPE(TW_K_GEMM_SMALLM);
@@ -147,6 +151,7 @@ gemm_smallm_kernel(const bf16* __restrict__ w, const bf16* __restrict__ x, int M
         }
     }
     tw_grid_launch_dependents_late();     // the stream of weights is over: the next kernel may be scheduled
+    if (threadIdx.x == WARPS * 32 - 1) tw_prefetch_l2_share(next_weights, next_bytes);
     if (KS > 1) {
         // the warps of the later values of k hand their sums to the first warp of their tile
         float* mine = s_part + (tile * 32 + lane) * NT * 4;
@@ -216,8 +221,10 @@ __global__ void reduce_partial_kernel(T* __restrict__ out, const float* __restri
 // (then kper < K); 3: bf16 [M, out_stride] = silu(gate) * up for weights whose rows alternate between eight
 // gate rows and their eight up rows (N a multiple of 16, no split).  K must be a multiple of 8; kper of 32.
 TW_EXPORT int tw_gemm_smallm(const void* w, const void* x, int M, int N, int K, int kper, void* out, int out_mode,
-                             int out_stride, cudaStream_t stream) {
+                             int out_stride, const void* next_weights, long long next_bytes, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
+    if ((uintptr_t)next_weights & 15) return (int)cudaErrorMisalignedAddress;
+    if (!next_weights || next_bytes < 0) next_bytes = 0;
     if (M > 64 || K <= 0 || (K & 7) || kper <= 0 || (kper & 31) || (out_mode & ~OUT_EARLY_DEPENDENTS) < 0 || (out_mode & ~OUT_EARLY_DEPENDENTS) > 3 || ((out_mode & ~OUT_EARLY_DEPENDENTS) == OUT_SILU_MUL && (N & 15)))
         return (int)cudaErrorInvalidValue;
     const int ksplit = (K + kper - 1) / kper;
@@ -235,15 +242,20 @@ TW_EXPORT int tw_gemm_smallm(const void* w, const void* x, int M, int N, int K, 
     const bool pair_warps = M <= 8 && (long)grid.x * grid.y * 10 <= (long)sm_count * 32 && kper >= 512;
     if (pair_warps) {
         grid.x = (N + (WARPS / 2) * 16 - 1) / ((WARPS / 2) * 16);
-        tw_launch(gemm_smallm_kernel<1, 2>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<1, 2>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride,
+                  next_weights, next_bytes);
     } else if (M <= 8)
-        tw_launch(gemm_smallm_kernel<1, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<1, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride,
+                  next_weights, next_bytes);
     else if (M <= 16)
-        tw_launch(gemm_smallm_kernel<2, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<2, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride,
+                  next_weights, next_bytes);
     else if (M <= 32)
-        tw_launch(gemm_smallm_kernel<4, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<4, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride,
+                  next_weights, next_bytes);
     else
-        tw_launch(gemm_smallm_kernel<8, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride);
+        tw_launch(gemm_smallm_kernel<8, 1>, dim3(grid), dim3(WARPS * 32), 0, stream, 1, wp, xp, M, N, K, kper, out, out_mode, out_stride,
+                  next_weights, next_bytes);
     return TW_LAUNCH_CHECK();
 }
 

@@ -48,7 +48,7 @@ template <int BN>
 __global__ void __launch_bounds__(THREADS)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, int n_rows,
                    int m_tokens, int K, int kper, int ksplit, void* __restrict__ out, int out_mode, int out_stride,
-                   int* status) {
+                   int* status, const void* next_weights, long long next_bytes) {
     using C = Config<BN>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -96,6 +96,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     tma_load_2d(a_tile + A_BYTES, &map_x, &full[s], k0, 0);
                 }
             }
+            // this block's last copy is on its way: its share of what the kernel after this one streams may follow
+            if (ok) tw_prefetch_l2_share(next_weights, next_bytes);
             if (!ok) {
                 // wait (bounded) for the copies already in flight, so that none lands after the block has gone
                 for (int j = max(0, it - C::STAGES); j < it; ++j) mbar_wait(&full[j % C::STAGES], (j / C::STAGES) & 1, status);
@@ -195,7 +197,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 template <int BN>
 int launch(const void* w, int n, const void* x, int m, int K, int kper, int ksplit, void* out, int out_mode, int out_stride,
-           int* status, int blocks, cudaStream_t stream) {
+           int* status, int blocks, const void* next_weights, long long next_bytes, cudaStream_t stream) {
     using C = Config<BN>;
     static bool attr_set = false;
     if (!attr_set) {
@@ -207,7 +209,7 @@ int launch(const void* w, int n, const void* x, int m, int K, int kper, int kspl
     if (int e = get_map(w, n, K, BM, &mw)) return e;
     if (int e = get_map(x, m, K, BN, &mx)) return e;
     return tw_launch(gemm_stream_kernel<BN>, dim3(blocks), dim3(THREADS), (size_t)C::SMEM, stream, 1, mw, mx, n, m, K, kper, ksplit,
-                     out, out_mode, out_stride, status);
+                     out, out_mode, out_stride, status, next_weights, next_bytes);
 }
 
 }  // namespace
@@ -217,8 +219,11 @@ int launch(const void* w, int n, const void* x, int m, int K, int kper, int kspl
 // out_mode 0: bf16 [m, out_stride]; 1: fp32 [m, out_stride]; 3: bf16 [m, out_stride] = silu(gate) * up with n / 2
 // columns, for w whose rows come in groups of eight gates followed by their eight ups (n a multiple of 16, no slices).
 TW_EXPORT int tw_gemm_tcgen05_stream(const void* x, const void* w, int m, int n, int k, int kper, void* out, int out_mode,
-                                     int out_stride, int* status, cudaStream_t stream) {
+                                     int out_stride, int* status, const void* next_weights, long long next_bytes,
+                                     cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
+    if ((uintptr_t)next_weights & 15) return (int)cudaErrorMisalignedAddress;
+    if (!next_weights || next_bytes < 0) next_bytes = 0;
     const int mode = out_mode & ~OUT_EARLY_DEPENDENTS;
     if (m > 128 || k <= 0 || (k & 7) || kper <= 0 || (kper & 63) || mode < 0 || mode > 3 ||
         (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
@@ -234,10 +239,10 @@ TW_EXPORT int tw_gemm_tcgen05_stream(const void* x, const void* w, int m, int n,
     }
     const long long items = (long long)((n + BM - 1) / BM) * ksplit;
     const int blocks = (int)(items < sm_count ? items : sm_count);
-    if (m <= 16) return launch<16>(w, n, x, m, k, kper, ksplit, out, out_mode, out_stride, status, blocks, stream);
-    if (m <= 32) return launch<32>(w, n, x, m, k, kper, ksplit, out, out_mode, out_stride, status, blocks, stream);
-    if (m <= 64) return launch<64>(w, n, x, m, k, kper, ksplit, out, out_mode, out_stride, status, blocks, stream);
-    return launch<128>(w, n, x, m, k, kper, ksplit, out, out_mode, out_stride, status, blocks, stream);
+    if (m <= 16) return launch<16>(w, n, x, m, k, kper, ksplit, out, out_mode, out_stride, status, blocks, next_weights, next_bytes, stream);
+    if (m <= 32) return launch<32>(w, n, x, m, k, kper, ksplit, out, out_mode, out_stride, status, blocks, next_weights, next_bytes, stream);
+    if (m <= 64) return launch<64>(w, n, x, m, k, kper, ksplit, out, out_mode, out_stride, status, blocks, next_weights, next_bytes, stream);
+    return launch<128>(w, n, x, m, k, kper, ksplit, out, out_mode, out_stride, status, blocks, next_weights, next_bytes, stream);
 }
 
 TW_EXPORT int tw_gemm_tcgen05_stream_sm_count() {

@@ -398,6 +398,27 @@ def weight_prefetch_bytes() -> int:
     return WEIGHT_PREFETCH_BYTES if mb is None else max(0, int(mb)) << 20
 
 
+PRODUCT_PREFETCH_BYTES = 16 << 20
+
+
+def weight_head(w: torch.Tensor | None, nbytes: int) -> torch.Tensor | None:
+    """The first ``nbytes`` of a contiguous weight as a flat view (all of it if it is smaller), or None."""
+    if w is None or nbytes <= 0 or not w.is_contiguous():
+        return None
+    return w.view(-1)[: nbytes // w.element_size()]
+
+
+def product_prefetch_bytes() -> int:
+    """How much of the next matrix a small-batch product asks into L2 when its own stream of weights ends
+    (gate/up before down).  Measured on a 7B-size layer: 8 to 24 MB are alike, 0.6 to 0.8 % of a step at 1 and 8
+    requests.  Before a product that is resident early (q/k/v behind the norm, the attention's output product)
+    the same request makes the step slower, so only the feed-forward uses it.  TESSWEAVE_PRODUCT_PREFETCH_MB
+    overrides it; 0 switches it off."""
+    import os
+    mb = os.environ.get("TESSWEAVE_PRODUCT_PREFETCH_MB")
+    return PRODUCT_PREFETCH_BYTES if mb is None else max(0, int(mb)) << 20
+
+
 def weight_prefetch_min_cache_bytes() -> int:
     """The attention of a decode step prefetches weights only if it reads at least this much of the cache: a
     shorter kernel ends while the output product still fetches its own matrix, and the prefetch gets in its way
@@ -632,13 +653,17 @@ def small_m_split(n: int, k: int, max_slices: int = 12) -> tuple[int, int]:
 
 
 def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kper: int | None = None,
-                 silu_mul_pairs: bool = False, early_dependents: bool = False) -> None:
+                 silu_mul_pairs: bool = False, early_dependents: bool = False,
+                 prefetch: torch.Tensor | None = None) -> None:
     """out[:m] = x[:m] @ w.T for m <= 64 rows.  ``out`` is bf16 or fp32 [>=m, n]; or, when the
     product is split over k (kper < k), fp32 slices [slices, m, n]; or, with ``silu_mul_pairs``
     (rows of w in groups of eight gates and their eight ups), bf16 [>=m, n / 2] = silu(gate) * up.
     ``early_dependents``: the kernel launched next may become resident while this one runs (it waits for
-    the result itself); worth it when that kernel is small."""
+    the result itself); worth it when that kernel is small.  ``prefetch``: a contiguous, 16-byte aligned tensor
+    that the kernel after this one streams; the blocks ask for it to be brought into L2 when their own stream ends."""
     _cuda(out, x, w)
+    if prefetch is not None:
+        _need(prefetch.is_cuda and prefetch.is_contiguous(), "gemm_small_m: the tensor to prefetch must be contiguous")
     n, k = w.shape
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x.is_contiguous()
           and x.shape[1] == k and k % 8 == 0 and m <= 64, "gemm_small_m: bf16 operands, k a multiple of 8, m <= 64")
@@ -659,7 +684,9 @@ def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kp
     if early_dependents:
         mode |= 16          # the kernel after this one may become resident while this one runs
     code = _fn("gemm_smallm", "tw_gemm_smallm")(_ptr(w), _ptr(x), c_int(m), c_int(n), c_int(k), c_int(kper), _ptr(out),
-                                                c_int(mode), c_int(stride), _stream())
+                                                c_int(mode), c_int(stride), _ptr(prefetch),
+                                                ctypes.c_longlong(prefetch.numel() * prefetch.element_size()
+                                                                  if prefetch is not None else 0), _stream())
     _check(code, "gemm_small_m")
 
 
@@ -793,12 +820,16 @@ def stream_split(n: int, k: int, allow: bool = True, sms: int | None = None) -> 
 
 
 def gemm_tcgen05_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, status: torch.Tensor,
-                        kper: int | None = None, silu_mul_pairs: bool = False, early_dependents: bool = False) -> None:
+                        kper: int | None = None, silu_mul_pairs: bool = False, early_dependents: bool = False,
+                        prefetch: torch.Tensor | None = None) -> None:
     """out[:m] = x[:m] @ w.T for up to 128 rows on the 5th-generation tensor cores, the weights streamed once by a
     persistent kernel.  ``out`` is bf16 or fp32 [>=m, n]; fp32 slices [slices, m, n] when ``kper`` (a multiple of
     64) is less than k; with ``silu_mul_pairs`` (rows of w in groups of eight gates and their eight ups) bf16
-    [>=m, n / 2] = silu(gate) * up."""
+    [>=m, n / 2] = silu(gate) * up.  ``prefetch``: a contiguous, 16-byte aligned tensor that the kernel after
+    this one streams; a block asks for its share of it to be brought into L2 once its own last copy is issued."""
     _cuda(out, x, w, status)
+    if prefetch is not None:
+        _need(prefetch.is_cuda and prefetch.is_contiguous(), "gemm_tcgen05_stream: the tensor to prefetch must be contiguous")
     n, k = w.shape
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x.is_contiguous()
           and x.shape[1] == k and k % 8 == 0 and 0 < m <= STREAM_MAX_M and x.shape[0] >= m,
@@ -823,5 +854,8 @@ def gemm_tcgen05_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: 
         mode |= 16          # the kernel after this one may become resident while this one runs
     # the token rows the kernel reads: exactly m (rows beyond are filled with zeros by the copy engine)
     code = _fn("gemm_tcgen05_stream", "tw_gemm_tcgen05_stream")(_ptr(x), _ptr(w), c_int(m), c_int(n), c_int(k), c_int(kper),
-                                                                _ptr(out), c_int(mode), c_int(stride), _ptr(status), _stream())
+                                                                _ptr(out), c_int(mode), c_int(stride), _ptr(status),
+                                                                _ptr(prefetch), ctypes.c_longlong(
+                                                                    prefetch.numel() * prefetch.element_size()
+                                                                    if prefetch is not None else 0), _stream())
     _check(code, "gemm_tcgen05_stream")

@@ -149,10 +149,9 @@ class GQAAttention(Mixer):
         upcoming = ctx.upcoming_weights
         keys = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
         cache_bytes = ctx.n_seqs * keys * 2 * self.n_kv_heads * self.head_dim * cache.k_pages.element_size()
-        if (fused is not None and upcoming is not None and upcoming.is_contiguous()
+        if (fused is not None and upcoming is not None
                 and cache_bytes >= ops.weight_prefetch_min_cache_bytes()):
-            head = ops.weight_prefetch_bytes() // upcoming.element_size()
-            prefetch = upcoming.view(-1)[:head] if head else None
+            prefetch = ops.weight_head(upcoming, ops.weight_prefetch_bytes())
         if tma:
             ops.attention_decode_tma(out, q, product, self.b_qkv if fused is not None else None, table, write_cache,
                                      ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot, cache.block_table,

@@ -55,12 +55,14 @@ class SwiGLU(FeedForward):
         n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
         act = ws.get("ffn.act", (n, self.intermediate), dt)
         if self.interleaved and ops.small_m_supported(h, self.w_gate_up, n):
-            ops.gemm_small_m(act, h, self.w_gate_up, n, silu_mul_pairs=True)
+            ops.gemm_small_m(act, h, self.w_gate_up, n, silu_mul_pairs=True,
+                             prefetch=ops.weight_head(self.w_down, ops.product_prefetch_bytes()))
         elif (self.interleaved and ops.stream_product_preferred(h, self.w_gate_up, n)
               and (ops.stream_whole_k_balanced(2 * self.intermediate) or ops.stream_split_gate_up_enabled())):
             # decode steps of 9 to 64 requests: persistent tcgen05 kernel, weights as the 128-row operand
             if ops.stream_whole_k_balanced(2 * self.intermediate):
-                ops.gemm_tcgen05_stream(act, h, self.w_gate_up, n, ctx.status, silu_mul_pairs=True)    # SiLU.mul in its epilogue
+                ops.gemm_tcgen05_stream(act, h, self.w_gate_up, n, ctx.status, silu_mul_pairs=True,    # SiLU.mul in its epilogue
+                                        prefetch=ops.weight_head(self.w_down, ops.product_prefetch_bytes()))
             else:
                 # the row tiles alone would leave half of the blocks with half of the work: slices over k, added
                 # by the SiLU.mul kernel
