@@ -16,9 +16,9 @@
 // slice holds that newest position takes the row from its own registers (through shared memory), not from
 // the copy, which may have read the page before the write.
 //
-// Slices of a request merge, in slice order, inside a thread-block cluster through distributed shared
-// memory, or -- when there are more slices than a cluster can hold -- through scratch memory in the block
-// that finishes last.
+// Slices of a request merge, in slice order, inside a thread-block cluster (every block sends its slice to
+// the shared memory of the block that merges those values), or -- when there are more slices than a cluster
+// can hold -- through scratch memory in the block that finishes last.
 //
 //   score = (q . k) * scale,  visible iff  position - window < p <= position
 // Reference: flow_engine/model.py:193-200 and flow_engine/kernels/paged_decode.py:13-43.
@@ -63,15 +63,34 @@ constexpr int HEADS = 8;                           // query heads per block (col
 constexpr int BLKB = TILE * 128;                   // bytes of a [64 keys][64 values of d] swizzled block
 constexpr int STAGE_BYTES = 2 * KB * BLKB;         // K, then V
 constexpr int MAX_STAGES = 8;
-constexpr int STATIC_SMEM_ROOM = 9 * 1024;         // barriers, block-table entries, query heads, alignment slack
+constexpr int STATIC_SMEM_ROOM = 9 * 1024 + HEADS * D * 4;   // barriers, block-table entries, query heads, the cluster's merge, alignment slack
 constexpr int DEEPEST = (227 * 1024 - STATIC_SMEM_ROOM) / STAGE_BYTES < MAX_STAGES ? (227 * 1024 - STATIC_SMEM_ROOM) / STAGE_BYTES : MAX_STAGES;
 constexpr int PAGE_CACHE = 512;                    // block-table entries kept in shared memory
 constexpr int KSTEPS = D / 16;
 constexpr int MT_O = D / 16;                       // m-tiles of O^T
 constexpr int MAX_CLUSTER = 16;
+
+// -DTW_TRACE: the first consumer thread and the producer of every block record the global timer (ns) at
+// their phase boundaries, for a timeline of one launch (tw_attn_decode_tma_trace_ptr gives the buffer:
+// [block][slot]).  Off in the product.
+#ifdef TW_TRACE
+constexpr int TRACE_BLOCKS = 2048, TRACE_SLOTS = 12;
+__device__ long long g_trace[TRACE_BLOCKS * TRACE_SLOTS];
+#define TW_TTRACE(slot)                                                                                      \
+    do {                                                                                                     \
+        const int b_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                       \
+        if ((threadIdx.x & 31) == 0 && b_ < TRACE_BLOCKS) {                                                  \
+            long long t_;                                                                                    \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                           \
+            g_trace[b_ * TRACE_SLOTS + (slot)] = t_;                                                         \
+        }                                                                                                    \
+    } while (0)
+#else
+#define TW_TTRACE(slot) do {} while (0)
+#endif
 constexpr float NEG_INF = -INFINITY;
-// after the last tile the ring holds the warps' partial results and this block's merged slice
-constexpr int MERGE_BYTES = (CWARPS + 1) * HEADS * (D + 2) * 4;
+// after the last tile the ring holds the warps' partial results
+constexpr int MERGE_BYTES = CWARPS * HEADS * (D + 2) * 4;
 constexpr int MIN_STAGES = (MERGE_BYTES + STAGE_BYTES - 1) / STAGE_BYTES < 2 ? 2 : (MERGE_BYTES + STAGE_BYTES - 1) / STAGE_BYTES;
 
 // byte offset of (key row, 16-byte chunk of d) inside a K or V tile of a stage
@@ -99,6 +118,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     __shared__ __align__(16) bf16 s_fresh[2 * D];                 // the newest position's key and value, when this block made them
     __shared__ int s_is_last, s_aborted;
     __shared__ float s_row_max[HEADS];
+    __shared__ float2 s_row_ml[HEADS];                            // this block's (maximum, sum) per head, warps merged
+    // what the other blocks of the cluster send this one to merge: their slices of the groups of four values it
+    // owns, and their maxima and sums.  Of its own, not in the ring: a neighbour may be done before this block is.
+    __shared__ __align__(16) float4 s_recv_o[HEADS * D / 4 + MAX_CLUSTER];
+    __shared__ float2 s_recv_ml[MAX_CLUSTER][HEADS];
 
     const int s = blockIdx.z, kvh = blockIdx.y;
     const int split = blockIdx.x % nsplit, ht = blockIdx.x / nsplit;
@@ -151,6 +175,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         // cache is from earlier steps and may be fetched at once; otherwise the kernel before this one (or
         // one before that) wrote the newest position, and the copies wait for it.
         if (!(FUSED && fq.k_cache)) tw_grid_wait();
+        TW_TTRACE(9);
         const int box_rows = min(page_size, TILE);
         const int boxes = TILE / box_rows;
         int issued = 0;
@@ -186,14 +211,29 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             issued = i + 1;
         }
-        if (*aborted && lane == 0) {
-            // wait (bounded) for the copies already in flight, so that none lands after the block has gone
-            for (int i = max(0, issued - nstages); i < issued; ++i) mbar_wait(&full[i % nstages], (i / nstages) & 1, status);
+        TW_TTRACE(10);
+        // The producer takes no part in the merges.  It arrives at the cluster's one barrier now (it has nothing to
+        // publish) and leaves when its own work is done; the barrier counts the threads that have not exited.
+        if (CLUSTER && nsplit > 1) cg::this_cluster().barrier_arrive();
+        if (lane == 0) {
+            if (*aborted) {
+                // wait (bounded) for the copies already in flight, so that none lands after the block has gone
+                for (int i = max(0, issued - nstages); i < issued; ++i) mbar_wait(&full[i % nstages], (i / nstages) & 1, status);
+            } else if (FUSED && fq.next_weights) {
+                // The last keys and values are on their way.  Once they are in, the memory system has little to do
+                // while the slices merge: it may fetch weights of the kernels that follow.  Asked for from here,
+                // not by a consumer: the requests take a thread one or two microseconds to issue.
+                if (issued > 0) mbar_wait(&full[(issued - 1) % nstages], ((issued - 1) / nstages) & 1, status);
+                tw_prefetch_l2_share(fq.next_weights, fq.next_bytes);
+            }
         }
         if (FUSED && fq.k_cache) tw_grid_wait();
+        return;
     } else {
         // ---- consumers
+        if (warp == 0) TW_TTRACE(0);
         tw_grid_wait();
+        if (warp == 0) TW_TTRACE(1);
         TW_TIMELINE_MARK();
         constexpr int half = D / 2;
         const int width = (Hq + 2 * Hkv) * D;
@@ -263,6 +303,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
         }
         consumer_sync();
+        if (warp == 0) TW_TTRACE(2);
         // q as the B operand: head g, values of d 16 ks + 2c, + 1 and + 8, + 9
         uint32_t qb[KSTEPS][2];
 #pragma unroll
@@ -275,6 +316,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             const int st = i % nstages;
             ok = !*aborted && mbar_wait(&full[st], (i / nstages) & 1, status);
             if (!ok) { *aborted = 1; break; }
+            if (warp == 0 && i == 0) TW_TTRACE(3);
             const int key0 = k_begin + i * TILE + warp * 16;
             if (key0 < k_end && key0 + 16 > first_key) {
                 unsigned char* ks_ = ring + st * STAGE_BYTES;
@@ -355,10 +397,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[st]);
         }
-        // the keys and values are in: while the slices merge, the memory system may fetch the next kernel's weights
-        if constexpr (FUSED) {
-            if (threadIdx.x == 0) tw_prefetch_l2_share(fq.next_weights, fq.next_bytes);
-        }
+        if (warp == 0) TW_TTRACE(4);
         // sums over the keys of the other threads with the same heads
 #pragma unroll
         for (int o = 4; o < 32; o <<= 1) {
@@ -367,120 +406,154 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
     }
 
-    // ---- merge the warps through shared memory (the ring is free: every copy that was issued has been waited for)
-    __syncthreads();
+    // ---- merge the warps (the ring is free: every copy that was issued has been waited for).  The warps exchange
+    // their maxima, each scales its sums to the block's maximum in registers, and the four are added in warp order.
+    // Only the consumer warps are here: the producer has left (see above), so every barrier below is theirs.
+    consumer_sync();
     const bool failed = *aborted != 0;
     float* mo = reinterpret_cast<float*>(ring);                  // [warps][heads][D]
-    float* mml = mo + CWARPS * HEADS * D;                        // [warps][heads][2]
-    if (warp < CWARPS) {
+    float* wml = mo + CWARPS * HEADS * D;                        // [warps][heads][2]
+    if (g == 0) {
+        wml[(warp * HEADS + 2 * c) * 2] = m0; wml[(warp * HEADS + 2 * c) * 2 + 1] = l0;
+        wml[(warp * HEADS + 2 * c + 1) * 2] = m1; wml[(warp * HEADS + 2 * c + 1) * 2 + 1] = l1;
+    }
+    consumer_sync();
+    {
+        float M0 = NEG_INF, M1 = NEG_INF;
+#pragma unroll
+        for (int w = 0; w < CWARPS; ++w) {
+            M0 = fmaxf(M0, wml[(w * HEADS + 2 * c) * 2]);
+            M1 = fmaxf(M1, wml[(w * HEADS + 2 * c + 1) * 2]);
+        }
+        if (failed) M0 = M1 = NEG_INF;
+        const float f0 = (m0 == NEG_INF || M0 == NEG_INF) ? 0.f : exp2f(m0 - M0);
+        const float f1 = (m1 == NEG_INF || M1 == NEG_INF) ? 0.f : exp2f(m1 - M1);
+        float* p0 = mo + (warp * HEADS + 2 * c) * D;
+        float* p1 = p0 + D;
 #pragma unroll
         for (int mt = 0; mt < MT_O; ++mt) {
             const int d = mt * 16 + g;
-            float* p0 = mo + (warp * HEADS + 2 * c) * D;
-            float* p1 = p0 + D;
-            p0[d] = oacc[mt][0]; p1[d] = oacc[mt][1];
-            p0[d + 8] = oacc[mt][2]; p1[d + 8] = oacc[mt][3];
+            p0[d] = oacc[mt][0] * f0; p1[d] = oacc[mt][1] * f1;
+            p0[d + 8] = oacc[mt][2] * f0; p1[d + 8] = oacc[mt][3] * f1;
         }
-        if (g == 0) {
-            mml[(warp * HEADS + 2 * c) * 2] = m0; mml[(warp * HEADS + 2 * c) * 2 + 1] = l0;
-            mml[(warp * HEADS + 2 * c + 1) * 2] = m1; mml[(warp * HEADS + 2 * c + 1) * 2 + 1] = l1;
-        }
-    }
-    float* part_o = mml + CWARPS * HEADS * 2;                    // [heads][D]: this block's slice, for the cluster
-    float* part_ml = part_o + HEADS * D;                         // [heads][2]
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nheads * D; idx += THREADS) {
-        const int row = idx / D, d = idx - row * D;
-        float M = NEG_INF;
-#pragma unroll
-        for (int w = 0; w < CWARPS; ++w) M = fmaxf(M, mml[(w * HEADS + row) * 2]);
-        float L = 0.f, o = 0.f;
-        if (M != NEG_INF && !failed) {
+        if (warp == 0 && g == 0) {
+            float L0 = 0.f, L1 = 0.f;
 #pragma unroll
             for (int w = 0; w < CWARPS; ++w) {
-                const float mw = mml[(w * HEADS + row) * 2];
-                const float f = mw == NEG_INF ? 0.f : exp2f(mw - M);
-                L += mml[(w * HEADS + row) * 2 + 1] * f;
-                o += mo[(w * HEADS + row) * D + d] * f;
+                const float w0 = wml[(w * HEADS + 2 * c) * 2], w1 = wml[(w * HEADS + 2 * c + 1) * 2];
+                L0 += wml[(w * HEADS + 2 * c) * 2 + 1] * ((w0 == NEG_INF || M0 == NEG_INF) ? 0.f : exp2f(w0 - M0));
+                L1 += wml[(w * HEADS + 2 * c + 1) * 2 + 1] * ((w1 == NEG_INF || M1 == NEG_INF) ? 0.f : exp2f(w1 - M1));
             }
-        } else {
-            M = NEG_INF;
+            s_row_ml[2 * c] = make_float2(M0, L0);
+            s_row_ml[2 * c + 1] = make_float2(M1, L1);
+        }
+    }
+    consumer_sync();
+    // Four values of d at a time: the block's slice of (head, d .. d + 3).  It goes to the output (one slice), to
+    // the block of the cluster that merges these four values (see below), or to scratch memory.
+    constexpr int D4 = D / 4;
+    const int n4 = nheads * D4;
+    const int own4 = (n4 + nsplit - 1) / nsplit;                 // groups of four a block of the cluster merges
+    const float4* mo4 = reinterpret_cast<const float4*>(mo);
+    for (int j = threadIdx.x; j < n4; j += CTHREADS) {
+        const int row = j / D4, d4 = j - row * D4;
+        float4 o = mo4[j];
+#pragma unroll
+        for (int w = 1; w < CWARPS; ++w) {
+            const float4 v = mo4[w * HEADS * D4 + j];
+            o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
         }
         const int head = kvh * G + h0 + row;
         if (nsplit == 1) {
-            out[(size_t)n * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+            const float L = s_row_ml[row].y;
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            uint2 packed;
+            packed.x = pack_bf16(o.x * inv, o.y * inv);
+            packed.y = pack_bf16(o.z * inv, o.w * inv);
+            *reinterpret_cast<uint2*>(out + (size_t)n * out_stride + (size_t)head * D + 4 * d4) = packed;
         } else if (CLUSTER) {
-            part_o[row * D + d] = o;
-            if (d == 0) { part_ml[row * 2] = M; part_ml[row * 2 + 1] = L; }
+            cg::cluster_group cluster = cg::this_cluster();
+            *cluster.map_shared_rank(s_recv_o + split * own4 + j / nsplit, j % nsplit) = o;
         } else {
             const size_t at = ((size_t)s * Hq + head) * nsplit + split;
-            partial_o[at * D + d] = o;
-            if (d == 0) { partial_ml[at * 2] = M; partial_ml[at * 2 + 1] = L; }
+            *reinterpret_cast<float4*>(partial_o + at * D + 4 * d4) = o;
+            if (d4 == 0) { partial_ml[at * 2] = s_row_ml[row].x; partial_ml[at * 2 + 1] = s_row_ml[row].y; }
         }
     }
     if (nsplit == 1) return;
+    if (warp == 0) TW_TTRACE(5);
 
     if constexpr (CLUSTER) {
-        // The slices of this (request, head tile) are the blocks of one cluster, slice i being block i.  Every
-        // block merges its share of the outputs, reading all slices in slice order:
-        //   out = sum_i o_i 2^(m_i - M) / sum_i l_i 2^(m_i - M)
+        // The slices of this (request, head tile) are the blocks of one cluster, slice i being block i.  Block r
+        // merges the groups of four values j with j mod nsplit = r: every block has written its slice of them, and
+        // its maxima and sums, into r's shared memory; after the cluster's barrier r reads its own memory only, so
+        // nobody waits for a neighbour before it leaves.
+        //   out = sum_i o_i 2^(m_i - M) / sum_i l_i 2^(m_i - M),   slices added in slice order
         cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();
-        for (int idx = split * THREADS + threadIdx.x; idx < nheads * D; idx += nsplit * THREADS) {
-            const int row = idx / D, d = idx - row * D;
+        for (int t = threadIdx.x; t < nsplit * nheads; t += CTHREADS) {
+            const int r = t / nheads, row = t - r * nheads;
+            *cluster.map_shared_rank(&s_recv_ml[split][row], r) = s_row_ml[row];
+        }
+        cluster.barrier_arrive();
+        cluster.barrier_wait();
+        if (warp == 0) TW_TTRACE(6);
+        for (int e = threadIdx.x; e < own4 * 4; e += CTHREADS) {
+            const int jj = e >> 2, comp = e & 3;
+            const int j = jj * nsplit + split;
+            if (j >= n4) continue;
+            const int row = j / D4, d = (j - row * D4) * 4 + comp;
             float M = NEG_INF;
-            for (int i = 0; i < nsplit; ++i) M = fmaxf(M, *cluster.map_shared_rank(part_ml + row * 2, i));
+            for (int i = 0; i < nsplit; ++i) M = fmaxf(M, s_recv_ml[i][row].x);
             float L = 0.f, o = 0.f;
+            const float* mine = reinterpret_cast<const float*>(s_recv_o) + comp;
             for (int i = 0; i < nsplit; ++i) {
-                const float* ml = cluster.map_shared_rank(part_ml + row * 2, i);
-                const float mi = ml[0];
-                const float f = (mi == NEG_INF || M == NEG_INF) ? 0.f : exp2f(mi - M);
-                L += ml[1] * f;
-                o += *cluster.map_shared_rank(part_o + row * D + d, i) * f;
+                const float2 ml = s_recv_ml[i][row];
+                const float f = (ml.x == NEG_INF || M == NEG_INF) ? 0.f : exp2f(ml.x - M);
+                L += ml.y * f;
+                o += mine[(i * own4 + jj) * 4] * f;
             }
             out[(size_t)n * out_stride + (size_t)(kvh * G + h0 + row) * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
         }
-        cluster.sync();          // nobody leaves while a neighbour may still read its shared memory
+        if (warp == 0) TW_TTRACE(7);
         return;
     }
 
     // The block that finishes last among the slices of this (request, head tile) merges them, in slice order,
     // so the result does not depend on which block that is.
     __threadfence();
-    __syncthreads();
+    consumer_sync();
     int* counter = counters + ((size_t)s * Hkv + kvh) * (gridDim.x / nsplit) + ht;
     if (threadIdx.x == 0) {
         const int done = atomicAdd(counter, 1);
         s_is_last = done == nsplit - 1;
         if (s_is_last) *counter = 0;         // ready for the next launch
     }
-    __syncthreads();
+    consumer_sync();
     if (!s_is_last) return;
     __threadfence();
     float* fac = reinterpret_cast<float*>(ring);                  // [nheads][nsplit]
     float* lsum = fac + HEADS * nsplit;                           // [nheads][nsplit]
     const size_t group_base = ((size_t)s * Hq + kvh * G + h0) * nsplit;      // slices of head h0 start here
-    for (int idx = threadIdx.x; idx < nheads * nsplit; idx += THREADS) {
+    for (int idx = threadIdx.x; idx < nheads * nsplit; idx += CTHREADS) {
         fac[idx] = __ldcg(partial_ml + (group_base + idx) * 2);
         lsum[idx] = __ldcg(partial_ml + (group_base + idx) * 2 + 1);
     }
-    __syncthreads();
+    consumer_sync();
     if (threadIdx.x < nheads) {
         float M = NEG_INF;
         for (int i = 0; i < nsplit; ++i) M = fmaxf(M, fac[threadIdx.x * nsplit + i]);
         s_row_max[threadIdx.x] = M;
     }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nheads * nsplit; idx += THREADS) {
+    consumer_sync();
+    for (int idx = threadIdx.x; idx < nheads * nsplit; idx += CTHREADS) {
         const float M = s_row_max[idx / nsplit];
         const float mi = fac[idx];
         const float f = (mi == NEG_INF || M == NEG_INF) ? 0.f : exp2f(mi - M);
         fac[idx] = f;
         lsum[idx] *= f;
     }
-    __syncthreads();
-    constexpr int D4 = D / 4;
-    for (int idx = threadIdx.x; idx < nheads * D4; idx += THREADS) {
+    consumer_sync();
+    for (int idx = threadIdx.x; idx < nheads * D4; idx += CTHREADS) {
         const int row = idx / D4, d4 = idx - row * D4;
         const float* f = fac + row * nsplit;
         const float4* po = reinterpret_cast<const float4*>(partial_o + (group_base + (size_t)row * nsplit) * D) + d4;
@@ -563,6 +636,13 @@ int g_sm_count = 0;
 
 }  // namespace
 
+#ifdef TW_TRACE
+TW_EXPORT int tw_attn_decode_tma_trace_ptr(void** ptr, int* blocks, int* slots) {
+    *blocks = TRACE_BLOCKS; *slots = TRACE_SLOTS;
+    return (int)cudaGetSymbolAddress(ptr, g_trace);
+}
+#endif
+
 TW_EXPORT int tw_attn_decode_tma_head_dim() { return D; }
 TW_EXPORT int tw_attn_decode_tma_max_splits() { return DEC_MAX_SPLITS; }
 TW_EXPORT int tw_attn_decode_tma_max_stages() { return DEEPEST; }
@@ -602,7 +682,7 @@ TW_EXPORT int tw_attn_decode_tma(void* out, int out_stride, const void* q, int q
     const int G = Hq / Hkv, htiles = (G + HEADS - 1) / HEADS;
     const long long blocks = (long long)nsplit * htiles * Hkv * n_seqs;
     const int deepest = tw_attn_decode_tma_max_stages();
-    if (nstages <= 0) nstages = blocks <= g_sm_count ? deepest : (113 * 1024 - 8 * 1024) / STAGE_BYTES;
+    if (nstages <= 0) nstages = blocks <= g_sm_count ? deepest : (113 * 1024 - STATIC_SMEM_ROOM) / STAGE_BYTES;
     if (nstages > deepest) nstages = deepest;
     if (nstages < MIN_STAGES) nstages = MIN_STAGES;
     const long long rows = (long long)num_pages * Hkv * page_size;
