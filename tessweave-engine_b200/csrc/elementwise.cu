@@ -260,9 +260,10 @@ __device__ __forceinline__ void tw_store4(__nv_bfloat16* p, float4 v) {
 }
 
 // Many rows (prompt portions): four values per thread and access, one pass, values kept in registers.
-// Dense delta only; hidden a multiple of 4 and at most 4 * 256 * TW_NORM_V4 wide.
-#define TW_NORM_V4 8          // float4 per thread: rows up to 8,192 wide
-template <typename T>
+// Dense delta only; hidden a multiple of 4 and at most 4 * 256 * V4 wide.  V4 = float4 per thread: 4 for rows up
+// to 4,096 wide (half the registers, twice the blocks per SM), 8 up to 8,192.
+#define TW_NORM_V4 8
+template <typename T, int V4>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_vec4_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,
                         const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
@@ -275,10 +276,10 @@ add_rmsnorm_vec4_kernel(T* __restrict__ out, float* __restrict__ resid, const T*
     const int src = rows ? rows[r] : r;
     float4* x4 = reinterpret_cast<float4*>(resid + (size_t)src * hidden);
     const int n4 = hidden >> 2;
-    float4 v[TW_NORM_V4];
+    float4 v[V4];
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < TW_NORM_V4; ++j) {
+    for (int j = 0; j < V4; ++j) {
         const int i = threadIdx.x + j * 256;
         v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i < n4) {
@@ -295,7 +296,7 @@ add_rmsnorm_vec4_kernel(T* __restrict__ out, float* __restrict__ resid, const T*
     const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
     const float4* w4 = reinterpret_cast<const float4*>(weight);
 #pragma unroll
-    for (int j = 0; j < TW_NORM_V4; ++j) {
+    for (int j = 0; j < V4; ++j) {
         const int i = threadIdx.x + j * 256;
         if (i < n4) {
             const float4 w = w4[i];
@@ -314,8 +315,12 @@ static int launch_add_rmsnorm(T* out, float* resid, const T* delta, const float*
                          TW_NORM_CLUSTER, out, resid, delta, partial, nsplit, split_stride, weight, eps, hidden, rows);
     }
     if (!partial && (hidden & 3) == 0 && hidden <= 4 * 256 * TW_NORM_V4) {
-        tw_launch(add_rmsnorm_vec4_kernel<T>, dim3(n_rows), dim3(256), 0, stream, 1, out, resid, delta, weight, eps, hidden,
-                  rows);
+        if (hidden <= 4 * 256 * 4)
+            tw_launch(add_rmsnorm_vec4_kernel<T, 4>, dim3(n_rows), dim3(256), 0, stream, 1, out, resid, delta, weight, eps,
+                      hidden, rows);
+        else
+            tw_launch(add_rmsnorm_vec4_kernel<T, TW_NORM_V4>, dim3(n_rows), dim3(256), 0, stream, 1, out, resid, delta, weight,
+                      eps, hidden, rows);
         return TW_LAUNCH_CHECK();
     }
     if (hidden <= TW_NORM_THREADS * TW_NORM_MAXV)

@@ -668,6 +668,43 @@ def test_silu_mul_from_slices(nslices, interleaved, inter):
     assert torch.equal(out, two.to(torch.bfloat16))
 
 
+def test_products_with_a_prefetch_give_the_same_bits_and_refuse_a_misaligned_one():
+    """Asking for the next matrix to be brought into L2 changes no result; a tensor that does not start on a
+    16-byte boundary is refused by the entry point before anything is launched."""
+    g = torch.Generator().manual_seed(5)
+    nxt = dev(torch.randn(300, 72, generator=g), torch.bfloat16)
+    o = ops()
+    assert o.weight_head(nxt, 1 << 10).numel() == 512 and o.weight_head(nxt, 1 << 30).numel() == nxt.numel()
+    assert o.weight_head(nxt, 0) is None and o.weight_head(None, 64) is None and o.weight_head(nxt.t(), 64) is None
+    # the small-M product, plain and with SiLU.mul
+    x = dev(torch.randn(5, 96, generator=g), torch.bfloat16)
+    w = dev(torch.randn(208, 96, generator=g) * 0.1, torch.bfloat16)
+    for silu in (False, True):
+        shape = (5, 104) if silu else (5, 208)
+        a = torch.full(shape, float("nan"), device="cuda", dtype=torch.bfloat16)
+        b = torch.full(shape, float("nan"), device="cuda", dtype=torch.bfloat16)
+        o.gemm_small_m(a, x, w, 5, silu_mul_pairs=silu)
+        o.gemm_small_m(b, x, w, 5, silu_mul_pairs=silu, prefetch=o.weight_head(nxt, 1 << 14))
+        assert torch.equal(a, b) and not torch.isnan(a.float()).any()
+        c = torch.full(shape, float("nan"), device="cuda", dtype=torch.bfloat16)
+        with pytest.raises(RuntimeError, match="gemm_small_m"):
+            o.gemm_small_m(c, x, w, 5, silu_mul_pairs=silu, prefetch=nxt.view(-1)[1:])
+        assert torch.isnan(c.float()).all()
+    # the tcgen05 stream product
+    x = dev(torch.randn(24, 128, generator=g), torch.bfloat16)
+    w = dev(torch.randn(272, 128, generator=g) * 0.1, torch.bfloat16)
+    st = status()
+    a = torch.full((24, 136), float("nan"), device="cuda", dtype=torch.bfloat16)
+    b = torch.full((24, 136), float("nan"), device="cuda", dtype=torch.bfloat16)
+    o.gemm_tcgen05_stream(a, x, w, 24, st, silu_mul_pairs=True)
+    o.gemm_tcgen05_stream(b, x, w, 24, st, silu_mul_pairs=True, prefetch=o.weight_head(nxt, 1 << 14))
+    assert int(st) == 0 and torch.equal(a, b) and not torch.isnan(a.float()).any()
+    c = torch.full((24, 136), float("nan"), device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="gemm_tcgen05_stream"):
+        o.gemm_tcgen05_stream(c, x, w, 24, st, silu_mul_pairs=True, prefetch=nxt.view(-1)[1:])
+    assert torch.isnan(c.float()).all()
+
+
 def test_gemm_tcgen05_stream_refuses_what_it_cannot_do():
     x = dev(torch.randn(130, 64), torch.bfloat16)
     w = dev(torch.randn(32, 64), torch.bfloat16)
