@@ -110,7 +110,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ block_table, int table_stride, int Hq, int Hkv, int page_size,
                         int num_pages, int window, float scale_log2e, int skip_single, int* status) {
     extern __shared__ unsigned char smem_raw[];
+    TW_TIMELINE_SCOPE(TW_K_ATTN_PREFILL);
+    if (threadIdx.x == 0) TW_TRACE_AT(0, 0, 5);
     tw_grid_wait();
+    TW_TIMELINE_MARK();
     // Blocks start in the order of blockIdx.x, and a block's work grows with the position of its rows: x counts
     // (row tile, key/value head) with the head fastest and the last row tile first, so that the longest blocks of
     // all heads start first and the short ones fill the gaps (with the head as blockIdx.y, the long blocks of
@@ -162,23 +165,40 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
 
-    // the block's query rows into shared memory, in the swizzled K-major layout (rows beyond the portion are zero)
-    for (int i = threadIdx.x; i < NQ * BM * (D / 8); i += THREADS) {
-        const int rr = i / (D / 8), c = i - rr * (D / 8);
-        const int r = row0 + rr;
-        uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (r < rows_total) {
-            const int t = r / G;
-            val = *reinterpret_cast<const uint4*>(q + (size_t)(n0 + t) * q_stride + (size_t)(kvh * G + (r - t * G)) * D + c * 8);
+    // the block's query rows into shared memory, in the swizzled K-major layout (rows beyond the portion are zero).
+    // All of a thread's loads are issued before the first store: one round trip to L2, not thirteen in a row
+    // (which was 9 of the 13 us a block spent outside its key tiles).
+    {
+        constexpr int Q_ITEMS = NQ * BM * (D / 8);
+        constexpr int Q_PER_THREAD = (Q_ITEMS + THREADS - 1) / THREADS;
+        uint4 vals[Q_PER_THREAD];
+#pragma unroll
+        for (int j = 0; j < Q_PER_THREAD; ++j) {
+            const int i = threadIdx.x + j * THREADS;
+            const int rr = i / (D / 8), c = i - rr * (D / 8);
+            const int r = row0 + rr;
+            vals[j] = make_uint4(0u, 0u, 0u, 0u);
+            if (i < Q_ITEMS && r < rows_total) {
+                const int t = r / G;
+                vals[j] = *reinterpret_cast<const uint4*>(q + (size_t)(n0 + t) * q_stride + (size_t)(kvh * G + (r - t * G)) * D + c * 8);
+            }
         }
-        const int x = rr / BM, rt = rr - x * BM;
-        *reinterpret_cast<uint4*>(q_s + (x * KB + (c >> 3)) * BLK + rt * 128 + (((c & 7) ^ (rt & 7)) << 4)) = val;
+#pragma unroll
+        for (int j = 0; j < Q_PER_THREAD; ++j) {
+            const int i = threadIdx.x + j * THREADS;
+            if (i < Q_ITEMS) {
+                const int rr = i / (D / 8), c = i - rr * (D / 8);
+                const int x = rr / BM, rt = rr - x * BM;
+                *reinterpret_cast<uint4*>(q_s + (x * KB + (c >> 3)) * BLK + rt * 128 + (((c & 7) ^ (rt & 7)) << 4)) = vals[j];
+            }
+        }
     }
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) TW_TRACE_AT(0, 0, 6);
 
     if (warp == 0) {
         // ---- producer: one TMA box per page (and 64 columns of d); lane b owns box b of a tile
@@ -409,6 +429,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             if (lane == 0) TW_TRACE_AT(warp, i, 4);
         }
         if (ok && ntiles > 0) ok = mbar_wait(&o_done[x], (ntiles - 1) & 1, status);
+        if (lane == 0) TW_TRACE_AT(warp, TRACE_TILES - 1, 0);
         if (!ok) {
             *aborted = 1;
         } else if (ntiles > 0) {
@@ -434,10 +455,12 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             }
         }
     }
+    if (lane == 0) TW_TRACE_AT(warp, TRACE_TILES - 1, 1);
     __syncwarp();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+    if (threadIdx.x == 32) TW_TRACE_AT(0, 0, 7);
 }
 
 }  // namespace
