@@ -163,30 +163,86 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         *aborted = 0;
         mbar_fence_init();
     }
+    // The producer's work for key tile i: one TMA box per page (and 64 columns of d) for the keys, then for the
+    // values; lane b owns box b of a tile.  False if a wait ran out.
+    const int box_rows = min(page_size, BN);
+    const int boxes = BN / box_rows;
+    auto issue_tile = [&](int i) -> bool {
+        const int st = i % KV_STAGES;
+        const uint32_t parity = (i / KV_STAGES) & 1;
+        int row_coord = -1;
+        if (lane < boxes) {
+            const int key0 = (j_begin + i) * BN + lane * box_rows;
+            if (key0 < kv_len) {
+                const int blk = key0 / page_size;
+                const int page = blk < table_stride ? table[blk] : -1;
+                if (page < 0 || page >= num_pages) atomicOr(status, TW_ERR_PAGE);
+                else row_coord = (page * Hkv + kvh) * page_size + (key0 - blk * page_size);
+            }
+        }
+        const uint32_t bytes = (uint32_t)__popc(__ballot_sync(0xffffffffu, row_coord >= 0)) * KB * box_rows * 128;
+        int ok = 1;
+        if (lane == 0) {
+            ok = (!*aborted && mbar_wait(&k_empty[st], parity ^ 1, status)) ? 1 : 0;
+            if (ok) mbar_expect_tx(&k_full[st], bytes); else *aborted = 1;
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return false;
+        if (lane == 0) TW_TRACE_AT(0, i, 0);
+        if (row_coord >= 0) {
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_2d(k_s + st * KV_STAGE_BYTES + kb * BLK + lane * box_rows * 128, &map_k, &k_full[st], kb * 64, row_coord);
+        }
+        if (lane == 0) {
+            ok = (!*aborted && mbar_wait(&v_empty[st], parity ^ 1, status)) ? 1 : 0;
+            if (ok) mbar_expect_tx(&v_full[st], bytes); else *aborted = 1;
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {                                   // K of this tile is in flight: let it land
+            if (lane == 0) mbar_wait(&k_full[st], parity, status);
+            return false;
+        }
+        if (lane == 0) TW_TRACE_AT(1, i, 2);
+        if (row_coord >= 0) {
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_2d(v_s + st * KV_STAGE_BYTES + kb * BLK + lane * box_rows * 128, &map_v, &v_full[st], kb * 64, row_coord);
+        }
+        return true;
+    };
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    // The first key and value tiles need nothing of what follows: the producer warp (whose first thread has just
+    // set up the barriers) asks for them now, and the other warps bring the query rows in meanwhile.
+    int issued = 0;
+    if (warp == 0) {
+        __syncwarp();
+        while (issued < ntiles && issued < KV_STAGES && issue_tile(issued)) ++issued;
+    }
 
     // the block's query rows into shared memory, in the swizzled K-major layout (rows beyond the portion are zero).
     // All of a thread's loads are issued before the first store: one round trip to L2, not thirteen in a row
     // (which was 9 of the 13 us a block spent outside its key tiles).
     {
         constexpr int Q_ITEMS = NQ * BM * (D / 8);
-        constexpr int Q_PER_THREAD = (Q_ITEMS + THREADS - 1) / THREADS;
+        constexpr int Q_THREADS = THREADS - 32;                          // every warp but the producer
+        constexpr int Q_PER_THREAD = (Q_ITEMS + Q_THREADS - 1) / Q_THREADS;
         uint4 vals[Q_PER_THREAD];
 #pragma unroll
         for (int j = 0; j < Q_PER_THREAD; ++j) {
-            const int i = threadIdx.x + j * THREADS;
+            const int i = (int)threadIdx.x - 32 + j * Q_THREADS;
             const int rr = i / (D / 8), c = i - rr * (D / 8);
             const int r = row0 + rr;
             vals[j] = make_uint4(0u, 0u, 0u, 0u);
-            if (i < Q_ITEMS && r < rows_total) {
+            if (warp != 0 && i < Q_ITEMS && r < rows_total) {
                 const int t = r / G;
                 vals[j] = *reinterpret_cast<const uint4*>(q + (size_t)(n0 + t) * q_stride + (size_t)(kvh * G + (r - t * G)) * D + c * 8);
             }
         }
 #pragma unroll
         for (int j = 0; j < Q_PER_THREAD; ++j) {
-            const int i = threadIdx.x + j * THREADS;
-            if (i < Q_ITEMS) {
+            const int i = (int)threadIdx.x - 32 + j * Q_THREADS;
+            if (warp != 0 && i < Q_ITEMS) {
                 const int rr = i / (D / 8), c = i - rr * (D / 8);
                 const int x = rr / BM, rt = rr - x * BM;
                 *reinterpret_cast<uint4*>(q_s + (x * KB + (c >> 3)) * BLK + rt * 128 + (((c & 7) ^ (rt & 7)) << 4)) = vals[j];
@@ -201,54 +257,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     if (threadIdx.x == 0) TW_TRACE_AT(0, 0, 6);
 
     if (warp == 0) {
-        // ---- producer: one TMA box per page (and 64 columns of d); lane b owns box b of a tile
-        const int box_rows = min(page_size, BN);
-        const int boxes = BN / box_rows;
-        int issued = 0;
-        for (int i = 0; i < ntiles; ++i) {
-            const int st = i % KV_STAGES;
-            const uint32_t parity = (i / KV_STAGES) & 1;
-            int row_coord = -1;
-            if (lane < boxes) {
-                const int key0 = (j_begin + i) * BN + lane * box_rows;
-                if (key0 < kv_len) {
-                    const int blk = key0 / page_size;
-                    const int page = blk < table_stride ? table[blk] : -1;
-                    if (page < 0 || page >= num_pages) atomicOr(status, TW_ERR_PAGE);
-                    else row_coord = (page * Hkv + kvh) * page_size + (key0 - blk * page_size);
-                }
-            }
-            const uint32_t bytes = (uint32_t)__popc(__ballot_sync(0xffffffffu, row_coord >= 0)) * KB * box_rows * 128;
-            int ok = 1;
-            if (lane == 0) {
-                ok = (!*aborted && mbar_wait(&k_empty[st], parity ^ 1, status)) ? 1 : 0;
-                if (ok) mbar_expect_tx(&k_full[st], bytes); else *aborted = 1;
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            if (lane == 0) TW_TRACE_AT(0, i, 0);
-            if (row_coord >= 0) {
-#pragma unroll
-                for (int kb = 0; kb < KB; ++kb)
-                    tma_load_2d(k_s + st * KV_STAGE_BYTES + kb * BLK + lane * box_rows * 128, &map_k, &k_full[st], kb * 64, row_coord);
-            }
-            if (lane == 0) {
-                ok = (!*aborted && mbar_wait(&v_empty[st], parity ^ 1, status)) ? 1 : 0;
-                if (ok) mbar_expect_tx(&v_full[st], bytes); else *aborted = 1;
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) {                                   // K of this tile is in flight: let it land
-                if (lane == 0) mbar_wait(&k_full[st], parity, status);
-                break;
-            }
-            if (lane == 0) TW_TRACE_AT(1, i, 2);
-            if (row_coord >= 0) {
-#pragma unroll
-                for (int kb = 0; kb < KB; ++kb)
-                    tma_load_2d(v_s + st * KV_STAGE_BYTES + kb * BLK + lane * box_rows * 128, &map_v, &v_full[st], kb * 64, row_coord);
-            }
-            issued = i + 1;
-        }
+        // ---- producer: the remaining tiles, each as soon as its stage is free
+        while (issued < ntiles && !*aborted && issue_tile(issued)) ++issued;
         if (tail_rows && issued == ntiles) {
             // The last tile reaches past the request's last key.  What its value rows hold there (the rest
             // of a page, or whatever the stage held before) must not reach a product, since 0 x NaN is NaN:
