@@ -61,7 +61,7 @@ class GQAAttention(Mixer):
     def forward(self, ctx: StepContext, h: torch.Tensor, cache, write_cache: bool):
         if not isinstance(cache, PagedView):
             raise TypeError("gqa_attention needs a paged key/value cache")
-        return self.project_out(ctx, self.attend(ctx, self.project_qkv(ctx, h), cache, write_cache))
+        return self.project_out(ctx, self.attend(ctx, self.project_qkv(ctx, h, cache), cache, write_cache))
 
     def _fused_decode(self, ctx: StepContext):
         """The rotation table, if this step's attention kernel adds the bias, rotates, writes the new key and value
@@ -72,16 +72,30 @@ class GQAAttention(Mixer):
             return table
         return None
 
-    def project_qkv(self, ctx: StepContext, h: torch.Tensor):
+    def project_qkv(self, ctx: StepContext, h: torch.Tensor, cache: PagedView | None = None):
         """h @ [Wq; Wk; Wv].T without the bias: a tensor, or the slices of a split product where the kernel
-        that follows adds them itself (both rotary kernels do)."""
+        that follows adds them itself (both rotary kernels do).  With the cache the attention will read, the
+        product knows how large that launch will be and lets a small one settle on the SMs while it runs."""
         rotary = self.position.fused_rotary_table(self.head_dim) is not None
+        fused = self._fused_decode(ctx) is not None
+        early = False
+        if fused and cache is not None:
+            tma, nsplit, blocks = self._decode_launch(ctx, cache)
+            early = tma and ops.decode_attention_resident_early(blocks, nsplit)
         # the decode kernel reads the product once per block: up to four slices are one round trip to L2 for it
-        return linear(ctx, "attn.qkv", h, self.w_qkv, allow_split=rotary,
-                      max_slices=4 if self._fused_decode(ctx) is not None else 12)
+        return linear(ctx, "attn.qkv", h, self.w_qkv, allow_split=rotary, max_slices=4 if fused else 12,
+                      consumer_early=early)
+
+    def _decode_launch(self, ctx: StepContext, cache: PagedView) -> tuple[bool, int, int]:
+        """(fed by TMA?, slices per request, blocks) of the decode attention this step will launch."""
+        group = self.n_heads // self.n_kv_heads
+        tma = ops.decode_tma_supported(self.runtime.dtype, self.head_dim, cache.page_size)
+        splits = ops.decode_tma_splits if tma else ops.decode_splits
+        nsplit = splits(ctx.n_seqs, self.n_kv_heads, group, ctx.max_kv_len)
+        return tma, nsplit, ctx.n_seqs * self.n_kv_heads * -(-group // 8) * nsplit
 
     def project_out(self, ctx: StepContext, out: torch.Tensor):
-        return linear(ctx, "mixer.delta", out, self.w_o, allow_split=True, small_consumer=True)
+        return linear(ctx, "mixer.delta", out, self.w_o, allow_split=True, consumer_early=True)
 
     def attend(self, ctx: StepContext, qkv, cache: PagedView, write_cache: bool) -> torch.Tensor:
         """Bias, position encoding, cache write and attention for the step's rows; [rows, Hq * D]."""
@@ -132,9 +146,7 @@ class GQAAttention(Mixer):
         write_cache) the kernel makes q, k and v of the new token from the product itself.  Head sizes that are
         multiples of 64 take the kernel that is fed by TMA, the others the one that loads keys through registers."""
         group = self.n_heads // self.n_kv_heads
-        tma = ops.decode_tma_supported(self.runtime.dtype, self.head_dim, cache.page_size)
-        splits = ops.decode_tma_splits if tma else ops.decode_splits
-        nsplit = splits(ctx.n_seqs, self.n_kv_heads, group, ctx.max_kv_len)
+        tma, nsplit, _ = self._decode_launch(ctx, cache)
         scratch = ctx.workspace.get("attn.decode_scratch", (ops.decode_scratch_floats(self.n_heads, self.head_dim),),
                                     torch.float32)
         counters = ctx.workspace.get(

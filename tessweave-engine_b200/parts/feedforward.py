@@ -48,7 +48,7 @@ class SwiGLU(FeedForward):
 
     def down(self, ctx: StepContext, act: torch.Tensor):
         """delta = act @ Wd.T (a tensor, or the slices of the product for the next norm to add)."""
-        return linear(ctx, "ffn.delta", act, self.w_down, allow_split=True, small_consumer=True)
+        return linear(ctx, "ffn.delta", act, self.w_down, allow_split=True, consumer_early=True)
 
     def gate_up(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         """act = silu(h @ Wg.T) * (h @ Wu.T), by whichever kernel takes the step's number of rows."""

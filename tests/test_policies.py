@@ -126,3 +126,21 @@ def test_tma_decode_slices_fill_about_two_blocks_per_sm():
     assert ops.decode_tma_splits(8, 4, 7, 4096) == 8 and ops.decode_tma_splits(64, 4, 7, 4096) == 1
     assert ops.decode_tma_splits(8, 8, 5, 4096) == 4         # 14B sizes: twice the key/value heads, half the slices
     assert ops.decode_tma_supported(__import__("torch").bfloat16, 128, 16)
+
+
+def test_small_decode_launches_become_resident_early(monkeypatch):
+    """The q/k/v product lets the decode attention settle on the SMs while it runs only where that launch leaves
+    most of the GPU free, or does not merge in clusters; at the benchmark's 7B sizes that is 1 to 3 requests."""
+    monkeypatch.delenv("TESSWEAVE_DECODE_EARLY", raising=False)
+    monkeypatch.delenv("TESSWEAVE_DECODE_SPLITS", raising=False)
+    early = {}
+    for batch in (1, 2, 3, 4, 8, 64):
+        ns = ops.decode_tma_splits(batch, 4, 7, 4096)
+        early[batch] = ops.decode_attention_resident_early(batch * 4 * ns, ns)
+    assert early == {1: True, 2: True, 3: True, 4: False, 8: False, 64: False}
+    ns = ops.decode_tma_splits(2, 4, 7, 16384)
+    assert ns > ops.DECODE_TMA_CLUSTER_SLICES and ops.decode_attention_resident_early(2 * 4 * ns, ns)
+    monkeypatch.setenv("TESSWEAVE_DECODE_EARLY", "0")
+    assert not ops.decode_attention_resident_early(4, 1)
+    monkeypatch.setenv("TESSWEAVE_DECODE_EARLY", "1")
+    assert ops.decode_attention_resident_early(10_000, 2)
