@@ -95,7 +95,25 @@ class GQAAttention(Mixer):
         return tma, nsplit, ctx.n_seqs * self.n_kv_heads * -(-group // 8) * nsplit
 
     def project_out(self, ctx: StepContext, out: torch.Tensor):
-        return linear(ctx, "mixer.delta", out, self.w_o, allow_split=True, consumer_early=True)
+        return linear(ctx, "mixer.delta", out, self.w_o, allow_split=True, consumer_early=True,
+                      prefetch=self._prefetch_plan(ctx)[1])
+
+    def _prefetch_plan(self, ctx: StepContext):
+        """What a decode-only step asks into L2 ahead of its kernel, of the weights the part after this one
+        streams first (``ctx.upcoming_weights``): (the attention kernel's share, the output product's share).
+        While the attention's slices merge and while the output product ends, the memory system has little to do.
+        Not this part's own output matrix (the product that reads it starts fetching it before the attention has
+        ended); and the attention only asks where its keys take longer to read than the output matrix, else the
+        two fetches collide."""
+        upcoming = ctx.upcoming_weights
+        if upcoming is None or self._fused_decode(ctx) is None:
+            return None, None
+        window = self.window or 0
+        keys = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
+        cache_bytes = ctx.n_seqs * keys * 2 * self.n_kv_heads * self.head_dim * self.w_qkv.element_size()   # the cache has the weights' type
+        first = ops.weight_prefetch_bytes() if cache_bytes >= ops.weight_prefetch_min_cache_bytes() else 0
+        return (ops.weight_head(upcoming, first),
+                ops.weight_head(upcoming, ops.output_product_prefetch_bytes(), skip_bytes=first))
 
     def attend(self, ctx: StepContext, qkv, cache: PagedView, write_cache: bool) -> torch.Tensor:
         """Bias, position encoding, cache write and attention for the step's rows; [rows, Hq * D]."""
@@ -153,17 +171,7 @@ class GQAAttention(Mixer):
             "attn.decode_counters", (ops.decode_counter_ints(ctx.n_seqs, self.n_kv_heads, group),), torch.int32, zero=True)
         window = self.window or 0
         product, table, write_cache = fused if fused is not None else (None, None, False)
-        # While the slices merge, the memory system has little to do: the kernel asks it to bring weights of the
-        # kernels that follow into L2.  Not this part's own output matrix -- the product that reads it starts
-        # fetching it before this kernel has ended -- but the head of what the part after this one streams; and
-        # only where the keys take longer to read than the output matrix, else the two fetches collide.
-        prefetch = None
-        upcoming = ctx.upcoming_weights
-        keys = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
-        cache_bytes = ctx.n_seqs * keys * 2 * self.n_kv_heads * self.head_dim * cache.k_pages.element_size()
-        if (fused is not None and upcoming is not None
-                and cache_bytes >= ops.weight_prefetch_min_cache_bytes()):
-            prefetch = ops.weight_head(upcoming, ops.weight_prefetch_bytes())
+        prefetch = self._prefetch_plan(ctx)[0] if fused is not None else None
         if tma:
             ops.attention_decode_tma(out, q, product, self.b_qkv if fused is not None else None, table, write_cache,
                                      ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot, cache.block_table,

@@ -59,7 +59,8 @@ def matmul_nt(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tens
 
 
 def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-           allow_split: bool = False, consumer_early: bool = False, max_slices: int = 12):
+           allow_split: bool = False, consumer_early: bool = False, max_slices: int = 12,
+           prefetch: torch.Tensor | None = None):
     """``x @ w.T`` into the workspace buffer ``name``.
 
     Steps with up to 8 rows (decode) in bfloat16 go through the weight-streaming kernel of
@@ -70,7 +71,8 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
     to add.  Everything else is a library product.  ``consumer_early``: the weight-streaming kernel lets the kernel
     that follows become resident while it runs (that kernel waits for the result itself).  It pays where the
     follower is small (a norm, a sampler) or leaves most of the GPU free; the caller knows which.
-    ``max_slices``: the most slices the consumer of a ``SplitSum`` wants to add.
+    ``max_slices``: the most slices the consumer of a ``SplitSum`` wants to add.  ``prefetch``: weights of a
+    later kernel that the weight-streaming kernels ask into L2 when their own stream ends (the library ignores it).
     """
     m, n = x.shape[0], w.shape[0]
     dtype = out_dtype or x.dtype
@@ -80,24 +82,25 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
         split, kper = ops.stream_split(n, w.shape[1])
         if split > 1 and allow_split:
             slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
-            ops.gemm_tcgen05_stream(slices, x, w, m, ctx.status, kper=kper, early_dependents=consumer_early)
+            ops.gemm_tcgen05_stream(slices, x, w, m, ctx.status, kper=kper, early_dependents=consumer_early,
+                                    prefetch=prefetch)
             return SplitSum(slices)
         if split == 1:
             out = ctx.workspace.get(name, (m, n), dtype)
-            ops.gemm_tcgen05_stream(out, x, w, m, ctx.status, early_dependents=consumer_early)
+            ops.gemm_tcgen05_stream(out, x, w, m, ctx.status, early_dependents=consumer_early, prefetch=prefetch)
             return out
         # slices that nobody would add: the library's product below, which reduces its own split inside the kernel
     if x.is_cuda and ops.small_m_supported(x, w, m):
         split, kper = ops.small_m_split(n, w.shape[1], max_slices if allow_split else 12)
         if split > 1 and allow_split:
             slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
-            ops.gemm_small_m(slices, x, w, m, kper, early_dependents=consumer_early)
+            ops.gemm_small_m(slices, x, w, m, kper, early_dependents=consumer_early, prefetch=prefetch)
             return SplitSum(slices)
         if split > 1:
             slices = ctx.workspace.get(name + ".slices", (split, m, n), torch.float32)
             ops.gemm_small_m(slices, x, w, m, kper)
             return SplitSum(slices).dense(dtype, ctx.workspace.get(name, (m, n), dtype))
         out = ctx.workspace.get(name, (m, n), dtype)
-        ops.gemm_small_m(out, x, w, m, early_dependents=consumer_early)
+        ops.gemm_small_m(out, x, w, m, early_dependents=consumer_early, prefetch=prefetch)
         return out
     return matmul_nt(ctx.workspace.get(name, (m, n), dtype), x, w)
