@@ -109,3 +109,27 @@ def test_long_portions_against_plain(dtype, how, medium, tmp_path, monkeypatch):
         worst = max(float(np.abs(rows[(rid, p)] - want[rid][p]).max()) for p in got)
         note_error("long_portions", f"{dtype}/{how}/{rid}", worst, scale)
         assert worst <= tol, f"{dtype} {how} request {rid}: off by {worst:.3e}"
+
+
+@pytest.fixture(scope="module")
+def model_7b(tmp_path_factory):
+    folder = tw.write_random_model(tmp_path_factory.mktemp("graphs") / "7b", BIG, seed=6)
+    return tw.load_model(folder, "bfloat16", "cuda")
+
+
+@pytest.mark.parametrize("n_requests", [1, 3, 8])
+def test_graph_steps_at_benchmark_sizes_equal_eager_steps(n_requests, model_7b):
+    """Decode steps replayed from CUDA graphs launch every kernel with programmatic serialization: kernels are
+    resident before the one before them has ended, the q/k/v product lets a small attention launch start early,
+    and the attention, its output product and the gate/up product ask for later weights.  None of that may change
+    a token: the same requests, generated with graphs and kernel by kernel, at the 7B layer sizes (the TMA decode
+    attention, clusters, split products) and with a context long enough for every prefetch to be issued."""
+    model = model_7b
+    prompts = [random_tokens(BIG["vocab_size"], 30 + 7 * i, 90 + i) for i in range(n_requests)]
+    outs = []
+    for graphs in (True, False):
+        cfg = tw.EngineConfig(block_size=16, kv_blocks=64 * n_requests + 8, max_context=1024, max_active=n_requests,
+                              prefill_chunk=256, cuda_graphs=graphs)
+        outs.append(tw.generate(model, prompts, max_tokens=16, ignore_eos=True, engine_config=cfg))
+    assert outs[0] == outs[1]
+    assert all(len(o) == 16 for o in outs[0])
