@@ -410,15 +410,16 @@ def weight_head(w: torch.Tensor | None, nbytes: int, skip_bytes: int = 0) -> tor
     return part if part.numel() else None
 
 
-OUTPUT_PRODUCT_PREFETCH_BYTES = 32 << 20
+OUTPUT_PRODUCT_PREFETCH_BYTES = 24 << 20
 
 
 def output_product_prefetch_bytes() -> int:
     """How much more of the feed-forward's first matrix the attention's output product asks into L2 when its own
     stream of weights ends, after what the attention kernel asked for.  The feed-forward's product is resident by
     then and fetches its first rows itself; these are rows it reaches later.  Measured on a 7B-size layer, whole
-    decode steps: 8 / 16 / 32 / 48 / 64 / 96 MB give 0.6 / 1.0 / 1.2 / 1.1 / 0.6 / 0 % at 8 requests and the same
-    at one.  TESSWEAVE_OUTPUT_PREFETCH_MB overrides it; 0 switches it off."""
+    decode steps: 8 / 16 / 24 / 32 / 48 / 64 / 96 MB give 0.6 / 1.0 / 1.2 / 1.2 / 1.1 / 0.6 / 0 % at 8 requests and
+    the same at one; at the 14B sizes 16 and 24 MB are better than 32 (one request: 2 and 1 %).
+    TESSWEAVE_OUTPUT_PREFETCH_MB overrides it; 0 switches it off."""
     import os
     mb = os.environ.get("TESSWEAVE_OUTPUT_PREFETCH_MB")
     return OUTPUT_PRODUCT_PREFETCH_BYTES if mb is None else max(0, int(mb)) << 20
