@@ -9,7 +9,9 @@
 // tile: S^T = K Q^T and O^T += V^T P^T on mma.sync with fragments read by ldmatrix (conflict-free under the
 // swizzle), online softmax in fp32.  How many bytes a block keeps in flight is the depth of the ring (up to
 // 200 KB per SM), not a matter of registers, and the producer starts before the kernel ahead of this one has
-// finished wherever the cache it reads was written by earlier steps.
+// finished wherever the cache it reads was written by earlier steps.  When its last copy has landed the
+// producer asks for weights of a later kernel to be brought into L2 (`fq.next_weights`) and leaves; the merges
+// below are the consumer warps' alone.
 //
 // With `fq` (a decode-only step whose q/k/v product has not been touched yet) the block adds the bias,
 // rotates q and k by position, and writes the new key and value to their cache page itself; the block whose
