@@ -674,17 +674,42 @@ def small_m_supported(x: torch.Tensor, w: torch.Tensor, m: int) -> bool:
             and w.shape[1] % 8 == 0 and w.is_contiguous() and x.is_contiguous())
 
 
-def small_m_split(n: int, k: int, max_slices: int = 12) -> tuple[int, int]:
+SMALL_M_ROWS_PER_BLOCK = 64      # weight rows of a block of csrc/gemm_smallm.cu (four warps of 16 rows)
+SMALL_M_BLOCKS_PER_SM = 5        # how many of its blocks an SM holds
+
+
+def small_m_split(n: int, k: int, max_slices: int = 12, sms: int | None = None) -> tuple[int, int]:
     """(slices, k per slice): enough slices that rows / 16 * slices warps fill the GPU, each
     slice a multiple of 32 wide and at least 256.  ``max_slices``: the most slices the consumer wants to add
-    (the kernel then gives a row tile to two warps where that fills the GPU better)."""
+    (the kernel then gives a row tile to two warps where that fills the GPU better).
+
+    All blocks of such a launch are resident at once and share the memory bandwidth about equally, so the launch
+    takes as long as the SM with the most blocks: among the slice counts near the one that fills the GPU, the one
+    that leaves the SMs most evenly loaded is taken.  Measured on B200, whole decode steps of the 7B-sized model
+    (3,584 rows in blocks of 64: 56 blocks per slice): 11 slices = 616 blocks, 4.2 per SM, 3.18 ms; 10 slices =
+    560 blocks, 3.8 per SM, 3.13 ms; 13 slices 3.17; 9 slices 3.18; 8 slices (448 blocks, which the kernel doubles:
+    6 per SM, two rounds) 3.30; at the 14B sizes (5,120 rows: 80 blocks per slice) 9 slices = 720 blocks 6.88 ms,
+    8 slices = 640 blocks 6.93."""
+    sms = sms or _SM_COUNT
     tiles = -(-n // 16)
     if tiles >= 1024:          # enough rows to fill the GPU without slices
         return 1, -(-k // 32) * 32
     want = max(1, min(12, max_slices, -(-_TARGET_WARPS // tiles)))
-    kper = max(256, -(-(-(-k // want)) // 32) * 32)
-    kper = min(kper, -(-k // 32) * 32)
-    return -(-k // kper), kper
+    best = None
+    for wanted in range(min(12, max_slices, want + 1), max(0, want - 3), -1):
+        kper = max(256, -(-(-(-k // wanted)) // 32) * 32)
+        kper = min(kper, -(-k // 32) * 32)
+        slices = -(-k // kper)
+        blocks = -(-n // SMALL_M_ROWS_PER_BLOCK) * slices
+        if blocks * 10 <= sms * 32 and kper >= 512:  # the kernel then gives every row tile to two warps: twice the blocks
+            blocks = -(-n // (SMALL_M_ROWS_PER_BLOCK // 2)) * slices
+        most = -(-blocks // sms)                     # blocks of the fullest SM
+        even = blocks / (most * sms) if most <= SMALL_M_BLOCKS_PER_SM else 0.0
+        # fewer slices than wanted only where that evens the load out by a tenth or more
+        score = even - 0.03 * abs(want - wanted)
+        if best is None or score > best[0]:
+            best = (score, slices, kper)
+    return best[1], best[2]
 
 
 def gemm_small_m(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: int, kper: int | None = None,

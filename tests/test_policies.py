@@ -144,3 +144,15 @@ def test_small_decode_launches_become_resident_early(monkeypatch):
     assert not ops.decode_attention_resident_early(4, 1)
     monkeypatch.setenv("TESSWEAVE_DECODE_EARLY", "1")
     assert ops.decode_attention_resident_early(10_000, 2)
+
+
+def test_split_products_load_the_sms_evenly():
+    """All blocks of a split small-batch product are resident at once, so the launch is as slow as the fullest SM:
+    3,584 rows (56 blocks of 64 rows per slice) take 10 slices (560 blocks, at most 4 on an SM), not the 11 that the
+    count of warps alone asks for (616 blocks: 24 SMs would hold 5); 5,120 rows take 9 (720 blocks, 4.9 per SM)."""
+    for n, k, slices in ((3584, 3584, 10), (3584, 18944, 10), (5120, 5120, 9), (5120, 13824, 9), (5120, 27648, 9)):
+        got, kper = ops.small_m_split(n, k, sms=148)
+        assert got == slices and kper % 32 == 0 and got * kper >= k > (got - 1) * kper
+        blocks = -(-n // ops.SMALL_M_ROWS_PER_BLOCK) * got
+        assert -(-blocks // 148) * 148 - blocks < 0.06 * blocks       # the fullest SM holds little more than its share
+    assert ops.small_m_split(4608, 3584, max_slices=4, sms=148)[0] == 4
