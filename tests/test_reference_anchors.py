@@ -25,7 +25,7 @@ ROOT = Path(__file__).resolve().parent.parent
 
 def reference():
     """The reference's package, or None."""
-    for place in (os.environ.get("TESSWEAVE_REFERENCE"), "/root/reference", str(ROOT / "baseline" / "_ref")):
+    for place in (os.environ.get("TESSWEAVE_REFERENCE"), str(ROOT / "baseline" / "_ref")):
         if place and (Path(place) / "flow_engine" / "engine.py").exists():
             if place not in sys.path:
                 sys.path.insert(0, place)
