@@ -264,6 +264,17 @@ def test_sample_greedy_and_temperature():
     out = torch.zeros(6, dtype=torch.int32, device="cuda")
     ops().sample(out, dev(logits), 6)
     assert out.tolist() == [int(logits[i].argmax()) if i != 1 else 777 for i in range(6)]
+    # a greedy row is shared by eight blocks: ties inside one block's part and across parts, rows whose length is
+    # no multiple of four (no 16-byte loads), rows shorter than the eight parts, a row of equal values
+    for vocab2 in (5, 7, 131, 1000, 4099):
+        rows = torch.randn(9, vocab2)
+        rows[1] = 3.0
+        rows[2, vocab2 - 1] = 9.0; rows[2, vocab2 // 2] = 9.0
+        rows[3, 0] = 9.0; rows[3, vocab2 - 1] = 9.0
+        rows[4, min(vocab2 - 1, vocab2 // 8 + 1)] = 9.0; rows[4, min(vocab2 - 1, vocab2 // 8 + 2)] = 9.0
+        got = torch.zeros(9, dtype=torch.int32, device="cuda")
+        ops().sample(got, dev(rows), 9)
+        assert got.tolist() == [int(torch.nonzero(rows[i] == rows[i].max())[0]) for i in range(9)], vocab2
     # temperature rows beside greedy rows; each row's draw depends on its own seed and counter only
     temps = [0.0, 0.8, 1.0, 2.0, 0.8, 0.3]
     seeds = [0, 11, 12, 13, 11, 99]
