@@ -91,6 +91,7 @@ class ModelRunner:
         self._graphs: dict[int, tuple] = {}
         self.graph_kernels: dict[int, int] = {}      # bucket -> this engine's kernels inside the captured graph
         self.launches = 0
+        self._graph_chose: int | None = None         # set by a graph step that chose a token of every row itself
 
     # ------------------------------------------------------------------ batch building
     def _stage(self, entries: list[StepEntry], pad_to: int = 0, all_rows: bool = False,
@@ -228,17 +229,29 @@ class ModelRunner:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
+            spare = torch.empty_like(self.sampled)      # `sampled` may hold tokens that the step being prepared refers to
             for _ in range(2):
                 self.model.forward(ctx, views, self._d["logit_rows"], rows, logits)
+                self._select_in_graph(logits, rows, spare)
         torch.cuda.current_stream().wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES[0]
         with torch.cuda.graph(graph):
             self.model.forward(ctx, views, self._d["logit_rows"], rows, logits)
+            # the graph also chooses a token for every row (by each row's own temperature, seed and counter, which
+            # travel in the step's staging copy) and puts the status word behind them: a step that wants a token of
+            # every row launches nothing after the graph but the copy to the host
+            self._select_in_graph(logits, rows)
         self.graph_kernels[bucket] = ops.LAUNCHES[0] - before
         self.status.zero_()
         self._graphs[bucket] = (graph, logits)
         return self._graphs[bucket]
+
+    def _select_in_graph(self, logits: torch.Tensor, rows: int, into: torch.Tensor | None = None) -> None:
+        into = self.sampled if into is None else into
+        select_tokens(into, logits, rows, self._d["temperature"].view(torch.float32),
+                      self._d["seed"].view(torch.int64), self._d["counter"].view(torch.int64))
+        into[rows:rows + 1].copy_(self.status)
 
     def _graph_step(self, entries: list[StepEntry], bucket: int, device_refs: bool = False) -> torch.Tensor:
         if not self._graphs:
@@ -255,6 +268,8 @@ class ModelRunner:
         self._stage([StepEntry(e.slot, e.tokens, e.start, []) for e in entries], pad_to=bucket, all_rows=True,
                     device_refs=device_refs)
         graph.replay()
+        if len(wanted) == len(entries):
+            self._graph_chose = bucket          # `sampled` holds a token of every row and, at [bucket], the status
         if wanted == list(range(len(wanted))):
             return logits[:len(wanted)]
         return logits.index_select(0, torch.tensor(wanted, dtype=torch.long, device=self.device))
@@ -295,28 +310,33 @@ class ModelRunner:
         i-th token chosen by the step launched just before, which is still on the device; so the next
         step can be launched before this one's tokens have reached the host.  ``finish`` waits."""
         self.stage_sampling(temperature, seed, counter)
+        self._graph_chose = None
         logits = self.step(entries, device_refs)
         m = logits.shape[0]
         host = self._sampled_hosts[self._launched % 2]
         self._launched += 1
-        if m:
-            if all(t == 0 for t in temperature):
-                select_tokens(self.sampled, logits, m)
-            else:
-                select_tokens(self.sampled, logits, m, self._d["temperature"].view(torch.float32),
-                              self._d["seed"].view(torch.int64), self._d["counter"].view(torch.int64))
-        self.sampled[m:m + 1].copy_(self.status)
-        host[:m + 1].copy_(self.sampled[:m + 1], non_blocking=True)
+        at = m                                  # where the status word lies behind the chosen ids
+        if self._graph_chose is not None:
+            at = self._graph_chose              # the captured graph has chosen the tokens already
+        else:
+            if m:
+                if all(t == 0 for t in temperature):
+                    select_tokens(self.sampled, logits, m)
+                else:
+                    select_tokens(self.sampled, logits, m, self._d["temperature"].view(torch.float32),
+                                  self._d["seed"].view(torch.int64), self._d["counter"].view(torch.int64))
+            self.sampled[m:m + 1].copy_(self.status)
+        host[:at + 1].copy_(self.sampled[:at + 1], non_blocking=True)
         done = torch.cuda.Event()
         done.record()
-        return (done, host, m)
+        return (done, host, m, at)
 
     def finish(self, pending) -> list[int]:
         """Wait for a launched step; its chosen token ids, in the order of the wanted rows."""
-        done, host, m = pending
+        done, host, m, at = pending
         done.synchronize()
-        out = host[:m + 1].tolist()
-        self._raise_on_status(out[m])
+        out = host[:at + 1].tolist()
+        self._raise_on_status(out[at])
         return out[:m]
 
     # ------------------------------------------------------------------ errors
