@@ -34,7 +34,8 @@ BENCH_CONFIG = {
 }
 PAGE_SIZE = 16
 PREFILL_TOKENS = 2048
-SHORT_CONTEXT = 512            # the benchmark configuration's prompts: generation starts here and runs to the context length
+SHORT_CONTEXT = 512             # the benchmark configuration's prompts: generation starts here and runs to the context length
+LONG_CONTEXT = 16384            # a further point: four times the benchmark's context
 LONG_PREFILL_TOKENS = 8192
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -504,6 +505,11 @@ def main() -> int:
         for b in (1, 8, 64):
             r = decode_run(model, cfg, b, SHORT_CONTEXT, max(8, args.steps // 2), 3, max_context=args.context)
             points[f"decode_b{b}_ctx{SHORT_CONTEXT}"] = round(r["tok_s"], 1)
+        # a longer context: 16,384 keys a request (the cache of the live requests is then half of what a step reads)
+        r = decode_run(model, cfg, args.batch, LONG_CONTEXT, max(8, args.steps // 2), 3)
+        points[f"decode_b{args.batch}_ctx{LONG_CONTEXT}"] = round(r["tok_s"], 1)
+        points[f"decode_b{args.batch}_ctx{LONG_CONTEXT}_hbm_frac"] = round(
+            decode_bytes(model, cfg, args.batch, r["context"]) / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 4)
         # and the whole of it: prompts of 512 tokens generating to 4,096, end to end, averaged over the run
         run = generation_run(model, cfg, args.batch, SHORT_CONTEXT, args.context)
         points[f"decode_b{args.batch}_avg_{SHORT_CONTEXT}_to_{args.context}_e2e"] = round(run["tok_s"], 1)
