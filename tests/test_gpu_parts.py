@@ -511,3 +511,37 @@ def test_embedding_and_head_parts_alone(dtype):
         assert torch.allclose(logits[:7], want, atol=2e-5 if dtype == torch.float32 else 2e-3, rtol=0)
     with pytest.raises(ValueError, match="tied head"):
         build_part("head", PartSpec("linear_head", {"vocab": vocab + 1, "hidden": hidden}), rt, tied=emb.shared_matrix())
+
+
+def test_attention_shares_out_what_is_asked_into_l2(monkeypatch):
+    """What a decode-only step asks into L2 ahead of its kernel: the attention kernel gets the head of the weights
+    that the part after it streams first, its output product the part that follows; a short cache leaves all of it
+    to the output product; a step that is not decode-only, or a block that announces nothing, asks for nothing."""
+    for name in ("TESSWEAVE_WEIGHT_PREFETCH_MB", "TESSWEAVE_OUTPUT_PREFETCH_MB", "TESSWEAVE_WEIGHT_PREFETCH_MIN_KB"):
+        monkeypatch.delenv(name, raising=False)
+    rt = Runtime(torch.device("cuda"), torch.bfloat16)
+    mixer = build_part("mixer", PartSpec("gqa_attention", {"hidden": 256, "n_heads": 4, "n_kv_heads": 2, "head_dim": 64,
+                                                            "qkv_bias": True, "position": PartSpec("rope", {"theta": 1e4})}), rt)
+    upcoming = torch.zeros(5000, 8192, dtype=torch.bfloat16, device="cuda")        # 78 MB
+    mb = 1 << 20
+
+    def plan(kv_len, q_len=1):
+        ctx = hand_made_context(rt, [kv_len - 1] * q_len, [0] * q_len, [0], [0], [q_len], [kv_len])
+        ctx.upcoming_weights = upcoming
+        return ctx, mixer._prefetch_plan(ctx)
+
+    ctx, (first, later) = plan(8192)                                   # 8,192 keys x 2 x 2 heads x 64 x 2 bytes = 4 MB
+    assert first.data_ptr() == upcoming.data_ptr() and first.numel() * 2 == 24 * mb
+    assert later.data_ptr() == upcoming.data_ptr() + 24 * mb and later.numel() * 2 == 24 * mb
+    _, (first, later) = plan(512)                                      # 256 KB of cache: the kernel is too short
+    assert first is None and later.data_ptr() == upcoming.data_ptr() and later.numel() * 2 == 24 * mb
+    _, (first, later) = plan(8192, q_len=3)                            # a prompt portion: not the fused decode path
+    assert first is None and later is None
+    ctx.upcoming_weights = None
+    assert mixer._prefetch_plan(ctx) == (None, None)
+    monkeypatch.setenv("TESSWEAVE_OUTPUT_PREFETCH_MB", "70")           # more than is left: what there is
+    _, (first, later) = plan(8192)
+    assert later.numel() * 2 == upcoming.numel() * 2 - 24 * mb
+    monkeypatch.setenv("TESSWEAVE_WEIGHT_PREFETCH_MB", "0")
+    monkeypatch.setenv("TESSWEAVE_OUTPUT_PREFETCH_MB", "0")
+    assert plan(8192)[1] == (None, None)
